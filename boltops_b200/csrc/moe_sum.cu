@@ -1,0 +1,95 @@
+// Top-k combine: out[m, :] = cast(scale * sum_k f32(in[m, k, :]) [* w[m, k]]).
+// HBM-bound: (topk + 1) * elem bytes per output element, 128-bit accesses,
+// k ascending with an fp32 accumulator (matches the reference's summation order).
+#include "common.cuh"
+
+namespace bolt {
+namespace {
+
+template <typename TIn, typename TOut, int VEC>
+__global__ void __launch_bounds__(256) k_moe_sum(const TIn* __restrict__ in, TOut* __restrict__ out,
+                                                 int64_t num_tokens, int topk, int n, float scale,
+                                                 const float* __restrict__ weights) {
+  using VI = Vec<TIn, VEC>;
+  using VO = Vec<TOut, VEC>;
+  const int nvec = n / VEC;
+  const int64_t total = num_tokens * nvec;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = idx / nvec;
+    const int c = (int)(idx - m * nvec) * VEC;
+    const TIn* base = in + (m * topk) * (int64_t)n + c;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    for (int k = 0; k < topk; ++k) {
+      const VI v = *reinterpret_cast<const VI*>(base + (int64_t)k * n);
+      if (weights != nullptr) {
+        const float w = weights[m * topk + k];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(to_f32(v.v[i]), w));
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] += to_f32(v.v[i]);
+      }
+    }
+    VO o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o.v[i] = from_f32<TOut>(acc[i] * scale);
+    *reinterpret_cast<VO*>(out + m * (int64_t)n + c) = o;
+  }
+}
+
+template <typename TIn, typename TOut>
+int launch_sum(const void* in, void* out, int64_t num_tokens, int topk, int n, float scale,
+               const float* weights, cudaStream_t st) {
+  constexpr int VEC = 16 / (sizeof(TIn) > sizeof(TOut) ? sizeof(TIn) : sizeof(TOut));
+  const bool vec_ok = (n % VEC == 0) && (reinterpret_cast<uintptr_t>(in) % 16 == 0) &&
+                      (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+  const int64_t total = vec_ok ? num_tokens * (n / VEC) : num_tokens * n;
+  if (total == 0) return BOLT_OK;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 32;
+  if (blocks > cap) blocks = cap;
+  if (vec_ok)
+    k_moe_sum<TIn, TOut, VEC><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const TIn*>(in), static_cast<TOut*>(out), num_tokens, topk, n, scale, weights);
+  else
+    k_moe_sum<TIn, TOut, 1><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const TIn*>(in), static_cast<TOut*>(out), num_tokens, topk, n, scale, weights);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+template <typename TIn>
+int dispatch_out(const void* in, void* out, int out_dtype, int64_t num_tokens, int topk, int n,
+                 float scale, const float* weights, cudaStream_t st) {
+  switch (out_dtype) {
+    case BOLT_BF16:
+      return launch_sum<TIn, __nv_bfloat16>(in, out, num_tokens, topk, n, scale, weights, st);
+    case BOLT_F16: return launch_sum<TIn, __half>(in, out, num_tokens, topk, n, scale, weights, st);
+    case BOLT_F32: return launch_sum<TIn, float>(in, out, num_tokens, topk, n, scale, weights, st);
+    default: set_error("moe_sum: unsupported output dtype %d", out_dtype); return BOLT_ERR_INVALID;
+  }
+}
+
+}  // namespace
+}  // namespace bolt
+
+extern "C" int bolt_moe_sum(const void* in, int in_dtype, void* out, int out_dtype,
+                            int64_t num_tokens, int topk, int n, float scale, const float* weights,
+                            void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(num_tokens >= 0 && topk > 0 && n > 0, "moe_sum: bad shape");
+  BOLT_REQUIRE(num_tokens == 0 || (in && out), "moe_sum: null pointer");
+  switch (in_dtype) {
+    case BOLT_BF16:
+      return dispatch_out<__nv_bfloat16>(in, out, out_dtype, num_tokens, topk, n, scale, weights, st);
+    case BOLT_F16:
+      return dispatch_out<__half>(in, out, out_dtype, num_tokens, topk, n, scale, weights, st);
+    case BOLT_F32:
+      return dispatch_out<float>(in, out, out_dtype, num_tokens, topk, n, scale, weights, st);
+    default: set_error("moe_sum: unsupported input dtype %d", in_dtype); return BOLT_ERR_INVALID;
+  }
+}

@@ -1,0 +1,268 @@
+// Dynamic activation quantisation (per token / per 1xG group, e4m3 or int8) and
+// the row gather into the expert-sorted layout.  Both are HBM-bound: 128-bit
+// loads/stores, one pass over the data.
+#include "common.cuh"
+
+namespace bolt {
+namespace {
+
+template <int QT>
+struct QTraits;
+template <>
+struct QTraits<BOLT_FP8_E4M3> {
+  using type = uint8_t;
+  static constexpr float kMax = 448.0f;
+  __device__ static __forceinline__ uint8_t cvt(float v) { return f32_to_e4m3(v); }
+};
+template <>
+struct QTraits<BOLT_INT8> {
+  using type = int8_t;
+  static constexpr float kMax = 127.0f;
+  __device__ static __forceinline__ int8_t cvt(float v) { return f32_to_i8(v); }
+};
+
+// scale and its reciprocal from the group absmax.
+template <int QT, bool POW2>
+__device__ __forceinline__ void scale_from_amax(float amax, float& scale, float& inv) {
+  if (POW2) {
+    const float raw = fmaxf(amax, 1.0e-10f) * (float)(1.0 / 448.0);
+    const float lg = ceilf((float)log2((double)raw));
+    scale = ldexpf(1.0f, (int)lg);
+    inv = ldexpf(1.0f, -(int)lg);
+  } else {
+    scale = __fdiv_rn(fmaxf(amax, 1.0e-10f), QTraits<QT>::kMax);
+    inv = __frcp_rn(scale);
+  }
+}
+
+template <int QT, bool POW2>
+__device__ __forceinline__ typename QTraits<QT>::type quant_one(float x, float inv) {
+  float y = x * inv;
+  if (POW2) y = fminf(fmaxf(y, -448.0f), 448.0f);
+  return QTraits<QT>::cvt(y);
+}
+
+// ---- small groups: TPG threads (a power of two <= 32) share one group ----------
+template <typename TIn, int QT, bool POW2>
+__global__ void __launch_bounds__(256) k_quant_group(const TIn* __restrict__ x,
+                                                     typename QTraits<QT>::type* __restrict__ q,
+                                                     float* __restrict__ scales,
+                                                     int64_t num_groups, int tpg) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  using VIn = Vec<TIn, VEC>;
+  using VOut = Vec<typename QTraits<QT>::type, VEC>;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t grp = tid / tpg;
+  const bool live = grp < num_groups;
+  VIn v;
+  float amax = 0.f;
+  if (live) {
+    v = reinterpret_cast<const VIn*>(x)[tid];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(to_f32(v.v[i])));
+  }
+  for (int o = tpg >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (!live) return;
+  float scale, inv;
+  scale_from_amax<QT, POW2>(amax, scale, inv);
+  VOut o;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) o.v[i] = quant_one<QT, POW2>(to_f32(v.v[i]), inv);
+  reinterpret_cast<VOut*>(q)[tid] = o;
+  if ((tid % tpg) == 0) scales[grp] = scale;
+}
+
+// ---- one CTA per group (large or oddly sized groups) ---------------------------
+template <typename TIn, int QT, bool POW2>
+__global__ void __launch_bounds__(256) k_quant_row(const TIn* __restrict__ x,
+                                                   typename QTraits<QT>::type* __restrict__ q,
+                                                   float* __restrict__ scales, int group) {
+  const int64_t g = blockIdx.x;
+  const TIn* xr = x + g * (int64_t)group;
+  typename QTraits<QT>::type* qr = q + g * (int64_t)group;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < group; i += blockDim.x) amax = fmaxf(amax, fabsf(to_f32(xr[i])));
+  __shared__ float red[8];
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  float scale, inv;
+  scale_from_amax<QT, POW2>(amax, scale, inv);
+  for (int i = threadIdx.x; i < group; i += blockDim.x)
+    qr[i] = quant_one<QT, POW2>(to_f32(xr[i]), inv);
+  if (threadIdx.x == 0) scales[g] = scale;
+}
+
+// vectorised variant of the above: group % VEC == 0 and 16-byte aligned rows.
+template <typename TIn, int QT, bool POW2, int NV>
+__global__ void __launch_bounds__(256) k_quant_row_vec(const TIn* __restrict__ x,
+                                                       typename QTraits<QT>::type* __restrict__ q,
+                                                       float* __restrict__ scales, int group) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  using VIn = Vec<TIn, VEC>;
+  using VOut = Vec<typename QTraits<QT>::type, VEC>;
+  const int64_t g = blockIdx.x;
+  const VIn* xr = reinterpret_cast<const VIn*>(x + g * (int64_t)group);
+  VOut* qr = reinterpret_cast<VOut*>(q + g * (int64_t)group);
+  const int nvec = group / VEC;
+  VIn cache[NV];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < nvec) {
+      cache[j] = xr[i];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(to_f32(cache[j].v[e])));
+    }
+  }
+  for (int i = threadIdx.x + NV * 256; i < nvec; i += 256) {
+    VIn v = xr[i];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(to_f32(v.v[e])));
+  }
+  __shared__ float red[8];
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  float scale, inv;
+  scale_from_amax<QT, POW2>(amax, scale, inv);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < nvec) {
+      VOut o;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o.v[e] = quant_one<QT, POW2>(to_f32(cache[j].v[e]), inv);
+      qr[i] = o;
+    }
+  }
+  for (int i = threadIdx.x + NV * 256; i < nvec; i += 256) {
+    VIn v = xr[i];
+    VOut o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o.v[e] = quant_one<QT, POW2>(to_f32(v.v[e]), inv);
+    qr[i] = o;
+  }
+  if (threadIdx.x == 0) scales[g] = scale;
+}
+
+template <typename TIn, int QT, bool POW2>
+int launch_quant(const void* x, int64_t rows, int cols, int group, void* q, float* scales,
+                 cudaStream_t st) {
+  using QTy = typename QTraits<QT>::type;
+  constexpr int VEC = 16 / sizeof(TIn);
+  const int64_t num_groups = rows * (int64_t)(cols / group);
+  if (num_groups == 0) return BOLT_OK;
+  BOLT_REQUIRE(num_groups < (1ll << 31), "quant: too many groups");
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(q) % (VEC * sizeof(QTy)) == 0) &&
+                       (group % VEC == 0);
+  const int tpg = aligned ? group / VEC : 0;
+  if (aligned && tpg <= 32 && (tpg & (tpg - 1)) == 0) {
+    const int64_t threads = num_groups * tpg;
+    const int64_t blocks = (threads + 255) / 256;
+    k_quant_group<TIn, QT, POW2><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const TIn*>(x), static_cast<QTy*>(q), scales, num_groups, tpg);
+  } else if (aligned) {
+    k_quant_row_vec<TIn, QT, POW2, 4><<<(unsigned)num_groups, 256, 0, st>>>(
+        static_cast<const TIn*>(x), static_cast<QTy*>(q), scales, group);
+  } else {
+    k_quant_row<TIn, QT, POW2><<<(unsigned)num_groups, 256, 0, st>>>(
+        static_cast<const TIn*>(x), static_cast<QTy*>(q), scales, group);
+  }
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+template <typename TIn>
+int dispatch_quant(const void* x, int64_t rows, int cols, int group, int q_dtype, int power2,
+                   void* q, float* scales, cudaStream_t st) {
+  if (q_dtype == BOLT_FP8_E4M3) {
+    return power2 ? launch_quant<TIn, BOLT_FP8_E4M3, true>(x, rows, cols, group, q, scales, st)
+                  : launch_quant<TIn, BOLT_FP8_E4M3, false>(x, rows, cols, group, q, scales, st);
+  }
+  return launch_quant<TIn, BOLT_INT8, false>(x, rows, cols, group, q, scales, st);
+}
+
+// ---- gather into expert-sorted rows ----------------------------------------------
+__global__ void __launch_bounds__(256) k_gather_rows(const uint4* __restrict__ src,
+                                                     int num_tokens, int row_vecs,
+                                                     const float* __restrict__ src_scale,
+                                                     int groups,
+                                                     const int32_t* __restrict__ sorted_ids,
+                                                     const int32_t* __restrict__ num_valid,
+                                                     int capacity, uint4* __restrict__ dst,
+                                                     float* __restrict__ dst_scale,
+                                                     int64_t dst_scale_ld) {
+  const int valid = min(*num_valid, capacity);
+  for (int row = blockIdx.x; row < valid; row += gridDim.x) {
+    const int token = sorted_ids[row] & 0xFFFFFF;
+    if (token >= num_tokens) continue;  // pad row: never consumed, left untouched
+    const uint4* s = src + (int64_t)token * row_vecs;
+    uint4* d = dst + (int64_t)row * row_vecs;
+    for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = __ldg(s + i);
+    if (src_scale != nullptr) {
+      if (groups == 1) {
+        if (threadIdx.x == 0) dst_scale[row] = src_scale[token];
+      } else {
+        for (int g = threadIdx.x; g < groups; g += blockDim.x)
+          dst_scale[(int64_t)g * dst_scale_ld + row] = src_scale[(int64_t)token * groups + g];
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace bolt
+
+extern "C" int bolt_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int group,
+                               int q_dtype, int power2, void* q, float* scales, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(rows >= 0 && cols > 0, "quant: bad shape");
+  BOLT_REQUIRE(group > 0 && cols % group == 0, "quant: group %d does not divide cols %d", group,
+               cols);
+  BOLT_REQUIRE(q_dtype == BOLT_FP8_E4M3 || q_dtype == BOLT_INT8, "quant: bad q_dtype %d", q_dtype);
+  BOLT_REQUIRE(!power2 || q_dtype == BOLT_FP8_E4M3, "quant: power-of-two scales need e4m3");
+  BOLT_REQUIRE(rows == 0 || (x && q && scales), "quant: null pointer");
+  switch (x_dtype) {
+    case BOLT_BF16:
+      return dispatch_quant<__nv_bfloat16>(x, rows, cols, group, q_dtype, power2, q, scales, st);
+    case BOLT_F16:
+      return dispatch_quant<__half>(x, rows, cols, group, q_dtype, power2, q, scales, st);
+    case BOLT_F32:
+      return dispatch_quant<float>(x, rows, cols, group, q_dtype, power2, q, scales, st);
+    default:
+      set_error("quant: unsupported input dtype %d", x_dtype);
+      return BOLT_ERR_INVALID;
+  }
+}
+
+extern "C" int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
+                                const float* src_scale, int groups, const int32_t* sorted_ids,
+                                const int32_t* num_valid_ids, int capacity, void* dst,
+                                float* dst_scale, int64_t dst_scale_ld, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "gather: row_bytes must be a multiple of 16");
+  BOLT_REQUIRE(capacity >= 0 && num_tokens >= 0, "gather: bad sizes");
+  if (capacity == 0 || num_tokens == 0) return BOLT_OK;
+  BOLT_REQUIRE(src && dst && sorted_ids && num_valid_ids, "gather: null pointer");
+  BOLT_REQUIRE((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0,
+               "gather: buffers must be 16-byte aligned");
+  BOLT_REQUIRE(src_scale == nullptr || (dst_scale != nullptr && groups >= 1),
+               "gather: scale arguments inconsistent");
+  const int grid = capacity < 148 * 16 ? capacity : 148 * 16;
+  k_gather_rows<<<grid, 256, 0, st>>>(static_cast<const uint4*>(src), num_tokens, row_bytes / 16,
+                                      src_scale, groups, sorted_ids, num_valid_ids, capacity,
+                                      static_cast<uint4*>(dst), dst_scale, dst_scale_ld);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}

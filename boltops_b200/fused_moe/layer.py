@@ -1,0 +1,269 @@
+"""Orchestration of one fused-MoE layer on a B200.
+
+Drop-in for the reference's ``fused_experts`` / ``fused_experts_impl``
+(boltops/fused_moe/triton/fused_moe.py:647-724, 1200-1777; reference paths are
+relative to the reference project root): same arguments, defaults, error
+behaviour and numerics contract; the schedule is B200-native:
+
+    sort (CK format, 128-row units) -> [quantise hidden once per token]
+    -> gather rows into the expert-sorted layout
+    -> grouped GEMM 1 with SiLU(gate)*up (+ 1x128 re-quantisation) in its epilogue
+    -> grouped GEMM 2 with the router weight in its epilogue, scattered to [M, topk, H]
+    -> top-k combine.
+
+No step synchronises the host; the padded row count stays on the device.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+
+from .. import _cabi
+from . import ops
+from .activation import activation_quant, apply_activation, normalize_moe_activation
+
+_FLOAT_OUT = (torch.float16, torch.bfloat16, torch.float32)
+
+
+def _chunk_size() -> int:
+    raw = os.environ.get("BOLTOPS_FUSED_MOE_CHUNK_SIZE",
+                         os.environ.get("TRITON_FUSED_MOE_CHUNK_SIZE", "32768"))
+    size = int(raw)
+    if size <= 0:
+        raise ValueError("TRITON_FUSED_MOE_CHUNK_SIZE must be positive")
+    return size
+
+
+def _gemm_kind(w_dtype, use_fp8, use_int8, per_channel, block_shape) -> int:
+    if use_fp8:
+        return _cabi.GEMM_FP8_CHANNEL if per_channel else _cabi.GEMM_FP8_BLOCK
+    if use_int8:
+        return _cabi.GEMM_INT8_CHANNEL if per_channel else _cabi.GEMM_INT8_BLOCK
+    if w_dtype == torch.bfloat16:
+        return _cabi.GEMM_BF16
+    if w_dtype == torch.float16:
+        return _cabi.GEMM_F16
+    raise NotImplementedError(f"unquantised experts in {w_dtype} are not built in boltops_b200")
+
+
+def fused_experts_impl(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    output_dtype: Optional[torch.dtype] = None,
+    inplace: bool = False,
+    activation: str = "silu",
+    is_gated: Optional[bool] = None,
+    b1: Optional[torch.Tensor] = None,
+    b2: Optional[torch.Tensor] = None,
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    use_int4_w4a8: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    expert_map: Optional[torch.Tensor] = None,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    w1_zp: Optional[torch.Tensor] = None,
+    w2_zp: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[List[int]] = None,
+    no_combine: bool = False,
+    routed_scaling_factor: Optional[float] = 1.0,
+    gemm1_alpha: Optional[float] = None,
+    gemm1_limit: Optional[float] = None,
+    activation_situ_beta: Optional[float] = None,
+    activation_situ_linear_beta: Optional[float] = None,
+    use_mxfp4_w4a8: bool = False,
+    use_ue8m0: bool = False,
+    use_mxfp8: bool = False,
+    gemm1_beta: Optional[float] = None,
+) -> torch.Tensor:
+    # ---- variants outside this build -------------------------------------------------
+    if use_mxfp4_w4a8 or use_mxfp8:
+        name = "MXFP8" if use_mxfp8 else "MXFP4"
+        if any((use_fp8_w8a8, use_int8_w8a8, use_int8_w8a16, use_int4_w4a16, use_int4_w4a8,
+                per_channel_quant)):
+            raise ValueError(f"{name} cannot be combined with other quantization flags")
+        raise NotImplementedError(f"{name} experts are not built in boltops_b200")
+    if use_int8_w8a16 or use_int4_w4a16 or use_int4_w4a8:
+        raise NotImplementedError("weight-only / int4 experts are not built in boltops_b200")
+    if w1_zp is not None or w2_zp is not None:
+        raise NotImplementedError("zero points are not built in boltops_b200")
+
+    # ---- contract checks (same order and exception types as the reference) ------------
+    if use_fp8_w8a8:
+        e8m0 = getattr(torch, "float8_e8m0fnu", None)
+        for name, scale in (("w1_scale", w1_scale), ("w2_scale", w2_scale),
+                            ("a1_scale", a1_scale), ("a2_scale", a2_scale)):
+            if scale is not None and (not scale.is_floating_point() or scale.dtype == e8m0):
+                raise ValueError(
+                    f"{name} must be a decoded floating-point multiplier for FP8; "
+                    "convert checkpoint UE8M0 scales during weight preparation")
+    if use_ue8m0 and (not use_fp8_w8a8 or block_shape is None or per_channel_quant):
+        raise ValueError(
+            "use_ue8m0 requires use_fp8_w8a8=True, block_shape, and per_channel_quant=False")
+    if routed_scaling_factor is None:
+        routed_scaling_factor = 1.0
+    activation, is_gated = normalize_moe_activation(activation, is_gated)
+    if gemm1_beta is not None:
+        raise ValueError("gemm1_beta requires native MXFP8 or static MXFP4")
+    if output_dtype is None:
+        output_dtype = hidden_states.dtype
+
+    assert hidden_states.shape[1] == w1.shape[2], "Hidden size mismatch"
+    assert topk_weights.shape == topk_ids.shape, "topk shape mismatch"
+    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    assert w1.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert w2.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert hidden_states.dtype in (torch.float32, torch.float16, torch.bfloat16, torch.int8,
+                                   torch.float8_e4m3fn)
+    assert output_dtype in _FLOAT_OUT, "Unsupported output_dtype"
+    if not hidden_states.is_cuda:
+        raise ValueError("boltops_b200 kernels need CUDA tensors (there is no CPU path)")
+
+    quantised = use_fp8_w8a8 or use_int8_w8a8
+    if quantised and not per_channel_quant and block_shape is None:
+        raise NotImplementedError("per-tensor quantised experts are not built in boltops_b200")
+    if quantised and block_shape is not None and not per_channel_quant:
+        if list(block_shape) != [128, 128]:
+            raise NotImplementedError("only block_shape [128, 128] is built in boltops_b200")
+    block_mode = quantised and not per_channel_quant
+    q_dtype = torch.float8_e4m3fn if use_fp8_w8a8 else torch.int8
+    kind = _gemm_kind(w1.dtype, use_fp8_w8a8, use_int8_w8a8, per_channel_quant, block_shape)
+    if quantised:
+        assert w1_scale is not None and w2_scale is not None, "weight scales are required"
+        assert w1.dtype == q_dtype and w2.dtype == q_dtype, "weight dtype does not match the flags"
+    else:
+        assert hidden_states.dtype == w1.dtype, "hidden_states / weight dtype mismatch"
+    if not w1.is_contiguous():
+        w1 = w1.contiguous()
+    if not w2.is_contiguous():
+        w2 = w2.contiguous()
+
+    num_tokens, hidden = hidden_states.shape
+    e_local, n1, _ = w1.shape
+    model_dim = w2.shape[1]
+    if global_num_experts == -1:
+        global_num_experts = expert_map.numel() if expert_map is not None else e_local
+    topk = topk_ids.shape[1]
+    act_dim = n1 // 2 if is_gated else n1
+    assert w2.shape[2] == act_dim, "w2 inner size does not match the activation output"
+    dev = hidden_states.device
+    mid_dtype = output_dtype
+
+    if no_combine:
+        assert not inplace, "no_combine + inplace is not supported"
+        out = torch.empty((num_tokens, topk, model_dim), device=dev, dtype=output_dtype)
+    elif inplace:
+        out = hidden_states
+    else:
+        out = torch.empty((num_tokens, model_dim), device=dev, dtype=output_dtype)
+    if num_tokens == 0:
+        return out
+
+    if topk_weights.dtype != torch.float32:
+        topk_weights = topk_weights.to(torch.float32)
+    expert_mask = (expert_map >= 0).to(torch.int32) if expert_map is not None else None
+    fused_silu = (is_gated and activation == "silu" and gemm1_alpha is None
+                  and gemm1_limit is None)
+    needs_router_weight = not (apply_router_weight_on_input or no_combine)
+    w1_scale_c = w1_scale.contiguous().float() if quantised else None
+    w2_scale_c = w2_scale.contiguous().float() if quantised else None
+
+    chunk = _chunk_size()
+    for begin in range(0, num_tokens, chunk):
+        end = min(begin + chunk, num_tokens)
+        m = end - begin
+        x = hidden_states[begin:end]
+        ids = topk_ids[begin:end]
+        wts = topk_weights[begin:end]
+
+        # ---- sort -----------------------------------------------------------------------
+        sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
+            ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
+            alloc_moe_buf=False)
+        cap = sorted_ids.shape[0]
+
+        # ---- A1: quantise once per token, then gather into sorted rows --------------------
+        a_scale = None
+        if quantised:
+            if x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+                if block_mode:
+                    x_q, x_s = ops.per_block_quant(x, 128, q_dtype, scale_ue8m0=use_ue8m0)
+                else:
+                    x_q, x_s = ops.per_token_quant(x, quant_dtype=q_dtype)
+            else:
+                assert a1_scale is not None, "pre-quantised hidden_states need a1_scale"
+                x_q = x
+                x_s = a1_scale[begin:end] if a1_scale.ndim == 2 else a1_scale
+                x_s = x_s.float()
+            a_sorted, a_scale = ops.gather_rows(x_q, sorted_ids, num_valid, cap, x_s)
+        else:
+            a_sorted, _ = ops.gather_rows(x, sorted_ids, num_valid, cap)
+
+        common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
+                      sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
+
+        # ---- GEMM1 (+ activation, + re-quantisation) ---------------------------------------
+        act_scale = None
+        fuse_quant = fused_silu and block_mode and not use_ue8m0
+        if fuse_quant:
+            act = torch.empty((cap, act_dim), device=dev, dtype=q_dtype)
+            act_scale = torch.empty((act_dim // 128, cap), device=dev, dtype=torch.float32)
+            ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
+                             a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
+                             c_scale=act_scale, c_scale_ld=cap, mid_dtype=mid_dtype,
+                             mul_routed_weight=apply_router_weight_on_input, **common)
+        else:
+            if fused_silu:
+                act_f = torch.empty((cap, act_dim), device=dev, dtype=mid_dtype)
+                ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL, a=a_sorted, b=w1, c=act_f,
+                                 a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
+                                 mid_dtype=mid_dtype,
+                                 mul_routed_weight=apply_router_weight_on_input, **common)
+            else:
+                c1 = torch.empty((cap, n1), device=dev, dtype=mid_dtype)
+                ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1, c=c1,
+                                 a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
+                                 mul_routed_weight=apply_router_weight_on_input, **common)
+                act_f = torch.empty((cap, act_dim), device=dev, dtype=mid_dtype)
+                apply_activation(activation, is_gated, act_f, c1, gemm1_alpha, gemm1_limit,
+                                 activation_situ_beta, activation_situ_linear_beta,
+                                 rows_dev=num_valid)
+            if quantised:
+                if block_mode:
+                    act, s = ops.per_block_quant(act_f, 128, q_dtype, scale_ue8m0=use_ue8m0)
+                    act_scale = s.t().contiguous()          # [act_dim/128, cap]
+                else:
+                    act, s = ops.per_token_quant(act_f, quant_dtype=q_dtype)
+                    act_scale = s.reshape(-1)
+            else:
+                act = act_f
+
+        # ---- GEMM2 (router weight in the epilogue, scattered to [m, topk, H]) -------------
+        if expert_map is not None:
+            c3 = torch.zeros((m, topk, model_dim), device=dev, dtype=output_dtype)
+        elif no_combine:
+            c3 = out[begin:end]
+        else:
+            c3 = torch.empty((m, topk, model_dim), device=dev, dtype=output_dtype)
+        ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2, c=c3.view(m * topk, model_dim),
+                         a_scale=act_scale, a_scale_ld=cap, b_scale=w2_scale_c, bias=b2,
+                         scatter=True, mul_routed_weight=needs_router_weight, **common)
+
+        # ---- combine ----------------------------------------------------------------------------
+        if no_combine:
+            if c3.data_ptr() != out[begin:end].data_ptr():
+                out[begin:end].copy_(c3)
+        else:
+            ops.moe_sum(c3, out[begin:end], routed_scaling_factor)
+    return out

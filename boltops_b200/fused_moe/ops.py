@@ -1,0 +1,267 @@
+"""Python faces of the C-ABI kernels (allocation, argument checks, stream lookup).
+
+Names and return conventions follow the reference helpers they replace
+(reference paths are relative to the reference project root):
+
+* ``moe_sorting_ck``        -- boltops/fused_moe/triton/fused_moe.py:441-485
+* ``moe_align_block_size``  -- boltops/fused_moe/triton/fused_moe.py:330-439
+* ``per_token_quant`` / ``per_block_quant`` -- boltops/fused_moe/triton/moe_compat.py:55-106
+* ``moe_sum``               -- boltops/fused_moe/triton/fused_moe.py:134-188
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _cabi
+from .._cabi import check, dtype_code, ptr, stream_of
+
+SORT_UNIT = 128  # row-tile of the grouped GEMM == padding unit of the sort
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("boltops_b200 kernels need CUDA tensors (there is no CPU path)")
+
+
+def ceil_to(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+# ---------------------------------------------------------------------------
+# sort
+# ---------------------------------------------------------------------------
+def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
+                   model_dim: Optional[int] = None, moebuf_dtype: Optional[torch.dtype] = None,
+                   block_size: int = 32, expert_mask: Optional[torch.Tensor] = None,
+                   alloc_moe_buf: bool = True):
+    """CK-format sort.  Returns ``(sorted_ids, sorted_weights, sorted_expert_ids,
+    num_valid_ids, tokens_positions_per_expert, moe_buf)`` like the reference.
+
+    ``sorted_ids``/``sorted_weights`` are allocated with the capacity rounded up to
+    a multiple of ``block_size`` so that the last row tile is always addressable.
+    """
+    _require_cuda(topk_ids, topk_weights, expert_mask)
+    if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape:
+        raise AssertionError("topk shape mismatch")
+    if topk_weights.dtype != torch.float32:
+        raise AssertionError("topk_weights must be float32")
+    lib = _cabi.load()
+    dev = topk_ids.device
+    m, topk = topk_ids.shape
+    if topk_ids.dtype != torch.int32:
+        topk_ids = topk_ids.to(torch.int32)
+    topk_ids = topk_ids.contiguous()
+    topk_weights = topk_weights.contiguous()
+    if expert_mask is not None:
+        expert_mask = expert_mask.to(torch.int32).contiguous()
+    cap = m * topk + num_experts * block_size - topk
+    cap_alloc = ceil_to(max(cap, 0), block_size)
+    blocks = cap_alloc // block_size
+    sorted_ids = torch.empty(cap_alloc, dtype=torch.int32, device=dev)
+    sorted_weights = torch.empty(cap_alloc, dtype=torch.float32, device=dev)
+    sorted_expert_ids = torch.empty(max(blocks, 1), dtype=torch.int32, device=dev)
+    positions = torch.empty(2 * num_experts, dtype=torch.int32, device=dev)
+    num_valid = torch.empty(1, dtype=torch.int32, device=dev)
+    moe_buf = None
+    if alloc_moe_buf and model_dim is not None and moebuf_dtype is not None:
+        moe_buf = torch.empty((m, model_dim), dtype=moebuf_dtype, device=dev)
+    ws_bytes = lib.bolt_moe_sort_workspace_bytes(m, topk, num_experts)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.bolt_moe_sort_ck(
+            ptr(topk_ids), ptr(topk_weights), ptr(expert_mask), m, topk, num_experts, block_size,
+            ptr(sorted_ids), ptr(sorted_weights), ptr(sorted_expert_ids), ptr(positions),
+            ptr(num_valid), ptr(moe_buf),
+            0 if moe_buf is None else moe_buf.numel() * moe_buf.element_size(),
+            ptr(ws), ws_bytes, stream_of(topk_ids)))
+    return sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int,
+                         expert_map: Optional[torch.Tensor] = None
+                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """vLLM-format sort: ``(sorted_token_ids, expert_ids, num_tokens_post_padded)``."""
+    _require_cuda(topk_ids, expert_map)
+    lib = _cabi.load()
+    dev = topk_ids.device
+    ids = topk_ids.to(torch.int32).contiguous()
+    numel = ids.numel()
+    cap = numel + num_experts * (block_size - 1)
+    blocks = (cap + block_size - 1) // block_size
+    sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device=dev)
+    num_post = torch.empty(1, dtype=torch.int32, device=dev)
+    if expert_map is not None:
+        expert_map = expert_map.to(torch.int32).contiguous()
+    ws_bytes = lib.bolt_moe_sort_workspace_bytes(numel, 1, num_experts)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.bolt_moe_align_block_size(
+            ptr(ids), numel, num_experts, block_size, ptr(expert_map), ptr(sorted_ids),
+            ptr(expert_ids), ptr(num_post), ptr(ws), ws_bytes, stream_of(ids)))
+    return sorted_ids, expert_ids, num_post
+
+
+# ---------------------------------------------------------------------------
+# quantisation
+# ---------------------------------------------------------------------------
+def quant_rows(x: torch.Tensor, quant_dtype: torch.dtype, group: Optional[int] = None,
+               scale_ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dynamic quantisation of a 2-D tensor per row (``group=None``) or per
+    ``1 x group`` block.  Returns ``(q, scales[rows, cols/group])``."""
+    _require_cuda(x)
+    if x.dim() != 2:
+        raise ValueError("quant_rows expects a 2-D tensor")
+    assert x.is_contiguous(), "x_in must be contiguous"
+    lib = _cabi.load()
+    rows, cols = x.shape
+    g = cols if group is None else group
+    q = torch.empty((rows, cols), dtype=quant_dtype, device=x.device)
+    scales = torch.empty((rows, cols // g), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.bolt_quant_rows(ptr(x), dtype_code(x.dtype), rows, cols, g,
+                                  dtype_code(quant_dtype), int(scale_ue8m0), ptr(q), ptr(scales),
+                                  stream_of(x)))
+    return q, scales
+
+
+def per_token_quant(x: torch.Tensor, scale: Optional[torch.Tensor] = None,
+                    quant_dtype: torch.dtype = torch.int8, scale_ue8m0: bool = False):
+    """Per-token dynamic quantisation; scale has shape ``[*x.shape[:-1], 1]``."""
+    if scale is not None:
+        raise ValueError("unsupported: static per token quant")
+    shape = x.shape
+    q, s = quant_rows(x.reshape(-1, shape[-1]), quant_dtype, None, scale_ue8m0)
+    return q.view(shape), s.view(*shape[:-1], 1)
+
+
+def per_block_quant(x: torch.Tensor, block_n: int = 128, quant_dtype: torch.dtype = torch.int8,
+                    scale_ue8m0: bool = False):
+    """1 x ``block_n`` group quantisation of a 2-D tensor: ``(q[m,n], s[m,n/block_n])``."""
+    assert x.shape[-1] % block_n == 0, f"block size {block_n} not match {x.shape[-1]}"
+    return quant_rows(x, quant_dtype, block_n, scale_ue8m0)
+
+
+# ---------------------------------------------------------------------------
+# gather / combine
+# ---------------------------------------------------------------------------
+def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Tensor,
+                capacity: int, src_scale: Optional[torch.Tensor] = None):
+    """Copy token rows into the expert-sorted padded layout.
+
+    Returns ``(dst[capacity, cols], dst_scale)`` where ``dst_scale`` is ``None``,
+    ``[capacity]`` (one scale per row) or ``[groups, capacity]`` (group-major)."""
+    lib = _cabi.load()
+    m, cols = src.shape
+    row_bytes = cols * src.element_size()
+    dst = torch.empty((capacity, cols), dtype=src.dtype, device=src.device)
+    dst_scale = None
+    groups = 0
+    ld = 0
+    if src_scale is not None:
+        src_scale = src_scale.reshape(m, -1).contiguous()
+        groups = src_scale.shape[1]
+        if groups == 1:
+            dst_scale = torch.empty(capacity, dtype=torch.float32, device=src.device)
+            ld = capacity
+        else:
+            dst_scale = torch.empty((groups, capacity), dtype=torch.float32, device=src.device)
+            ld = capacity
+    with torch.cuda.device(src.device):
+        check(lib.bolt_gather_rows(ptr(src), m, row_bytes, ptr(src_scale), groups,
+                                   ptr(sorted_ids), ptr(num_valid), capacity, ptr(dst),
+                                   ptr(dst_scale), ld, stream_of(src)))
+    return dst, dst_scale
+
+
+def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
+            routed_scaling_factor: float = 1.0,
+            router_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``output[m] = cast(scale * sum_k f32(input[m, k]) [* router_weights[m, k]])``."""
+    _require_cuda(input_tensor, output_tensor)
+    m, topk, n = input_tensor.shape
+    assert output_tensor.dtype in (torch.float16, torch.bfloat16, torch.float32)
+    assert input_tensor.is_contiguous()
+    assert output_tensor.is_contiguous()
+    assert input_tensor.shape[0] == output_tensor.shape[0]
+    assert input_tensor.shape[2] == output_tensor.shape[1]
+    if router_weights is not None:
+        router_weights = router_weights.to(torch.float32).contiguous()
+    lib = _cabi.load()
+    with torch.cuda.device(input_tensor.device):
+        check(lib.bolt_moe_sum(ptr(input_tensor), dtype_code(input_tensor.dtype),
+                               ptr(output_tensor), dtype_code(output_tensor.dtype), m, topk, n,
+                               float(routed_scaling_factor), ptr(router_weights),
+                               stream_of(input_tensor)))
+    return output_tensor
+
+
+# ---------------------------------------------------------------------------
+# grouped GEMM
+# ---------------------------------------------------------------------------
+_status_words = {}
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that the grouped GEMM sets when a bounded device-side
+    wait expired (0 = healthy).  Reading it synchronises; kernels never do."""
+    key = torch.device(device).index or 0
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_device_status(device: torch.device) -> None:
+    code = int(device_status(device).item())
+    if code != 0:
+        device_status(device).zero_()
+        raise _cabi.BoltError(f"grouped GEMM reported an expired device-side wait (code {code})")
+
+
+def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+                 sorted_expert_ids: torch.Tensor, num_valid: torch.Tensor,
+                 a_scale: Optional[torch.Tensor] = None, a_scale_ld: int = 0,
+                 b_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                 c_scale: Optional[torch.Tensor] = None, c_scale_ld: int = 0,
+                 mid_dtype: Optional[torch.dtype] = None, scatter: bool = False,
+                 num_tokens: int = 0, topk: int = 1, mul_routed_weight: bool = False,
+                 sorted_ids: Optional[torch.Tensor] = None,
+                 sorted_weights: Optional[torch.Tensor] = None, sm_count: int = 0) -> None:
+    """One grouped expert GEMM launch (see ``bolt_grouped_gemm``)."""
+    lib = _cabi.load()
+    args = _cabi.GemmArgs()
+    args.kind = kind
+    args.epilogue = epilogue
+    args.capacity = a.shape[0]
+    args.n = b.shape[1]
+    args.k = b.shape[2]
+    args.num_experts = b.shape[0]
+    args.a = ptr(a)
+    args.b = ptr(b)
+    args.a_scale = ptr(a_scale)
+    args.a_scale_ld = a_scale_ld
+    args.b_scale = ptr(b_scale)
+    args.bias = ptr(bias)
+    args.bias_dtype = dtype_code(bias.dtype) if bias is not None else _cabi.F32
+    args.c = ptr(c)
+    args.c_dtype = dtype_code(c.dtype)
+    args.mid_dtype = dtype_code(mid_dtype) if mid_dtype is not None else _cabi.F32
+    args.c_ld = c.stride(-2) if c.dim() >= 2 else c.shape[-1]
+    args.c_scale = ptr(c_scale)
+    args.c_scale_ld = c_scale_ld
+    args.scatter = int(scatter)
+    args.num_tokens = num_tokens
+    args.topk = topk
+    args.mul_routed_weight = int(mul_routed_weight)
+    args.sorted_ids = ptr(sorted_ids)
+    args.sorted_weights = ptr(sorted_weights)
+    args.sorted_expert_ids = ptr(sorted_expert_ids)
+    args.num_valid_ids = ptr(num_valid)
+    args.status = ptr(device_status(a.device))
+    args.sm_count = sm_count
+    with torch.cuda.device(a.device):
+        check(lib.bolt_grouped_gemm(C.byref(args), stream_of(a)))

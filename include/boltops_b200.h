@@ -1,0 +1,220 @@
+/*
+ * boltops_b200 -- C ABI of the B200 (sm_100a) fused-MoE hot path.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*), launches asynchronously on that stream, never
+ * synchronises the host, and returns a bolt_status.  No torch types appear in
+ * any signature.  Unless stated otherwise an entry point allocates nothing: the
+ * caller owns inputs, outputs and workspaces.
+ *
+ * The reference project exposes this path through Python only; the closest
+ * native interface it has is the pybind entry moe_sorting_fwd
+ * (boltops/fused_moe/triton/moe_sorting_hipc/csrc/moe_sorting_binding.cu:73-88).
+ * Each declaration below names the reference function it replaces
+ * (paths relative to the reference project root).
+ */
+#ifndef BOLTOPS_B200_H_
+#define BOLTOPS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BOLT_ABI_VERSION 1
+
+enum bolt_status {
+  BOLT_OK = 0,
+  BOLT_ERR_INVALID = 1,      /* argument contract violated                      */
+  BOLT_ERR_CUDA = 2,         /* a CUDA runtime/driver call failed               */
+  BOLT_ERR_UNSUPPORTED = 3,  /* valid request, not built for this variant       */
+  BOLT_ERR_DEVICE = 4        /* a kernel reported a bounded-wait expiry         */
+};
+
+enum bolt_dtype {
+  BOLT_BF16 = 0,
+  BOLT_F16 = 1,
+  BOLT_F32 = 2,
+  BOLT_FP8_E4M3 = 3,
+  BOLT_INT8 = 4
+};
+
+/* activation kinds of bolt_moe_activation (names follow the reference registry,
+ * boltops/fused_moe/triton/moe_activation.py:1065-1116) */
+enum bolt_activation {
+  BOLT_ACT_SILU = 0,
+  BOLT_ACT_GELU = 1,
+  BOLT_ACT_GELU_TANH = 2,
+  BOLT_ACT_RELU2 = 3,
+  BOLT_ACT_SWIGLU_OAI = 4,   /* gate'*sigmoid(alpha*gate')*(up'+1), chunked layout */
+  BOLT_ACT_SWIGLU_STEP = 5,  /* min(silu(gate),limit)*clamp(up,+-limit)            */
+  BOLT_ACT_SILU_CLAMP = 6    /* silu(min(gate,limit))*clamp(up,+-limit)            */
+};
+
+/* grouped-GEMM operand kinds */
+enum bolt_gemm_kind {
+  BOLT_GEMM_BF16 = 0,         /* bf16 x bf16 -> fp32                                    */
+  BOLT_GEMM_F16 = 1,          /* fp16 x fp16 -> fp32                                    */
+  BOLT_GEMM_FP8_BLOCK = 2,    /* e4m3, [128,128] weight blocks, 1x128 activation groups */
+  BOLT_GEMM_INT8_CHANNEL = 3, /* int8, per-row activation / per-output-channel weight   */
+  BOLT_GEMM_FP8_CHANNEL = 4,  /* e4m3, per-row activation / per-output-channel weight   */
+  BOLT_GEMM_INT8_BLOCK = 5    /* int8, [128,128] weight blocks, 1x128 activation groups */
+};
+
+enum bolt_gemm_epilogue {
+  BOLT_EPI_STORE = 0,        /* C = dequant(A.B^T)                                      */
+  BOLT_EPI_SILU_MUL = 1,     /* C = silu(gate)*up, B rows [0,N/2) gate, [N/2,N) up       */
+  BOLT_EPI_SILU_MUL_QUANT = 2/* as above, then 1x128-group quantisation to e4m3/int8    */
+};
+
+/* Message of the last non-OK status returned on the calling thread. */
+const char* bolt_last_error(void);
+int bolt_abi_version(void);
+
+/* ---------------------------------------------------------------------------
+ * Token-to-expert sort, CK format.
+ * Replaces moe_sorting_fwd (moe_sorting_hipc/csrc/moe_sorting_binding.cu:15-71,
+ * moe_sorting_api.cu:118-180) as driven by moe_sorting_ck
+ * (boltops/fused_moe/triton/fused_moe.py:441-485).
+ *   sorted_ids[i]   = token | slot << 24, ascending route order inside an expert,
+ *                     every expert padded to unit_size with id num_tokens|topk<<24
+ *                     and weight 0; experts without routes get no block; with a
+ *                     mask, masked experts get no block and expert ids are the
+ *                     count of enabled experts before them.
+ *   capacity        = num_tokens*topk + num_experts*unit_size - topk entries
+ *   sorted_expert_ids: ceil(capacity/unit_size) entries
+ *   tokens_positions_per_expert: [0,E) route counts, [E,2E) padded start offsets
+ *                     (-1 for masked experts)
+ *   num_valid_ids[0] = padded total
+ *   moe_buf (optional, may be NULL): zero-filled, moe_buf_bytes long.
+ *   workspace: bolt_moe_sort_workspace_bytes() bytes, 16-byte aligned; contents
+ *   are scratch and need no initialisation.
+ */
+size_t bolt_moe_sort_workspace_bytes(int num_tokens, int topk, int num_experts);
+int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weights,
+                     const int32_t* local_expert_mask, int num_tokens, int topk,
+                     int num_experts, int unit_size, int32_t* sorted_ids,
+                     float* sorted_weights, int32_t* sorted_expert_ids,
+                     int32_t* tokens_positions_per_expert, int32_t* num_valid_ids,
+                     void* moe_buf, size_t moe_buf_bytes, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/* Token-to-expert sort, vLLM format.
+ * Replaces moe_align_block_size (boltops/fused_moe/triton/fused_moe.py:330-439,
+ * stages :194-327): sorted_ids = flat route index, whole capacity
+ * numel + E*(block_size-1) pre-filled with numel; expert_ids zero-filled over
+ * ceil(capacity/block_size) entries, then mapped through expert_map if given.
+ */
+int bolt_moe_align_block_size(const int32_t* topk_ids, int numel, int num_experts,
+                              int block_size, const int32_t* expert_map,
+                              int32_t* sorted_ids, int32_t* expert_ids,
+                              int32_t* num_tokens_post_pad, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Dynamic activation quantisation.
+ * Replaces per_token_quant_triton / dynamic_per_token_quant_fp8_i8
+ * (boltops/fused_moe/triton/moe_compat.py:55-106, quant.py:145-368) and, with
+ * power2 != 0, dynamic_per_group_quant_fp8_power2 (quant.py:636-661).
+ *   x [rows, cols] (bf16/f16/f32, contiguous); group = cols (per token) or a
+ *   divisor of cols (1 x group); q [rows, cols] e4m3 or int8; scales fp32
+ *   [rows, cols/group].
+ */
+int bolt_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int group,
+                    int q_dtype, int power2, void* q, float* scales, void* stream);
+
+/* Row gather into the expert-sorted padded layout used by the grouped GEMMs.
+ *   dst[i, :] = src[sorted_ids[i] & 0xFFFFFF, :] for i < num_valid_ids[0]
+ *   (zero rows for pad ids); row_bytes must be a multiple of 16.
+ *   If src_scale != NULL, scales are gathered too:
+ *     groups > 1 : dst_scale[g * dst_scale_ld + i] = src_scale[token*groups + g]
+ *     groups == 1: dst_scale[i] = src_scale[token]
+ * No counterpart in the reference (its GEMM gathers rows through pointer
+ * arithmetic, boltops/fused_moe/triton/moe_op.py:1479,1611-1615).
+ */
+int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
+                     const float* src_scale, int groups, const int32_t* sorted_ids,
+                     const int32_t* num_valid_ids, int capacity, void* dst,
+                     float* dst_scale, int64_t dst_scale_ld, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Activations.  Replaces _apply_activation / moe_activation
+ * (boltops/fused_moe/triton/moe_activation.py:1382-1525; kernels :70-128 etc.).
+ * gated: in [rows, 2*n_out] = [gate | up], out [rows, n_out]; else in [rows, n_out].
+ * fp32 math, result stored in `dtype`.  alpha/limit as gemm1_alpha/gemm1_limit.
+ * rows_dev (optional): device int32 row count that further bounds `rows`.
+ */
+int bolt_moe_activation(const void* in, void* out, int dtype, int64_t rows, int n_out,
+                        int activation, int gated, float alpha, float limit,
+                        const int32_t* rows_dev, void* stream);
+
+/* Fused activation + per-token quantisation.  Replaces triton_activation_quant
+ * (boltops/fused_moe/triton/moe_activation.py:290-421,1239-1332): activation,
+ * rounding to `dtype`, per-row absmax quantisation, optional scale *= row
+ * multiplier (router-weight folding).
+ */
+int bolt_act_quant(const void* in, int dtype, int64_t rows, int n_out, int activation,
+                   int gated, int q_dtype, const float* row_multiplier, void* q,
+                   float* scales, const int32_t* rows_dev, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Top-k combine.  Replaces triton_moe_sum / moe_sum_kernel
+ * (boltops/fused_moe/triton/fused_moe.py:72-188):
+ *   out[m, :] = cast(scale * sum_k f32(in[m, k, :]) [* weights[m, k]]).
+ */
+int bolt_moe_sum(const void* in, int in_dtype, void* out, int out_dtype, int64_t num_tokens,
+                 int topk, int n, float scale, const float* weights, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Grouped expert GEMM (tcgen05 / TMEM / TMA, persistent).
+ * Replaces moe_op.fused_moe + fused_moe_kernel
+ * (boltops/fused_moe/triton/moe_op.py:2846-3417, 1294-1914) for the bf16/f16,
+ * fp8/int8 block-scaled and fp8/int8 per-channel variants.
+ *
+ * A rows are in the expert-sorted padded layout produced by bolt_moe_sort_ck with
+ * unit_size 128 (+ bolt_gather_rows for GEMM1): row tile t belongs to expert
+ * sorted_expert_ids[t]; only tiles below num_valid_ids[0] are computed.
+ */
+typedef struct bolt_gemm_args {
+  int kind;                 /* enum bolt_gemm_kind                               */
+  int epilogue;             /* enum bolt_gemm_epilogue                           */
+  int capacity;             /* rows of A (multiple of 128)                       */
+  int n;                    /* rows of B per expert                              */
+  int k;                    /* reduction length                                  */
+  int num_experts;          /* experts in B                                      */
+  const void* a;            /* [capacity, k] row-major                           */
+  const void* b;            /* [num_experts, n, k] row-major                     */
+  const float* a_scale;     /* block: [k/128, a_scale_ld]; channel: [capacity]   */
+  int64_t a_scale_ld;
+  const float* b_scale;     /* block: [E, n/128, k/128]; channel: [E, n]         */
+  const void* bias;         /* optional [E, n] in c_dtype-compatible float type  */
+  int bias_dtype;
+  void* c;                  /* output                                            */
+  int c_dtype;              /* BOLT_BF16/F16/F32, or FP8/INT8 for SILU_MUL_QUANT */
+  int mid_dtype;            /* gated epilogues: dtype the GEMM result and the
+                               activation are rounded through (the reference's
+                               intermediate cache dtype); BOLT_F32 = no rounding */
+  int64_t c_ld;             /* elements between output rows                      */
+  float* c_scale;           /* SILU_MUL_QUANT: [n/2/128, c_scale_ld]             */
+  int64_t c_scale_ld;
+  int scatter;              /* 0: row i -> c[i]; 1: row i -> c[token*topk+slot]  */
+  int num_tokens;           /* for pad detection: token >= num_tokens is a pad   */
+  int topk;
+  int mul_routed_weight;    /* multiply by sorted_weights[i] before the cast     */
+  const int32_t* sorted_ids;
+  const float* sorted_weights;
+  const int32_t* sorted_expert_ids;
+  const int32_t* num_valid_ids;
+  int32_t* status;          /* optional device int32: set non-zero if a bounded
+                               device-side wait expired                          */
+  int sm_count;             /* 0 = all SMs of the current device                 */
+} bolt_gemm_args;
+
+int bolt_grouped_gemm(const bolt_gemm_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BOLTOPS_B200_H_ */

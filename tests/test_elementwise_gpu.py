@@ -1,0 +1,142 @@
+"""Quantisers, activations and the combine vs the CPU oracle."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.helpers import bf16, load_npz, t
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def _bits(x):
+    return x.view(torch.uint8) if x.dtype == FP8 else x
+
+
+@pytest.mark.parametrize("shape,group", [((2, 128), None), ((257, 128), None), ((1281, 1232), None),
+                                         ((64, 7168), 128), ((33, 2048), 128), ((5, 4096), None),
+                                         ((3, 20000), None), ((7, 100), None), ((16, 512), 64)])
+@pytest.mark.parametrize("qdtype", [FP8, torch.int8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_quant_rows_bit_exact(shape, group, qdtype, dtype):
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(20)
+    x = (torch.randn(shape) * 3).to(dtype)
+    x[0] = 0
+    x[shape[0] // 2, : shape[1] // 2] = 0
+    q_ref, s_ref = O.quant_rows_kernel(x, qdtype, group)
+    q, s = ops.quant_rows(x.cuda(), qdtype, group)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(_bits(q.cpu()), _bits(q_ref))
+
+
+def test_quant_known_answers():
+    from boltops_b200.fused_moe import ops
+    v = torch.zeros(256, 128, dtype=torch.float16)
+    v[:, :6] = torch.tensor([0.5, -0.5, 1.5, -1.5, 126.5, 127.0], dtype=torch.float16)
+    q, s = ops.per_token_quant(v.cuda(), quant_dtype=torch.int8)
+    assert torch.equal(s.cpu(), torch.ones(256, 1))
+    assert q.cpu()[0, :6].tolist() == [0, 0, 2, -2, 126, 127]
+    v = torch.tensor([[0.5, 1.5, 2.5, 448.0]], dtype=torch.float16)
+    q, s = ops.per_token_quant(v.cuda(), quant_dtype=FP8)
+    assert torch.equal(s.cpu(), torch.ones(1, 1))
+    assert torch.equal(q.cpu().float(), v.float())
+    z = torch.zeros(4, 256, dtype=torch.bfloat16)
+    for qd, dmax in ((FP8, 448.0), (torch.int8, 127.0)):
+        q, s = ops.per_token_quant(z.cuda(), quant_dtype=qd)
+        assert torch.equal(s.cpu(), torch.full((4, 1), 1.0e-10, dtype=torch.float32) / dmax)
+        assert (q.cpu().float() == 0).all()
+
+
+@pytest.mark.parametrize("width", [32, 128, 256])
+def test_quant_power2(width):
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(225)
+    x = torch.randn(19, width)
+    x[0].zero_()
+    bounds = torch.tensor([448 * 2.0 ** e for e in range(-9, 8)])
+    x[1:18] *= 0.01
+    x[1:18, 0] = bounds
+    x[18, 0] = torch.nextafter(bounds[8], torch.tensor(float("inf")))
+    q_ref, s_ref = O.group_quant_fp8_power2(x)
+    q, s = ops.quant_rows(x.cuda(), FP8, None, scale_ue8m0=True)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(_bits(q.cpu()), _bits(q_ref))
+
+
+@pytest.mark.parametrize("name,gated,kw", [
+    ("silu", True, {}), ("gelu", True, {}), ("gelu_tanh", True, {}), ("swiglustep", True, {}),
+    ("silu", False, {}), ("gelu", False, {}), ("gelu_tanh", False, {}), ("relu2", False, {}),
+    ("silu", True, {"gemm1_limit": 4.0}),
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,n", [(9, 48), (64, 3072), (3, 1000), (1, 6)])
+def test_moe_activation(name, gated, kw, dtype, rows, n):
+    from boltops_b200.fused_moe import moe_activation
+    torch.manual_seed(13)
+    x = torch.randn(rows, n).to(dtype)
+    n_out = n // 2 if gated else n
+    out = torch.empty(rows, n_out, dtype=dtype, device="cuda")
+    moe_activation(out, x.cuda(), name, gated, **kw)
+    ref = O.activation_ref(x, name, gated, limit=kw.get("gemm1_limit")).to(dtype)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    if name == "silu" and gated and not kw:
+        # same formula, same rounding: at most 1 ulp of the storage type apart
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2 ** -7, atol=1e-6)
+
+
+def test_moe_activation_fixture_and_errors():
+    from boltops_b200.fused_moe import moe_activation
+    z = load_npz("activations.npz")
+    x = bf16(z["x"])
+    out = torch.empty(9, 24, dtype=torch.bfloat16, device="cuda")
+    moe_activation(activated_out=out, ffn1_out_2d=x.cuda(), activation="silu")
+    torch.testing.assert_close(out.cpu().float(), t(z["silu_1"]).bfloat16().float(),
+                               rtol=2 ** -7, atol=1e-6)
+    with pytest.raises(ValueError):
+        moe_activation(out, x.cuda(), "nope")
+    with pytest.raises(ValueError):
+        moe_activation(out[:, :5], x.cuda(), "silu")
+    with pytest.raises(ValueError):
+        moe_activation(out, x, "silu")
+    with pytest.raises(TypeError):
+        moe_activation(out.to(torch.int32), x.cuda().to(torch.int32), "silu")
+
+
+@pytest.mark.parametrize("qdtype", [FP8, torch.int8])
+def test_activation_quant_matches_unfused(qdtype):
+    from boltops_b200.fused_moe import ops
+    from boltops_b200.fused_moe.activation import activation_quant, apply_activation
+    torch.manual_seed(3)
+    x = torch.randn(37, 1536, dtype=torch.bfloat16, device="cuda")
+    act = torch.empty(37, 768, dtype=torch.bfloat16, device="cuda")
+    apply_activation("silu", True, act, x)
+    q_ref, s_ref = ops.per_token_quant(act, quant_dtype=qdtype)
+    q, s = activation_quant(x, "silu", True, qdtype)
+    assert torch.equal(s, s_ref) and torch.equal(_bits(q), _bits(q_ref))
+    mult = torch.rand(37, device="cuda")
+    q2, s2 = activation_quant(x, "silu", True, qdtype, row_multiplier=mult)
+    assert torch.equal(_bits(q2), _bits(q)) and torch.equal(s2, s * mult[:, None])
+
+
+@pytest.mark.parametrize("width", [128, 137, 7168])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_moe_sum(width, weighted):
+    from boltops_b200.fused_moe import ops
+    x = (torch.arange(3 * 2 * width).reshape(3, 2, width).float() / 256).bfloat16()
+    w = torch.tensor([[0.2, 0.8], [0.7, 0.3], [0.4, 0.6]]) if weighted else None
+    out = torch.empty(3, width, dtype=torch.bfloat16, device="cuda")
+    ops.moe_sum(x.cuda(), out, 1.25, None if w is None else w.cuda())
+    assert torch.equal(out.cpu(), O.moe_sum(x, 1.25, weights=w))
+
+
+def test_moe_sum_topk8_random():
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(0)
+    x = torch.randn(100, 8, 2048).bfloat16()
+    out = torch.empty(100, 2048, dtype=torch.bfloat16, device="cuda")
+    ops.moe_sum(x.cuda(), out, 2.5)
+    assert torch.equal(out.cpu(), O.moe_sum(x, 2.5))
+    out32 = torch.empty(100, 2048, dtype=torch.float32, device="cuda")
+    ops.moe_sum(x.cuda(), out32, 1.0)
+    assert torch.equal(out32.cpu(), O.moe_sum(x, 1.0, out_dtype=torch.float32))

@@ -1,0 +1,188 @@
+"""Grouped GEMM (tcgen05) vs fp32 CPU references, called through the C ABI."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def _routing(m, e, topk, seed):
+    w, ids = O.make_routing(m, e, topk, seed)
+    return w, ids
+
+
+def _sorted_problem(m, e, topk, seed):
+    """Sort on the GPU, return device handles + host copies of the layout."""
+    from boltops_b200.fused_moe import ops
+    w, ids = _routing(m, e, topk, seed)
+    s_ids, s_w, s_e, nv, _, _ = ops.moe_sorting_ck(ids.cuda(), w.cuda(), e, None, None, 128, None)
+    torch.cuda.synchronize()
+    return dict(w=w, ids=ids, s_ids=s_ids, s_w=s_w, s_e=s_e, nv=nv, cap=s_ids.shape[0],
+                nvi=int(nv.item()), h_ids=s_ids.cpu(), h_w=s_w.cpu(), h_e=s_e.cpu())
+
+
+def _reference_rows(pr, a_tokens_f32, b_f32):
+    """fp32 C[row] = A[token(row)] @ B[expert(row)]^T for all valid, non-pad rows."""
+    m = a_tokens_f32.shape[0]
+    out = {}
+    for row in range(pr["nvi"]):
+        tok = int(pr["h_ids"][row]) & 0xFFFFFF
+        if tok >= m:
+            continue
+        e = int(pr["h_e"][row // 128])
+        out[row] = (a_tokens_f32[tok] @ b_f32[e].t(), tok, (int(pr["h_ids"][row]) >> 24) & 0xFF)
+    return out
+
+
+@pytest.mark.parametrize("m,e,topk,n,k,dtype", [
+    (64, 8, 2, 512, 256, torch.bfloat16),
+    (200, 4, 2, 384, 336, torch.bfloat16),      # n tail (384 = 256 + 128), k tail (336 % 64 != 0)
+    (33, 16, 4, 256, 1024, torch.float16),
+    (700, 8, 2, 1024, 512, torch.bfloat16),     # several row tiles per expert
+])
+def test_gemm_16bit_store_sorted(m, e, topk, n, k, dtype):
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(m + n)
+    pr = _sorted_problem(m, e, topk, 11)
+    x = (torch.randn(m, k) / 4).to(dtype)
+    b = (torch.randn(e, n, k) / 8).to(dtype)
+    a_sorted, _ = ops.gather_rows(x.cuda(), pr["s_ids"], pr["nv"], pr["cap"])
+    c = torch.full((pr["cap"], n), -123.0, dtype=dtype, device="cuda")
+    kind = _cabi.GEMM_BF16 if dtype == torch.bfloat16 else _cabi.GEMM_F16
+    ops.grouped_gemm(kind=kind, epilogue=_cabi.EPI_STORE, a=a_sorted, b=b.cuda(), c=c,
+                     sorted_expert_ids=pr["s_e"], num_valid=pr["nv"], sorted_ids=pr["s_ids"],
+                     sorted_weights=pr["s_w"], num_tokens=m, topk=topk)
+    torch.cuda.synchronize()
+    ops.check_device_status(c.device)
+    got = c.cpu().float()
+    ref = _reference_rows(pr, x.float(), b.float())
+    assert ref
+    for row, (val, _, _) in ref.items():
+        torch.testing.assert_close(got[row], val.to(dtype).float(), rtol=2e-2, atol=2e-2)
+    # pad rows and rows beyond num_valid keep the sentinel
+    live = torch.zeros(pr["cap"], dtype=torch.bool)
+    live[list(ref)] = True
+    assert (got[~live] == -123.0).all()
+
+
+def test_gemm_bf16_scatter_weighted_and_fused_silu():
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(2)
+    m, e, topk, inter, k = 96, 8, 2, 256, 512
+    pr = _sorted_problem(m, e, topk, 3)
+    x = (torch.randn(m, k) / 4).bfloat16()
+    w1 = (torch.randn(e, 2 * inter, k) / 8).bfloat16()
+    a_sorted, _ = ops.gather_rows(x.cuda(), pr["s_ids"], pr["nv"], pr["cap"])
+    common = dict(kind=_cabi.GEMM_BF16, sorted_expert_ids=pr["s_e"], num_valid=pr["nv"],
+                  sorted_ids=pr["s_ids"], sorted_weights=pr["s_w"], num_tokens=m, topk=topk)
+    # fused SiLU-and-mul epilogue, sorted output
+    act = torch.full((pr["cap"], inter), -123.0, dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL, a=a_sorted, b=w1.cuda(), c=act,
+                     mid_dtype=torch.bfloat16, **common)
+    # plain store, scattered to route rows, router weight applied
+    c3 = torch.full((m * topk, 2 * inter), -123.0, dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1.cuda(), c=c3, scatter=True,
+                     mul_routed_weight=True, **common)
+    torch.cuda.synchronize()
+    ops.check_device_status(act.device)
+    ref = _reference_rows(pr, x.float(), w1.float())
+    got_act, got_c3 = act.cpu().float(), c3.cpu().float()
+    for row, (val, tok, slot) in ref.items():
+        c1 = val.bfloat16()
+        expect = O.silu_and_mul(c1[None])[0].float()
+        torch.testing.assert_close(got_act[row], expect, rtol=3e-2, atol=2e-2)
+        wgt = float(pr["h_w"][row])
+        torch.testing.assert_close(got_c3[tok * topk + slot], (val * wgt).bfloat16().float(),
+                                   rtol=2e-2, atol=2e-2)
+    assert (got_c3 != -123.0).all()   # every route row written exactly once
+
+
+@pytest.mark.parametrize("qdtype", [FP8, torch.int8])
+def test_gemm_block_scaled(qdtype):
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(4)
+    m, e, topk, inter, k = 80, 8, 2, 256, 512
+    pr = _sorted_problem(m, e, topk, 5)
+    x = (torch.randn(m, k) / 2).bfloat16()
+    if qdtype == FP8:
+        w1 = (torch.randn(e, 2 * inter, k) * 40).clamp(-448, 448).to(FP8)
+        kind = _cabi.GEMM_FP8_BLOCK
+    else:
+        w1 = torch.randint(-127, 128, (e, 2 * inter, k), dtype=torch.int8)
+        kind = _cabi.GEMM_INT8_BLOCK
+    w1_s = torch.rand(e, 2 * inter // 128, k // 128) * 1e-2
+    x_q, x_s = ops.per_block_quant(x.cuda(), 128, qdtype)
+    a_sorted, a_scale = ops.gather_rows(x_q, pr["s_ids"], pr["nv"], pr["cap"], x_s)
+    common = dict(kind=kind, sorted_expert_ids=pr["s_e"], num_valid=pr["nv"], a=a_sorted,
+                  b=w1.cuda(), a_scale=a_scale, a_scale_ld=pr["cap"], b_scale=w1_s.cuda(),
+                  sorted_ids=pr["s_ids"], sorted_weights=pr["s_w"], num_tokens=m, topk=topk)
+    c1 = torch.full((pr["cap"], 2 * inter), -123.0, dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm(epilogue=_cabi.EPI_STORE, c=c1, **common)
+    act = torch.full((pr["cap"], inter), -123.0, dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL, c=act, mid_dtype=torch.bfloat16, **common)
+    act_q = torch.zeros((pr["cap"], inter), dtype=qdtype, device="cuda")
+    act_s = torch.zeros((inter // 128, pr["cap"]), dtype=torch.float32, device="cuda")
+    ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, c=act_q, c_scale=act_s,
+                     c_scale_ld=pr["cap"], mid_dtype=torch.bfloat16, **common)
+    torch.cuda.synchronize()
+    ops.check_device_status(c1.device)
+    xq_h, xs_h = x_q.cpu(), x_s.cpu()
+    got_c1, got_act = c1.cpu(), act.cpu()
+    got_q, got_s = act_q.cpu(), act_s.cpu()
+    for row in range(pr["nvi"]):
+        tok = int(pr["h_ids"][row]) & 0xFFFFFF
+        if tok >= m:
+            continue
+        ex = int(pr["h_e"][row // 128])
+        ref = O.block_scaled_matmul(xq_h[tok:tok + 1], w1[ex], xs_h[tok:tok + 1], w1_s[ex],
+                                    (128, 128), torch.bfloat16)
+        torch.testing.assert_close(got_c1[row:row + 1].float(), ref.float(), rtol=2e-2, atol=2e-2)
+        ref_act = O.silu_and_mul(got_c1[row:row + 1])          # from the kernel's own C1 rounding
+        torch.testing.assert_close(got_act[row:row + 1].float(), ref_act.float(),
+                                   rtol=2 ** -6, atol=1e-3)
+        q_ref, s_ref = O.quant_rows_kernel(got_act[row:row + 1], qdtype, 128)
+        assert torch.equal(got_s[:, row], s_ref[0])
+        assert torch.equal(got_q[row].view(torch.uint8), q_ref[0].view(torch.uint8))
+
+
+@pytest.mark.parametrize("qdtype", [torch.int8, FP8])
+def test_gemm_per_channel(qdtype):
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(6)
+    m, e, topk, n, k = 70, 8, 2, 512, 384
+    pr = _sorted_problem(m, e, topk, 7)
+    x = (torch.randn(m, k) / 2).bfloat16()
+    if qdtype == torch.int8:
+        w = torch.randint(-127, 128, (e, n, k), dtype=torch.int8)
+        kind = _cabi.GEMM_INT8_CHANNEL
+    else:
+        w = (torch.randn(e, n, k) * 40).clamp(-448, 448).to(FP8)
+        kind = _cabi.GEMM_FP8_CHANNEL
+    w_s = torch.rand(e, n) * 1e-2
+    x_q, x_s = ops.per_token_quant(x.cuda(), quant_dtype=qdtype)
+    a_sorted, a_scale = ops.gather_rows(x_q, pr["s_ids"], pr["nv"], pr["cap"], x_s)
+    c = torch.full((pr["cap"], n), -123.0, dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm(kind=kind, epilogue=_cabi.EPI_STORE, a=a_sorted, b=w.cuda(), c=c,
+                     a_scale=a_scale, b_scale=w_s.cuda(), sorted_expert_ids=pr["s_e"],
+                     num_valid=pr["nv"], sorted_ids=pr["s_ids"], sorted_weights=pr["s_w"],
+                     num_tokens=m, topk=topk)
+    torch.cuda.synchronize()
+    ops.check_device_status(c.device)
+    got = c.cpu()
+    xq_h, xs_h = x_q.cpu(), x_s.cpu()
+    for row in range(pr["nvi"]):
+        tok = int(pr["h_ids"][row]) & 0xFFFFFF
+        if tok >= m:
+            continue
+        ex = int(pr["h_e"][row // 128])
+        ref = O.per_token_matmul(xq_h[tok:tok + 1], w[ex], xs_h[tok:tok + 1], w_s[ex], torch.bfloat16)
+        if qdtype == torch.int8:
+            torch.testing.assert_close(got[row:row + 1].float(), ref.float(), rtol=2 ** -7, atol=1e-6)
+        else:
+            torch.testing.assert_close(got[row:row + 1].float(), ref.float(), rtol=2e-2, atol=2e-2)

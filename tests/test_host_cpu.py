@@ -1,0 +1,134 @@
+"""CPU-only checks: the C-ABI library loads and exports every declared symbol,
+the ctypes struct matches the C header, host-side argument logic, and oracle
+self-consistency.  No compute entry point is called here."""
+import ctypes
+import re
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from boltops_b200 import build, _cabi
+    build.build()
+    return _cabi.load()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from boltops_b200 import _cabi
+    header = (ROOT / "include" / "boltops_b200.h").read_text()
+    declared = set(re.findall(r"\b(bolt_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert declared == set(_cabi.EXPORTS)
+    assert lib.bolt_abi_version() == 1
+
+
+def test_gemm_args_struct_matches_header(tmp_path):
+    from boltops_b200 import _cabi
+    fields = [f[0] for f in _cabi.GemmArgs._fields_]
+    prog = ['#include <stdio.h>', '#include <stddef.h>',
+            f'#include "{ROOT / "include" / "boltops_b200.h"}"', "int main(void){",
+            'printf("%zu\\n", sizeof(bolt_gemm_args));']
+    prog += [f'printf("%zu\\n", offsetof(bolt_gemm_args, {f}));' for f in fields]
+    prog += ["return 0;}"]
+    src = tmp_path / "abi.c"
+    src.write_text("\n".join(prog))
+    exe = tmp_path / "abi"
+    subprocess.run(["gcc", str(src), "-o", str(exe)], check=True)
+    nums = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True,
+                                           check=True).stdout.split()]
+    assert nums[0] == ctypes.sizeof(_cabi.GemmArgs)
+    for f, off in zip(fields, nums[1:]):
+        assert getattr(_cabi.GemmArgs, f).offset == off, f
+
+
+def test_workspace_query_is_host_only(lib):
+    assert lib.bolt_moe_sort_workspace_bytes(64, 2, 8) == 16          # single-CTA path
+    big = lib.bolt_moe_sort_workspace_bytes(16384, 8, 128)
+    assert big > 128 * 4 and big < (1 << 22)
+
+
+def test_activation_registry():
+    from boltops_b200.fused_moe import (moe_activation_output_size, normalize_moe_activation)
+    assert normalize_moe_activation("SiLU") == ("silu", True)
+    assert normalize_moe_activation("gelu_pytorch_tanh", False) == ("gelu_tanh", False)
+    assert normalize_moe_activation("relu2") == ("relu2", False)
+    with pytest.raises(ValueError, match="Unsupported activation"):
+        normalize_moe_activation("tanh")
+    with pytest.raises(ValueError, match="non-gated"):
+        normalize_moe_activation("relu2", True)
+    with pytest.raises(ValueError, match="requires gated"):
+        normalize_moe_activation("swigluoai", False)
+    assert moe_activation_output_size(10, True) == 5
+    assert moe_activation_output_size(10, False) == 10
+    with pytest.raises(ValueError):
+        moe_activation_output_size(0, False)
+    with pytest.raises(ValueError):
+        moe_activation_output_size(7, True)
+
+
+def test_public_signatures_match_reference_order():
+    import inspect
+    from boltops_b200.fused_moe import fused_experts, moe_activation
+    names = list(inspect.signature(fused_experts).parameters)
+    assert names[:10] == ["hidden_states", "w1", "w2", "topk_weights", "topk_ids", "inplace",
+                          "activation", "b1", "b2", "is_gated"]
+    assert names[-1] == "gemm1_beta" and len(names) == 37
+    sig = inspect.signature(moe_activation)
+    assert list(sig.parameters)[:4] == ["activated_out", "ffn1_out_2d", "activation", "is_gated"]
+    assert sig.parameters["gemm1_alpha"].kind is inspect.Parameter.KEYWORD_ONLY
+
+
+def test_no_cpu_fallback():
+    from boltops_b200.fused_moe import fused_experts, moe_activation
+    hid = torch.zeros(2, 128, dtype=torch.bfloat16)
+    w1 = torch.zeros(2, 256, 128, dtype=torch.bfloat16)
+    w2 = torch.zeros(2, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        fused_experts(hid, w1, w2, torch.ones(2, 1), torch.zeros(2, 1, dtype=torch.int32))
+    with pytest.raises(ValueError, match="CUDA"):
+        moe_activation(torch.zeros(2, 64), torch.zeros(2, 128), "silu")
+
+
+def test_product_does_not_import_oracle():
+    for path in (ROOT / "boltops_b200").rglob("*.py"):
+        text = path.read_text()
+        assert "oracle" not in text, f"{path} mentions the oracle"
+
+
+@pytest.mark.parametrize("tokens,E,topk,unit,use_mask", [(1, 8, 2, 16, False), (50, 16, 4, 8, True),
+                                                         (200, 64, 8, 32, True), (3, 4, 4, 128, False)])
+def test_oracle_sort_vectorised_equals_loops(tokens, E, topk, unit, use_mask):
+    rng = np.random.default_rng(tokens + E)
+    ids = np.argsort(rng.random((tokens, E)), axis=1)[:, :topk].astype(np.int32)
+    w = rng.random((tokens, topk), dtype=np.float32)
+    mask = None
+    if use_mask:
+        mask = np.ones(E, np.int32)
+        mask[1::4] = 0
+    a = O.sort_ck_loops(torch.from_numpy(ids), torch.from_numpy(w), E, unit, mask)
+    b = O.sort_ck_numpy(ids, w, E, unit, mask)
+    assert (b["sorted_ids"].astype(np.int64) & 0xFFFFFFFF).tolist() == a[0]
+    assert b["sorted_weights"].tolist() == a[1]
+    assert b["expert_ids"].tolist() == a[2]
+    assert b["counts"].tolist() == a[3]
+
+
+def test_oracle_kernel_quantiser_matches_clamped_oracle_on_benign_inputs():
+    torch.manual_seed(0)
+    x = torch.randn(32, 256).bfloat16()
+    q1, s1 = O.quant_rows_kernel(x, O.FP8, 128)
+    q2, s2 = O.group_quant_fp8_native(x, 128)
+    assert torch.equal(s1, s2)
+    assert (q1.float() - q2.float()).abs().max() <= 32     # at most one e4m3 step at the top binade
+    assert (q1.view(torch.uint8) != q2.view(torch.uint8)).float().mean() < 0.02

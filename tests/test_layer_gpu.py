@@ -1,0 +1,222 @@
+"""Full fused_experts layer vs the CPU oracle (through the public API)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.helpers import bf16, fp8, load_npz, t
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def _dev(*xs):
+    return [x.cuda() if isinstance(x, torch.Tensor) else x for x in xs]
+
+
+def _finish(out):
+    from boltops_b200.fused_moe import ops
+    torch.cuda.synchronize()
+    ops.check_device_status(out.device)
+    return out.cpu()
+
+
+def test_layer_bf16_golden_fixture():
+    from boltops_b200.fused_moe import fused_experts
+    z = load_npz("layer_bf16.npz")
+    args = _dev(bf16(z["hidden"]), bf16(z["w1"]), bf16(z["w2"]), t(z["topk_weights"]), t(z["topk_ids"]))
+    out = _finish(fused_experts(*args))
+    expect = bf16(z["out"])
+    assert O.rel_l2(out, expect) <= 1e-2
+    torch.testing.assert_close(out.float(), expect.float(), rtol=3e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("m", [1, 64, 333])
+def test_layer_bf16_config1(m):
+    """E=8, top-2, H=1024, I=512 (the CPU-runnable benchmark configuration)."""
+    from boltops_b200.fused_moe import fused_experts
+    g = torch.Generator().manual_seed(0)
+    hidden = torch.randn(m, 1024, generator=g).bfloat16()
+    w1 = (torch.randn(8, 1024, 1024, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn(8, 1024, 512, generator=g) * 0.02).bfloat16()
+    wts, ids = O.make_routing(m, 8, 2, 1)
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids)))
+    expect = O.moe_bf16(hidden, w1, w2, wts, ids)
+    assert out.shape == hidden.shape and out.dtype == hidden.dtype
+    assert O.rel_l2(out, expect) <= 1e-2
+
+
+def test_layer_bf16_reference_test_shape_topk1():
+    """hidden 336 (not a multiple of the K tile), as in the reference's top-1 test."""
+    from boltops_b200.fused_moe import fused_experts
+    torch.manual_seed(4)
+    m, h, i, e = 32, 336, 512, 4
+    hidden = (torch.randn(m, h) / 10).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h) / 10).bfloat16()
+    w2 = (torch.randn(e, h, i) / 10).bfloat16()
+    ids = (torch.arange(m)[:, None] % e).to(torch.int32)
+    wts = torch.ones(m, 1)
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids), activation="silu", is_gated=True,
+                                global_num_experts=e))
+    expect = O.moe_bf16(hidden, w1, w2, wts, ids)
+    torch.testing.assert_close(out.float(), expect.float(), rtol=3e-2, atol=2e-2)
+
+
+def _fp8_block_case(m, e, topk, h, i, seed):
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    w1q, w1s = O.quantize_weight_block_fp8(torch.randn(e, 2 * i, h, generator=g) * 0.02)
+    w2q, w2s = O.quantize_weight_block_fp8(torch.randn(e, h, i, generator=g) * 0.02)
+    wts, ids = O.make_routing(m, e, topk, seed + 1)
+    return hidden, w1q, w2q, w1s, w2s, wts, ids
+
+
+@pytest.mark.parametrize("m,e,topk,h,i", [(48, 8, 2, 512, 256), (130, 16, 4, 1024, 384)])
+def test_layer_fp8_block(m, e, topk, h, i):
+    from boltops_b200.fused_moe import fused_experts
+    hidden, w1q, w2q, w1s, w2s, wts, ids = _fp8_block_case(m, e, topk, h, i, 3)
+    out = _finish(fused_experts(*_dev(hidden, w1q, w2q, wts, ids), use_fp8_w8a8=True,
+                                w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128]))
+    expect = O.moe_block_fp8(hidden, w1q, w2q, w1s, w2s, wts, ids, (128, 128))
+    assert O.rel_l2(out, expect) <= 2e-2
+
+
+def test_layer_fp8_block_ue8m0_unfused_path():
+    from boltops_b200.fused_moe import fused_experts
+    hidden, w1q, w2q, w1s, w2s, wts, ids = _fp8_block_case(40, 8, 2, 512, 256, 8)
+    out = _finish(fused_experts(*_dev(hidden, w1q, w2q, wts, ids), use_fp8_w8a8=True,
+                                w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128],
+                                use_ue8m0=True))
+    expect = O.moe_block_fp8(hidden, w1q, w2q, w1s, w2s, wts, ids, (128, 128))
+    assert O.rel_l2(out, expect) <= 4e-2   # power-of-two scales lose up to one bit of range
+
+
+def test_layer_int8_block():
+    from boltops_b200.fused_moe import fused_experts
+    torch.manual_seed(3)
+    m, e, topk, h, i = 64, 8, 2, 512, 256
+    hidden = (torch.randn(m, h) / 10).half()
+    w1 = torch.randint(-127, 128, (e, 2 * i, h), dtype=torch.int8)
+    w2 = torch.randint(-127, 128, (e, h, i), dtype=torch.int8)
+    w1s = torch.rand(e, 2 * i // 128, h // 128) * 1e-2
+    w2s = torch.rand(e, h // 128, i // 128) * 1e-2
+    wts, ids = O.make_routing(m, e, topk, 2)
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids), use_int8_w8a8=True,
+                                w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128],
+                                output_dtype=hidden.dtype))
+    expect = O.moe_block_int8(hidden, w1, w2, w1s, w2s, wts, ids, (128, 128))
+    err = (out.float() - expect.float()).abs().mean() / expect.float().abs().mean()
+    assert err < 0.02 and O.rel_l2(out, expect) <= 2e-2
+
+
+@pytest.mark.parametrize("qdtype", [torch.int8, FP8])
+def test_layer_per_channel(qdtype):
+    from boltops_b200.fused_moe import fused_experts
+    g = torch.Generator().manual_seed(9)
+    m, e, topk, h, i = 100, 16, 4, 512, 384
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    if qdtype == torch.int8:
+        w1, w1s = O.quantize_weight_channel_int8(torch.randn(e, 2 * i, h, generator=g) * 0.02)
+        w2, w2s = O.quantize_weight_channel_int8(torch.randn(e, h, i, generator=g) * 0.02)
+        flags = dict(use_int8_w8a8=True)
+    else:
+        m1 = torch.randn(e, 2 * i, h, generator=g) * 0.02
+        m2 = torch.randn(e, h, i, generator=g) * 0.02
+        w1s = m1.abs().amax(-1) / 448
+        w2s = m2.abs().amax(-1) / 448
+        w1 = (m1 / w1s[..., None]).to(FP8)
+        w2 = (m2 / w2s[..., None]).to(FP8)
+        flags = dict(use_fp8_w8a8=True)
+    wts, ids = O.make_routing(m, e, topk, 4)
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids), per_channel_quant=True,
+                                w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), **flags))
+    expect = O.moe_per_channel(hidden, w1, w2, w1s, w2s, wts, ids, qdtype)
+    assert O.rel_l2(out, expect) <= 2e-2
+
+
+def test_layer_golden_quantised_fixtures():
+    """int8 per-channel fixture produced by the reference's own torch path."""
+    from boltops_b200.fused_moe import fused_experts
+    z = load_npz("layer_int8_channel.npz")
+    hidden, w1, w2 = bf16(z["hidden"]), t(z["w1"]), t(z["w2"])
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, t(z["topk_weights"]), t(z["topk_ids"])),
+                                use_int8_w8a8=True, per_channel_quant=True,
+                                w1_scale=t(z["w1_s"]).cuda(), w2_scale=t(z["w2_s"]).cuda()))
+    assert O.rel_l2(out, bf16(z["out"])) <= 2e-2
+
+
+def test_layer_variants_no_combine_inplace_expert_map_scaling():
+    from boltops_b200.fused_moe import fused_experts
+    g = torch.Generator().manual_seed(5)
+    m, e, topk, h, i = 50, 8, 2, 256, 128
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, i, generator=g) * 0.05).bfloat16()
+    wts, ids = O.make_routing(m, e, topk, 6)
+    base = O.moe_bf16(hidden, w1, w2, wts, ids)
+    d = _dev(hidden, w1, w2, wts, ids)
+    # routed scaling factor
+    out = _finish(fused_experts(*d, routed_scaling_factor=2.5))
+    assert O.rel_l2(out, O.moe_bf16(hidden, w1, w2, wts, ids, 2.5)) <= 1e-2
+    # no_combine returns unweighted per-route rows
+    nc = _finish(fused_experts(*d, no_combine=True))
+    assert nc.shape == (m, topk, h)
+    comb = (nc.float() * wts[:, :, None]).sum(1)
+    assert O.rel_l2(comb, base) <= 1e-2
+    # expert-parallel masking: two ranks' partial sums add up to the full layer
+    parts = []
+    for rank in range(2):
+        emap = torch.full((e,), -1, dtype=torch.int32)
+        emap[rank * 4:(rank + 1) * 4] = torch.arange(4, dtype=torch.int32)
+        sl = slice(rank * 4, rank * 4 + 4)
+        parts.append(_finish(fused_experts(hidden.cuda(), w1[sl].cuda(), w2[sl].cuda(), wts.cuda(),
+                                           ids.cuda(), expert_map=emap.cuda(),
+                                           global_num_experts=e)).float())
+    assert O.rel_l2(parts[0] + parts[1], base) <= 1.5e-2
+    # inplace returns the input tensor itself
+    hid_dev = hidden.cuda()
+    ret = fused_experts(hid_dev, d[1], d[2], d[3], d[4], inplace=True)
+    assert ret.data_ptr() == hid_dev.data_ptr()
+    assert O.rel_l2(_finish(ret), base) <= 1e-2
+
+
+def test_layer_non_fused_activation_and_bias():
+    from boltops_b200.fused_moe import fused_experts
+    g = torch.Generator().manual_seed(12)
+    m, e, topk, h, i = 40, 4, 2, 256, 128
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, i, generator=g) * 0.05).bfloat16()
+    b1 = (torch.randn(e, 2 * i, generator=g) * 0.1).bfloat16()
+    b2 = (torch.randn(e, h, generator=g) * 0.1).bfloat16()
+    wts, ids = O.make_routing(m, e, topk, 13)
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids), activation="gelu",
+                                b1=b1.cuda(), b2=b2.cuda()))
+    rep = hidden[:, None, :].expand(m, topk, h).reshape(-1, h)
+    flat = ids.reshape(-1)
+    routed = torch.zeros(m * topk, h)
+    for ex in range(e):
+        sel = flat == ex
+        c1 = (rep[sel].float() @ w1[ex].float().t() + b1[ex].float()).bfloat16()
+        act = O.activation_ref(c1, "gelu", True).bfloat16()
+        routed[sel] = (act.float() @ w2[ex].float().t() + b2[ex].float())
+    expect = (routed.view(m, topk, h) * wts[:, :, None]).sum(1)
+    assert O.rel_l2(out, expect) <= 1.5e-2
+
+
+def test_layer_argument_errors():
+    from boltops_b200.fused_moe import fused_experts
+    hid = torch.zeros(1, 128, dtype=torch.bfloat16, device="cuda")
+    w1 = torch.zeros(1, 256, 128, dtype=torch.bfloat16, device="cuda")
+    w2 = torch.zeros(1, 128, 128, dtype=torch.bfloat16, device="cuda")
+    wts = torch.ones(1, 1, device="cuda")
+    ids = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError):
+        fused_experts(hid, w1, w2, wts, ids, use_ue8m0=True)
+    with pytest.raises(ValueError):
+        fused_experts(hid, w1, w2, wts, ids, gemm1_beta=1.0)
+    with pytest.raises(ValueError):
+        fused_experts(hid, w1, w2, wts, ids, activation="nope")
+    with pytest.raises(AssertionError):
+        fused_experts(hid, w1, w2, wts[:, :0], ids)
+    with pytest.raises(NotImplementedError):
+        fused_experts(hid, w1, w2, wts, ids, use_int4_w4a16=True)
