@@ -1,0 +1,445 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-MoE layer (``fused_experts``) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--tokens M]
+    python bench.py --impl reference ...      # the reference's torch CPU path (oracle port)
+
+One "step" is one MoE layer forward over a batch of M synthetic tokens: dynamic
+activation quantisation, token-to-expert sort, gather, both grouped GEMMs (SiLU-
+and-mul fused), top-k combine -- the stages the reference times.  Weights and
+routing are generated once from a seed (untimed).  Rank 0 prints ONE JSON line.
+
+N > 1 (launched through torch.distributed.run): experts are sharded contiguously
+over the ranks (expert parallelism), every rank brings its own M tokens (weak
+scaling), tokens travel to the owning rank and back with NCCL all-to-all.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FP8 = torch.float8_e4m3fn
+
+# name -> shape of the benchmark configurations (E experts, K top-k, H hidden, I intermediate)
+WORKLOADS = {
+    "small_bf16": dict(kind="bf16", E=8, K=2, H=1024, I=512, M=64),
+    "mixtral_8x7b_bf16": dict(kind="bf16", E=8, K=2, H=4096, I=14336, M=8192),
+    "deepseek_v3_fp8_block": dict(kind="fp8_block", E=256, K=8, H=7168, I=2048, M=4096),
+    "qwen3_30b_int8_channel": dict(kind="int8_channel", E=128, K=8, H=2048, I=768, M=16384),
+    "qwen3_235b_fp8_block_zipf": dict(kind="fp8_block", E=128, K=8, H=4096, I=1536, M=256,
+                                      zipf=1.2),
+}
+DEFAULT_WORKLOAD = "deepseek_v3_fp8_block"
+
+# DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), keyed by
+# (workload, tokens); None when no capture exists for that case.
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0,
+                source="fallback")
+
+
+# ---------------------------------------------------------------------------
+# synthetic inputs (seeded; generated on the device expert by expert)
+# ---------------------------------------------------------------------------
+def _quant_block_fp8(w):
+    n, k = w.shape
+    v = w.float().reshape(n // 128, 128, k // 128, 128)
+    amax = v.abs().amax(dim=(1, 3), keepdim=True).clamp(min=1e-10)
+    s = amax / 448.0
+    q = (v / s).clamp(-448, 448).to(FP8).reshape(n, k)
+    return q, s.reshape(n // 128, k // 128)
+
+
+def _quant_channel_int8(w):
+    amax = w.float().abs().amax(dim=-1, keepdim=True).clamp(min=1e-10)
+    s = amax / 127.0
+    return (w.float() / s).round().clamp(-128, 127).to(torch.int8), s.squeeze(-1)
+
+
+def make_weights(cfg, device, experts, seed):
+    """Weights of the listed (global) expert ids: ~N(0, 0.02) masters, quantised per
+    the workload kind.  Each expert has its own seed, so any rank can build any shard."""
+    kind, H, I = cfg["kind"], cfg["H"], cfg["I"]
+    n = len(experts)
+    if kind == "bf16":
+        w1 = torch.empty(n, 2 * I, H, dtype=torch.bfloat16, device=device)
+        w2 = torch.empty(n, H, I, dtype=torch.bfloat16, device=device)
+        w1s = w2s = None
+    elif kind == "fp8_block":
+        w1 = torch.empty(n, 2 * I, H, dtype=FP8, device=device)
+        w2 = torch.empty(n, H, I, dtype=FP8, device=device)
+        w1s = torch.empty(n, 2 * I // 128, H // 128, dtype=torch.float32, device=device)
+        w2s = torch.empty(n, H // 128, I // 128, dtype=torch.float32, device=device)
+    else:
+        w1 = torch.empty(n, 2 * I, H, dtype=torch.int8, device=device)
+        w2 = torch.empty(n, H, I, dtype=torch.int8, device=device)
+        w1s = torch.empty(n, 2 * I, dtype=torch.float32, device=device)
+        w2s = torch.empty(n, H, dtype=torch.float32, device=device)
+    g = torch.Generator(device=device)
+    for j, e in enumerate(experts):
+        g.manual_seed(seed * 100003 + e)
+        m1 = torch.randn(2 * I, H, generator=g, device=device) * 0.02
+        m2 = torch.randn(H, I, generator=g, device=device) * 0.02
+        if kind == "bf16":
+            w1[j], w2[j] = m1.bfloat16(), m2.bfloat16()
+        elif kind == "fp8_block":
+            w1[j], w1s[j] = _quant_block_fp8(m1)
+            w2[j], w2s[j] = _quant_block_fp8(m2)
+        else:
+            w1[j], w1s[j] = _quant_channel_int8(m1)
+            w2[j], w2s[j] = _quant_channel_int8(m2)
+    return w1, w2, w1s, w2s
+
+
+def make_routing(m, num_experts, topk, seed, zipf_alpha=None):
+    """Router logits ~N(0,1) -> softmax -> top-k -> renormalise (fp32 weights, int32
+    ids).  With ``zipf_alpha`` the experts of a token are drawn without replacement from
+    p(e) ~ (rank_e + 1)^-alpha over a seed-fixed expert permutation."""
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(m, num_experts, generator=g, dtype=torch.float32)
+    scores = torch.softmax(logits, dim=-1)
+    if zipf_alpha is None:
+        wts, ids = torch.topk(scores, k=topk, dim=-1)
+    else:
+        perm = torch.randperm(num_experts, generator=g)
+        p = (torch.arange(num_experts, dtype=torch.float64) + 1.0) ** (-zipf_alpha)
+        prob = torch.empty(num_experts, dtype=torch.float64)
+        prob[perm] = p / p.sum()
+        ids = torch.multinomial(prob.expand(m, -1), topk, replacement=False, generator=g)
+        wts = scores.gather(1, ids)
+    wts = wts / wts.sum(dim=-1, keepdim=True)
+    return wts.float().contiguous(), ids.to(torch.int32).contiguous()
+
+
+def make_tokens(cfg, m, seed):
+    """hidden ~N(0,1) bf16 and softmax top-k routing, on the host."""
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(m, cfg["H"], generator=g).bfloat16()
+    wts, ids = make_routing(m, cfg["E"], cfg["K"], seed + 1, cfg.get("zipf"))
+    return hidden, wts, ids
+
+
+def layer_kwargs(cfg, w1s, w2s):
+    if cfg["kind"] == "fp8_block":
+        return dict(use_fp8_w8a8=True, w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+    if cfg["kind"] == "int8_channel":
+        return dict(use_int8_w8a8=True, per_channel_quant=True, w1_scale=w1s, w2_scale=w2s)
+    return {}
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=mx or None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ---------------------------------------------------------------------------
+# roofline bookkeeping
+# ---------------------------------------------------------------------------
+def gemm1_algorithmic(cfg, m, active_experts):
+    """Algorithmic bytes and flops of one GEMM1 launch (gate/up GEMM + fused epilogue)."""
+    K, H, I = cfg["K"], cfg["H"], cfg["I"]
+    routes = m * K
+    wb = 2 if cfg["kind"] == "bf16" else 1
+    ab = 2 if cfg["kind"] == "bf16" else 1
+    ob = 1 if cfg["kind"] == "fp8_block" else 2
+    byts = active_experts * 2 * I * H * wb + routes * H * ab + routes * I * ob
+    if cfg["kind"] == "fp8_block":
+        byts += active_experts * (2 * I // 128) * (H // 128) * 4 + routes * (H // 128) * 4 \
+            + routes * (I // 128) * 4
+    return byts, 4.0 * routes * H * I
+
+
+def layer_flops(cfg, m):
+    return 6.0 * m * cfg["K"] * cfg["H"] * cfg["I"]
+
+
+# ---------------------------------------------------------------------------
+# the reference arm: the reference's torch path (CPU oracle port) on host cores
+# ---------------------------------------------------------------------------
+def cpu_reference(cfg, m, seed, budget_experts=None):
+    """Time the CPU oracle on a bounded sample: the routes of the first ``E_s`` experts
+    of the M-token batch (all quantisation + both GEMMs + activation for those experts),
+    extrapolated linearly in the number of experts.  Returns tokens/s and a description."""
+    from oracle import moe_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    E, K = cfg["E"], cfg["K"]
+    per_expert_flops = layer_flops(cfg, m) / E
+    # aim for ~15 s at an assumed ~25 GFLOP/s/core effective rate of the fp32 reference path
+    if budget_experts is None:
+        budget_experts = int(max(1, min(E, 15.0 * cores * 25e9 / max(per_expert_flops, 1.0))))
+        budget_experts = max(1, min(budget_experts, 32 if cfg["kind"] != "bf16" else E))
+    es = budget_experts
+    hidden, wts, ids = make_tokens(cfg, m, seed)
+    w1, w2, w1s, w2s = make_weights(cfg, "cpu", list(range(es)), seed)
+    emap = torch.full((E,), -1, dtype=torch.int32)
+    emap[:es] = torch.arange(es, dtype=torch.int32)
+    t0 = time.perf_counter()
+    if cfg["kind"] == "fp8_block":
+        O.moe_block_fp8(hidden, w1, w2, w1s, w2s, wts, ids, (128, 128), expert_map=emap)
+    elif cfg["kind"] == "int8_channel":
+        O.moe_per_channel(hidden, w1, w2, w1s, w2s, wts, ids, torch.int8, expert_map=emap)
+    else:
+        sel_ids = torch.where(ids < es, ids, torch.full_like(ids, -1))
+        O.moe_bf16(hidden, w1, w2, wts, sel_ids)
+    dt = time.perf_counter() - t0
+    full = dt * E / es
+    sample = (f"oracle port of the reference torch path on {es} of {E} experts of the "
+              f"M={m} batch ({dt:.1f} s), scaled by {E}/{es}")
+    return m / full, cores, sample, full
+
+
+# ---------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (0 = workload default)")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    cfg = dict(WORKLOADS[args.workload])
+    m = args.tokens or cfg["M"]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    warmup = max(args.warmup, 3)
+    config = dict(workload=f"{args.workload}_M{m}", experts=cfg["E"], topk=cfg["K"],
+                  hidden=cfg["H"], intermediate=cfg["I"], tokens_per_gpu=m,
+                  parallelism=f"ep{world}" if world > 1 else "single",
+                  l2="inputs larger than L2 (weights stream from HBM every step)")
+    dtype = {"bf16": "bf16", "fp8_block": "fp8_e4m3", "int8_channel": "int8"}[cfg["kind"]]
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        value = None
+        samples = []
+        for _ in range(max(1, min(args.steps, 1))):
+            value, cores, sample, full = cpu_reference(cfg, m, args.seed)
+            samples.append(full)
+        line = dict(metric="moe_layer_tokens_per_s", value=value, unit="tokens/s",
+                    n_gpus=args.gpus, steps=1, warmup=0, ms_per_step=full * 1e3,
+                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype=dtype,
+                    data="synthetic", config=config, impl="reference",
+                    cpu_baseline=dict(value=value, unit="tokens/s", cores=cores, kind="port",
+                                      sample=sample),
+                    e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0,
+                             d2h_bytes_per_step=0))
+        print(json.dumps(line), flush=True)
+        return
+
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import fused_experts, layer, ops
+
+    _cabi.load()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    E = cfg["E"]
+    per_rank = E // world
+    my_experts = list(range(rank * per_rank, (rank + 1) * per_rank))
+    w1, w2, w1s, w2s = make_weights(cfg, device, my_experts, args.seed)
+    hidden_h, wts_h, ids_h = make_tokens(cfg, m, args.seed + 17 * rank)
+    hidden_h, wts_h, ids_h = hidden_h.pin_memory(), wts_h.pin_memory(), ids_h.pin_memory()
+    hidden, wts, ids = hidden_h.to(device), wts_h.to(device), ids_h.to(device)
+    kwargs = layer_kwargs(cfg, w1s, w2s)
+    out_host = torch.empty((m, cfg["H"]), dtype=torch.bfloat16).pin_memory()
+
+    if world > 1:
+        from boltops_b200.fused_moe.ep import ExpertParallelMoE
+
+        ep = ExpertParallelMoE(dist.group.WORLD, E, device)
+
+        def step(h, w, i):
+            return ep.forward(h, w1, w2, w, i, **kwargs)
+    else:
+        def step(h, w, i):
+            return fused_experts(h, w1, w2, w, i, **kwargs)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1) / steps
+        if dist is not None:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- device-resident timing ------------------------------------------------------------
+    for _ in range(warmup):
+        step(hidden, wts, ids)
+    sync_all()
+    ops.check_device_status(device)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = ops.launch_count()
+    ms = timed(lambda: step(hidden, wts, ids), args.steps)
+    launches = (ops.launch_count() - launches0) // max(args.steps, 1)
+
+    # ---- end to end through the public API with host buffers ----------------------------
+    def e2e_step():
+        h = hidden_h.to(device, non_blocking=True)
+        w = wts_h.to(device, non_blocking=True)
+        i = ids_h.to(device, non_blocking=True)
+        out = step(h, w, i)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_device_status(device)
+
+    # ---- per-stage timing of the dominant kernel (rank-local, CUDA events) ---------------
+    stage_ms = None
+    if world == 1:
+        timer = layer.StageTimer()
+        layer.STAGE_TIMER = timer
+        for _ in range(args.steps):
+            step(hidden, wts, ids)
+        torch.cuda.synchronize()
+        layer.STAGE_TIMER = None
+        stage_ms = timer.summary()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    total_tokens = m * world
+    value = total_tokens / (ms * 1e-3)
+    tflops = layer_flops(cfg, m) * world / (ms * 1e-3) / 1e12
+    line = dict(metric="moe_layer_tokens_per_s", value=value, unit="tokens/s", n_gpus=world,
+                steps=args.steps, warmup=warmup, ms_per_step=ms, higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype=dtype, data="synthetic", config=config,
+                tflops=tflops, gpu_launches=launches, clocks=clocks,
+                e2e=dict(value=total_tokens / (ms_e2e * 1e-3), unit="tokens/s",
+                         ms_per_step=ms_e2e,
+                         h2d_bytes_per_step=(hidden_h.numel() * 2 + wts_h.numel() * 4
+                                             + ids_h.numel() * 4) * world,
+                         d2h_bytes_per_step=out_host.numel() * 2 * world))
+    if stage_ms is not None:
+        line["stage_ms"] = stage_ms
+        active = int(torch.unique(ids_h).numel())
+        byts, flops = gemm1_algorithmic(cfg, m, active)
+        g_ms = stage_ms.get("gemm1")
+        if g_ms:
+            t_hbm = byts / (peaks["hbm_gbs"] * 1e9)
+            tc_peak = peaks["bf16_tflops"] * (1.0 if cfg["kind"] == "bf16" else 2.0)
+            t_tc = flops / (tc_peak * 1e12)
+            traffic = NCU_TRAFFIC_BYTES.get((args.workload, m))
+            if t_hbm >= t_tc:
+                ach = byts / (g_ms * 1e-3) / 1e9
+                roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s",
+                            frac=ach / peaks["hbm_gbs"], traffic=traffic)
+            else:
+                ach = flops / (g_ms * 1e-3) / 1e12
+                roof = dict(bound="tensor", achieved=ach, peak=tc_peak, unit="TFLOP/s",
+                            frac=ach / tc_peak, traffic=traffic)
+            roof.update(kernel="k_grouped_gemm (gate/up GEMM + SiLU-mul epilogue)",
+                        ms_per_launch=g_ms, algorithmic_bytes=byts, algorithmic_flops=flops,
+                        peak_source=peaks["source"] + (
+                            "" if cfg["kind"] == "bf16" or t_hbm >= t_tc
+                            else " bf16 x2 (no measured 8-bit peak)"))
+            line["roofline"] = roof
+    if not args.no_cpu_baseline and world == 1:
+        v, cores, sample, _ = cpu_reference(cfg, m, args.seed)
+        line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=cores, kind="port",
+                                    sample=sample)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

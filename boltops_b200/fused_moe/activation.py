@@ -121,6 +121,8 @@ def apply_activation(activation: str, is_gated: bool, activated_out: torch.Tenso
                                       dtype_code(ffn1_out_2d.dtype), rows, n_out, kind,
                                       int(is_gated), alpha, limit, ptr(rows_dev),
                                       stream_of(ffn1_out_2d)))
+    from . import ops
+    ops._count()
 
 
 def moe_activation(activated_out: torch.Tensor, ffn1_out_2d: torch.Tensor,
@@ -170,4 +172,6 @@ def activation_quant(ffn1_out_2d: torch.Tensor, activation: str, is_gated: bool,
         check(lib.bolt_act_quant(ptr(ffn1_out_2d), dtype_code(ffn1_out_2d.dtype), rows, n_out, kind,
                                  int(is_gated), dtype_code(quant_dtype), ptr(row_multiplier),
                                  ptr(q), ptr(scale), ptr(rows_dev), stream_of(ffn1_out_2d)))
+    from . import ops
+    ops._count()
     return q, scale

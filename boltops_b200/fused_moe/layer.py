@@ -27,6 +27,48 @@ from .activation import activation_quant, apply_activation, normalize_moe_activa
 _FLOAT_OUT = (torch.float16, torch.bfloat16, torch.float32)
 
 
+class StageTimer:
+    """Optional per-stage CUDA-event timing of the layer (benchmarks only).
+
+    Assign an instance to ``STAGE_TIMER``; every stage of ``fused_experts_impl`` is
+    then bracketed by events on torch's current stream.  ``summary()`` synchronises
+    and returns the mean milliseconds per stage."""
+
+    def __init__(self):
+        self._events = {}
+
+    def begin(self):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
+    def end(self, name, start):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._events.setdefault(name, []).append((start, ev))
+
+    def summary(self):
+        torch.cuda.synchronize()
+        return {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in self._events.items()}
+
+
+STAGE_TIMER: Optional[StageTimer] = None
+
+
+class _Stage:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        self.t = STAGE_TIMER
+        self.start = self.t.begin() if self.t is not None else None
+
+    def __exit__(self, *exc):
+        if self.t is not None:
+            self.t.end(self.name, self.start)
+        return False
+
+
 def _chunk_size() -> int:
     raw = os.environ.get("BOLTOPS_FUSED_MOE_CHUNK_SIZE",
                          os.environ.get("TRITON_FUSED_MOE_CHUNK_SIZE", "32768"))
@@ -188,27 +230,31 @@ def fused_experts_impl(
         wts = topk_weights[begin:end]
 
         # ---- sort -----------------------------------------------------------------------
-        sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
-            ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
-            alloc_moe_buf=False)
+        with _Stage("sort"):
+            sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
+                ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
+                alloc_moe_buf=False)
         cap = sorted_ids.shape[0]
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
         a_scale = None
         if quantised:
-            if x.dtype in (torch.float16, torch.bfloat16, torch.float32):
-                if block_mode:
-                    x_q, x_s = ops.per_block_quant(x, 128, q_dtype, scale_ue8m0=use_ue8m0)
+            with _Stage("quant_a1"):
+                if x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+                    if block_mode:
+                        x_q, x_s = ops.per_block_quant(x, 128, q_dtype, scale_ue8m0=use_ue8m0)
+                    else:
+                        x_q, x_s = ops.per_token_quant(x, quant_dtype=q_dtype)
                 else:
-                    x_q, x_s = ops.per_token_quant(x, quant_dtype=q_dtype)
-            else:
-                assert a1_scale is not None, "pre-quantised hidden_states need a1_scale"
-                x_q = x
-                x_s = a1_scale[begin:end] if a1_scale.ndim == 2 else a1_scale
-                x_s = x_s.float()
-            a_sorted, a_scale = ops.gather_rows(x_q, sorted_ids, num_valid, cap, x_s)
+                    assert a1_scale is not None, "pre-quantised hidden_states need a1_scale"
+                    x_q = x
+                    x_s = a1_scale[begin:end] if a1_scale.ndim == 2 else a1_scale
+                    x_s = x_s.float()
+            with _Stage("gather"):
+                a_sorted, a_scale = ops.gather_rows(x_q, sorted_ids, num_valid, cap, x_s)
         else:
-            a_sorted, _ = ops.gather_rows(x, sorted_ids, num_valid, cap)
+            with _Stage("gather"):
+                a_sorted, _ = ops.gather_rows(x, sorted_ids, num_valid, cap)
 
         common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
                       sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
@@ -219,20 +265,23 @@ def fused_experts_impl(
         if fuse_quant:
             act = torch.empty((cap, act_dim), device=dev, dtype=q_dtype)
             act_scale = torch.empty((act_dim // 128, cap), device=dev, dtype=torch.float32)
-            ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
+            with _Stage("gemm1"):
+              ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
                              a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
                              c_scale=act_scale, c_scale_ld=cap, mid_dtype=mid_dtype,
                              mul_routed_weight=apply_router_weight_on_input, **common)
         else:
             if fused_silu:
                 act_f = torch.empty((cap, act_dim), device=dev, dtype=mid_dtype)
-                ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL, a=a_sorted, b=w1, c=act_f,
+                with _Stage("gemm1"):
+                  ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL, a=a_sorted, b=w1, c=act_f,
                                  a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
                                  mid_dtype=mid_dtype,
                                  mul_routed_weight=apply_router_weight_on_input, **common)
             else:
                 c1 = torch.empty((cap, n1), device=dev, dtype=mid_dtype)
-                ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1, c=c1,
+                with _Stage("gemm1"):
+                  ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1, c=c1,
                                  a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
                                  mul_routed_weight=apply_router_weight_on_input, **common)
                 act_f = torch.empty((cap, act_dim), device=dev, dtype=mid_dtype)
@@ -240,12 +289,13 @@ def fused_experts_impl(
                                  activation_situ_beta, activation_situ_linear_beta,
                                  rows_dev=num_valid)
             if quantised:
-                if block_mode:
-                    act, s = ops.per_block_quant(act_f, 128, q_dtype, scale_ue8m0=use_ue8m0)
-                    act_scale = s.t().contiguous()          # [act_dim/128, cap]
-                else:
-                    act, s = ops.per_token_quant(act_f, quant_dtype=q_dtype)
-                    act_scale = s.reshape(-1)
+                with _Stage("quant_a2"):
+                    if block_mode:
+                        act, s = ops.per_block_quant(act_f, 128, q_dtype, scale_ue8m0=use_ue8m0)
+                        act_scale = s.t().contiguous()          # [act_dim/128, cap]
+                    else:
+                        act, s = ops.per_token_quant(act_f, quant_dtype=q_dtype)
+                        act_scale = s.reshape(-1)
             else:
                 act = act_f
 
@@ -256,14 +306,17 @@ def fused_experts_impl(
             c3 = out[begin:end]
         else:
             c3 = torch.empty((m, topk, model_dim), device=dev, dtype=output_dtype)
-        ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2, c=c3.view(m * topk, model_dim),
-                         a_scale=act_scale, a_scale_ld=cap, b_scale=w2_scale_c, bias=b2,
-                         scatter=True, mul_routed_weight=needs_router_weight, **common)
+        with _Stage("gemm2"):
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2,
+                             c=c3.view(m * topk, model_dim), a_scale=act_scale, a_scale_ld=cap,
+                             b_scale=w2_scale_c, bias=b2, scatter=True,
+                             mul_routed_weight=needs_router_weight, **common)
 
         # ---- combine ----------------------------------------------------------------------------
         if no_combine:
             if c3.data_ptr() != out[begin:end].data_ptr():
                 out[begin:end].copy_(c3)
         else:
-            ops.moe_sum(c3, out[begin:end], routed_scaling_factor)
+            with _Stage("combine"):
+                ops.moe_sum(c3, out[begin:end], routed_scaling_factor)
     return out

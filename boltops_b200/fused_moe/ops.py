@@ -20,6 +20,18 @@ from .._cabi import check, dtype_code, ptr, stream_of
 
 SORT_UNIT = 128  # row-tile of the grouped GEMM == padding unit of the sort
 
+_launches = 0   # kernels launched through this module (bookkeeping for benchmarks)
+
+
+def launch_count() -> int:
+    """Number of CUDA kernels this module has launched so far in this process."""
+    return _launches
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
 
 def _require_cuda(*tensors):
     for t in tensors:
@@ -78,6 +90,7 @@ def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_exper
             ptr(num_valid), ptr(moe_buf),
             0 if moe_buf is None else moe_buf.numel() * moe_buf.element_size(),
             ptr(ws), ws_bytes, stream_of(topk_ids)))
+    _count(1 if ws_bytes <= 16 else 3)
     return sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf
 
 
@@ -103,6 +116,7 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
         check(lib.bolt_moe_align_block_size(
             ptr(ids), numel, num_experts, block_size, ptr(expert_map), ptr(sorted_ids),
             ptr(expert_ids), ptr(num_post), ptr(ws), ws_bytes, stream_of(ids)))
+    _count(1 if ws_bytes <= 16 else 3)
     return sorted_ids, expert_ids, num_post
 
 
@@ -126,6 +140,7 @@ def quant_rows(x: torch.Tensor, quant_dtype: torch.dtype, group: Optional[int] =
         check(lib.bolt_quant_rows(ptr(x), dtype_code(x.dtype), rows, cols, g,
                                   dtype_code(quant_dtype), int(scale_ue8m0), ptr(q), ptr(scales),
                                   stream_of(x)))
+    _count()
     return q, scales
 
 
@@ -175,6 +190,7 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Te
         check(lib.bolt_gather_rows(ptr(src), m, row_bytes, ptr(src_scale), groups,
                                    ptr(sorted_ids), ptr(num_valid), capacity, ptr(dst),
                                    ptr(dst_scale), ld, stream_of(src)))
+    _count()
     return dst, dst_scale
 
 
@@ -197,6 +213,7 @@ def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
                                ptr(output_tensor), dtype_code(output_tensor.dtype), m, topk, n,
                                float(routed_scaling_factor), ptr(router_weights),
                                stream_of(input_tensor)))
+    _count()
     return output_tensor
 
 
@@ -265,3 +282,4 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
     args.sm_count = sm_count
     with torch.cuda.device(a.device):
         check(lib.bolt_grouped_gemm(C.byref(args), stream_of(a)))
+    _count()

@@ -343,11 +343,12 @@ def moe_bf16(hidden, w1, w2, topk_weights, topk_ids,
 
 
 def moe_block_fp8(hidden, w1, w2, w1_s, w2_s, topk_weights, topk_ids, block,
-                  expert_map=None):
+                  expert_map=None, power2: bool = False):
     """fp8 [bn,bk]-block-scaled layer (tune_moe_fp8.py:237-287): quantise the
     repeated rows per 1xbk group, block matmul -> activation dtype, gated SiLU
     (tools common.py:122-135: computed in the activation dtype), re-quantise,
-    block matmul, weighted sum in the activation dtype."""
+    block matmul, weighted sum in the activation dtype.  ``power2`` swaps in the
+    power-of-two-scale quantiser (the ``use_ue8m0`` recipe, quant.py:636-661)."""
     m, h = hidden.shape
     k = topk_ids.shape[1]
     rep = _repeat_rows(hidden, k)
@@ -355,7 +356,8 @@ def moe_block_fp8(hidden, w1, w2, w1_s, w2_s, topk_weights, topk_ids, block,
     flat = topk_ids.reshape(-1).long()
     if expert_map is not None:
         flat = expert_map.long()[flat]
-    a_q, a_s = group_quant_fp8_native(rep, block[1])
+    quant = group_quant_fp8_power2 if power2 else group_quant_fp8_native
+    a_q, a_s = quant(rep, block[1])
     for e in range(w1.shape[0]):
         sel = flat == e
         if not sel.any():
@@ -363,7 +365,7 @@ def moe_block_fp8(hidden, w1, w2, w1_s, w2_s, topk_weights, topk_ids, block,
         c1 = block_scaled_matmul(a_q[sel], w1[e], a_s[sel], w1_s[e], block, hidden.dtype)
         gate, up = torch.chunk(c1, 2, dim=-1)
         act = F.silu(gate) * up
-        act_q, act_s = group_quant_fp8_native(act.contiguous(), block[1])
+        act_q, act_s = quant(act.contiguous(), block[1])
         out[sel] = block_scaled_matmul(act_q, w2[e], act_s, w2_s[e], block, hidden.dtype)
     return (out.view(m, k, -1) * topk_weights.reshape(m, k, 1).to(out.dtype)).sum(dim=1)
 
