@@ -286,6 +286,32 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int tiles_n
 // ---------------------------------------------------------------------------
 // Kernel
 // ---------------------------------------------------------------------------
+// fast fp32 helpers for the epilogues (results are rounded to 16 bits right after)
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+// Round two floats through the 16-bit storage type `dt` (BOLT_F32: unchanged).
+__device__ __forceinline__ void round2(float& a, float& b, int dt) {
+  if (dt == BOLT_BF16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&h);
+    a = __uint_as_float(u << 16);
+    b = __uint_as_float(u & 0xFFFF0000u);
+  } else if (dt == BOLT_F16) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 f = __half22float2(h);
+    a = f.x;
+    b = f.y;
+  }
+}
+
+// Per-row tile metadata, fetched one tile ahead of its use.
+struct RowMeta {
+  int expert;
+  int sid;
+  float rw;
+  float a_s;  // channel kinds: row scale; block kinds: scale of K block 0
+};
+
 template <int OPK, bool BS, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -298,7 +324,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* ctrl = smem + kStages * kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[S], empty[S], tfull[2], tempty[2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[S], empty[S], tfull[2], tempty[2], x
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 132);
   float* amax_x = reinterpret_cast<float*>(ctrl + 1024);  // [2 tile parities][2 halves][128 rows]
@@ -341,115 +367,144 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int num_valid = min(*p.num_valid, p.capacity);
   const int num_m = num_valid / kBM;
   const int total_tiles = num_m * p.tiles_n;
+  const int stride = gridDim.x;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
-        const int expert = p.expert_ids[tc.m_blk];
-        if (expert < 0 || expert >= p.num_experts) continue;
-        const int n0 = GATED ? tc.n_blk * 128 : tc.n_blk * 256;
-        const int n1 = GATED ? p.n_half + tc.n_blk * 128 : n0 + 128;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1);
-          if (!ok) break;
-          const uint32_t full = bar_full + 8 * s;
-          const uint32_t sa = smem_base + s * kStageBytes;
-          mbar_expect_tx(full, kStageBytes);
-          tma_load_2d(sa, &tma_a, full, kb * kBKElems, tc.m_blk * kBM);
-          tma_load_3d(sa + kABytes, &tma_b, full, kb * kBKElems, n0, expert);
-          tma_load_3d(sa + kABytes + kBBytes / 2, &tma_b, full, kb * kBKElems, n1, expert);
-          if (++s == kStages) { s = 0; ph ^= 1; }
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        int tile = blockIdx.x;
+        int expert_next = -1;
+        if (tile < total_tiles)
+          expert_next = p.expert_ids[tile_coord(tile, num_m, p.tiles_n, p.group_m).m_blk];
+        for (; ok && tile < total_tiles; tile += stride) {
+          const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+          const int expert = expert_next;
+          if (tile + stride < total_tiles)
+            expert_next = p.expert_ids[tile_coord(tile + stride, num_m, p.tiles_n, p.group_m).m_blk];
+          if (expert < 0 || expert >= p.num_experts) continue;
+          const int n0 = GATED ? tc.n_blk * 128 : tc.n_blk * 256;
+          const int n1 = GATED ? p.n_half + tc.n_blk * 128 : n0 + 128;
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1);
+            if (!ok) break;
+            const uint32_t full = bar_full + 8 * s;
+            const uint32_t sa = smem_base + s * kStageBytes;
+            mbar_expect_tx(full, kStageBytes);
+            tma_load_2d(sa, &tma_a, full, kb * kBKElems, tc.m_blk * kBM);
+            tma_load_3d(sa + kABytes, &tma_b, full, kb * kBKElems, n0, expert);
+            tma_load_3d(sa + kABytes + kBBytes / 2, &tma_b, full, kb * kBKElems, n1, expert);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+          }
         }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      int s = 0, t = 0;
-      uint32_t ph = 0, tph = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
-        const int expert = p.expert_ids[tc.m_blk];
-        if (expert < 0 || expert >= p.num_experts) continue;
-        if (!BS) {
-          ok = mbar_wait(bar_tempty + 8 * t, tph ^ 1, abort_flag, p.status, 2);
-          if (!ok) break;
-          tc_fence_after();
-        }
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (BS) {
+    } else if (warp == 1) {
+      // ------------------------------ MMA issuer --------------------------------
+      if (lane == 0) {
+        int s = 0, t = 0;
+        uint32_t ph = 0, tph = 0;
+        bool ok = true;
+        int tile = blockIdx.x;
+        int expert_next = -1;
+        if (tile < total_tiles)
+          expert_next = p.expert_ids[tile_coord(tile, num_m, p.tiles_n, p.group_m).m_blk];
+        for (; ok && tile < total_tiles; tile += stride) {
+          const int expert = expert_next;
+          if (tile + stride < total_tiles)
+            expert_next = p.expert_ids[tile_coord(tile + stride, num_m, p.tiles_n, p.group_m).m_blk];
+          if (expert < 0 || expert >= p.num_experts) continue;
+          if (!BS) {
             ok = mbar_wait(bar_tempty + 8 * t, tph ^ 1, abort_flag, p.status, 2);
             if (!ok) break;
             tc_fence_after();
           }
-          ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t sa = smem_base + s * kStageBytes;
-          const uint64_t adesc = make_smem_desc(sa);
-          const uint64_t bdesc = make_smem_desc(sa + kABytes);
-          const uint32_t d = tmem_base + t * kAccCols;
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            if (BS) {
+              ok = mbar_wait(bar_tempty + 8 * t, tph ^ 1, abort_flag, p.status, 2);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_base + s * kStageBytes;
+            const uint64_t adesc = make_smem_desc(sa);
+            const uint64_t bdesc = make_smem_desc(sa + kABytes);
+            const uint32_t d = tmem_base + t * kAccCols;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t accum = BS ? (k > 0) : (kb > 0 || k > 0);
-            tc_mma<OPK>(d, adesc + 2 * k, bdesc + 2 * k, p.idesc, accum);
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t accum = BS ? (k > 0) : (kb > 0 || k > 0);
+              tc_mma<OPK>(d, adesc + 2 * k, bdesc + 2 * k, p.idesc, accum);
+            }
+            tc_commit(bar_empty + 8 * s);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+            if (BS) {
+              tc_commit(bar_tfull + 8 * t);
+              if (++t == 2) { t = 0; tph ^= 1; }
+            }
           }
-          tc_commit(bar_empty + 8 * s);
-          if (++s == kStages) { s = 0; ph ^= 1; }
-          if (BS) {
+          if (!BS && ok) {
             tc_commit(bar_tfull + 8 * t);
             if (++t == 2) { t = 0; tph ^= 1; }
           }
         }
-        if (!BS && ok) {
-          tc_commit(bar_tfull + 8 * t);
-          if (++t == 2) { t = 0; tph ^= 1; }
-        }
       }
     }
-  }
   } else {
     // ------------------------------ epilogue -----------------------------------
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int q = warp & 3;            // TMEM lane quarter
     const int h = (warp - 4) >> 2;     // column half
     const int row_in_tile = 32 * q + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * q) << 16);
+    const bool has_ids = p.sorted_ids != nullptr;
+    const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
     int t = 0;
     uint32_t tph = 0, xph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+
+    auto fetch_meta = [&](int tile_idx) {
+      RowMeta m;
+      const TileCoord c = tile_coord(tile_idx, num_m, p.tiles_n, p.group_m);
+      const int r = c.m_blk * kBM + row_in_tile;
+      m.expert = p.expert_ids[c.m_blk];
+      m.sid = has_ids ? p.sorted_ids[r] : 0;
+      m.rw = has_rw ? p.sorted_weights[r] : 1.0f;
+      m.a_s = (OPK != OP_F16) ? p.a_scale[r] : 1.0f;
+      return m;
+    };
+
+    int tile = blockIdx.x;
+    RowMeta next{};
+    if (tile < total_tiles) next = fetch_meta(tile);
+    for (; ok && tile < total_tiles; tile += stride) {
       const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
-      const int expert = p.expert_ids[tc.m_blk];
+      const RowMeta cur = next;
+      if (tile + stride < total_tiles) next = fetch_meta(tile + stride);
+      const int expert = cur.expert;
       if (expert < 0 || expert >= p.num_experts) continue;
       const int row = tc.m_blk * kBM + row_in_tile;
-      const int sid = p.sorted_ids ? p.sorted_ids[row] : row;
-      const int token = p.sorted_ids ? (sid & 0xFFFFFF) : 0;
+      const int token = cur.sid & 0xFFFFFF;
       const bool live = token < p.num_tokens;
-      const float rw = (p.mul_routed_weight && p.sorted_weights) ? p.sorted_weights[row] : 1.0f;
+      const float rw = cur.rw;
       int64_t out_row = row;
-      if (p.scatter) out_row = (int64_t)token * p.topk + ((uint32_t)sid >> 24);
+      if (p.scatter) out_row = (int64_t)token * p.topk + ((uint32_t)cur.sid >> 24);
       const int64_t row_off = out_row * p.c_ld;
-      float a_s = 1.0f;
-      if (CHANNEL) a_s = p.a_scale[row];
+      const int64_t brow = (int64_t)expert * p.n;  // first bias / channel-scale entry of the expert
 
-      // column bookkeeping for the four 32-column chunks this thread owns
-      //   STORE : acc cols 128h + 32i            -> out col 256*n_blk + 128h + 32i
-      //   GATED : gate cols 64h + 32i (i<2), up cols 128 + 64h + 32(i-2)
-      //           -> out col 128*n_blk + 64h + 32i
+      // Column ownership of this thread (four 32-column chunks):
+      //   STORE : acc cols 128h + 32i                        -> out col 256*n_blk + 128h + 32i
+      //   GATED : gate cols 64h + 32i (i<2), up cols 128 + 64h + 32(i-2) -> out col 128*n_blk + 64h + 32i
       if (!BS) {
         ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tbase = lane_addr + t * kAccCols;
+        const float a_s = cur.a_s;
         if (!GATED) {
           const int ncols = p.n;
 #pragma unroll 1
@@ -460,16 +515,19 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             const int col0 = tc.n_blk * 256 + 128 * h + 32 * i;
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = acc_to_f32<OPK>(raw[j]);
-              if (CHANNEL) {
-                const int col = min(col0 + j, ncols - 1);
-                x = x * a_s * p.b_scale[(int64_t)expert * p.n + col];
-              }
-              if (p.bias) x += load_bias(p.bias, p.bias_dtype,
-                                         (int64_t)expert * p.n + min(col0 + j, ncols - 1));
-              v[j] = x * rw;
+            for (int j = 0; j < 32; ++j) v[j] = acc_to_f32<OPK>(raw[j]);
+            if (CHANNEL) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] = v[j] * a_s * __ldg(p.b_scale + brow + min(col0 + j, ncols - 1));
             }
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] += load_bias(p.bias, p.bias_dtype, brow + min(col0 + j, ncols - 1));
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= rw;
             if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, v);
           }
         } else {
@@ -480,25 +538,37 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             tmem_ld32(tbase + 128 + 64 * h + 32 * i, ru);
             tmem_ld_wait();
             const int col0 = tc.n_blk * 128 + 64 * h + 32 * i;
-            float v[32];
+            float g[32], u[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              float g = acc_to_f32<OPK>(rg[j]);
-              float u = acc_to_f32<OPK>(ru[j]);
-              const int col = min(col0 + j, p.n_half - 1);
-              if (CHANNEL) {
-                g = g * a_s * p.b_scale[(int64_t)expert * p.n + col];
-                u = u * a_s * p.b_scale[(int64_t)expert * p.n + p.n_half + col];
-              }
-              if (p.bias) {
-                g += load_bias(p.bias, p.bias_dtype, (int64_t)expert * p.n + col);
-                u += load_bias(p.bias, p.bias_dtype, (int64_t)expert * p.n + p.n_half + col);
-              }
-              g = round_mid(g * rw, p.mid_dtype);
-              u = round_mid(u * rw, p.mid_dtype);
-              v[j] = silu_f32(g) * u;
+              g[j] = acc_to_f32<OPK>(rg[j]);
+              u[j] = acc_to_f32<OPK>(ru[j]);
             }
-            if (live) store_row32(p.c, p.c_dtype, row_off, col0, p.n_half, v);
+            if (CHANNEL) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = min(col0 + j, p.n_half - 1);
+                g[j] = g[j] * a_s * __ldg(p.b_scale + brow + col);
+                u[j] = u[j] * a_s * __ldg(p.b_scale + brow + p.n_half + col);
+              }
+            }
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = min(col0 + j, p.n_half - 1);
+                g[j] += load_bias(p.bias, p.bias_dtype, brow + col);
+                u[j] += load_bias(p.bias, p.bias_dtype, brow + p.n_half + col);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float g0 = g[j] * rw, g1 = g[j + 1] * rw, u0 = u[j] * rw, u1 = u[j + 1] * rw;
+              round2(g0, g1, p.mid_dtype);
+              round2(u0, u1, p.mid_dtype);
+              g[j] = silu_fast(g0) * u0;
+              g[j + 1] = silu_fast(g1) * u1;
+            }
+            if (live) store_row32(p.c, p.c_dtype, row_off, col0, p.n_half, g);
           }
         }
         tc_fence_before();
@@ -513,15 +583,19 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[i][j] = 0.f;
         const int nb0 = GATED ? tc.n_blk : min(2 * tc.n_blk + h, p.n / 128 - 1);  // chunks 0,1 (+2,3 if STORE)
-        const int nb1 = GATED ? p.n_half / 128 + tc.n_blk : nb0;      // chunks 2,3 when gated
+        const int nb1 = GATED ? p.n_half / 128 + tc.n_blk : nb0;                  // chunks 2,3 when gated
         const float* bs0 = p.b_scale + ((int64_t)expert * (p.n / 128) + nb0) * p.kb_scale_cols;
         const float* bs1 = p.b_scale + ((int64_t)expert * (p.n / 128) + nb1) * p.kb_scale_cols;
-        float as_next = p.a_scale[row];
+        float as_next = cur.a_s;
+        float b0_next = __ldg(bs0), b1_next = __ldg(bs1);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          const float as_cur = as_next;
-          if (kb + 1 < p.num_kb) as_next = p.a_scale[(int64_t)(kb + 1) * p.a_scale_ld + row];
-          const float s0 = as_cur * bs0[kb];
-          const float s1 = as_cur * bs1[kb];
+          const float s0 = as_next * b0_next;
+          const float s1 = as_next * b1_next;
+          if (kb + 1 < p.num_kb) {
+            as_next = p.a_scale[(int64_t)(kb + 1) * p.a_scale_ld + row];
+            b0_next = __ldg(bs0 + kb + 1);
+            b1_next = __ldg(bs1 + kb + 1);
+          }
           ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
           if (!ok) break;
           tc_fence_after();
@@ -556,34 +630,39 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int col0 = tc.n_blk * 256 + 128 * h + 32 * i;
-            float v[32];
+            if (p.bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = acc[i][j];
-              if (p.bias) x += load_bias(p.bias, p.bias_dtype,
-                                         (int64_t)expert * p.n + min(col0 + j, ncols - 1));
-              v[j] = x * rw;
+              for (int j = 0; j < 32; ++j)
+                acc[i][j] += load_bias(p.bias, p.bias_dtype, brow + min(col0 + j, ncols - 1));
             }
-            if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[i][j] *= rw;
+            if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, acc[i]);
           }
         } else {
           float amax = 0.f;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             const int col0 = tc.n_blk * 128 + 64 * h + 32 * i;
+            if (p.bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float g = acc[i][j], u = acc[2 + i][j];
-              if (p.bias) {
+              for (int j = 0; j < 32; ++j) {
                 const int col = min(col0 + j, p.n_half - 1);
-                g += load_bias(p.bias, p.bias_dtype, (int64_t)expert * p.n + col);
-                u += load_bias(p.bias, p.bias_dtype, (int64_t)expert * p.n + p.n_half + col);
+                acc[i][j] += load_bias(p.bias, p.bias_dtype, brow + col);
+                acc[2 + i][j] += load_bias(p.bias, p.bias_dtype, brow + p.n_half + col);
               }
-              g = round_mid(g * rw, p.mid_dtype);
-              u = round_mid(u * rw, p.mid_dtype);
-              const float y = round_mid(silu_f32(g) * u, p.mid_dtype);
-              acc[i][j] = y;
-              amax = fmaxf(amax, fabsf(y));
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float g0 = acc[i][j] * rw, g1 = acc[i][j + 1] * rw;
+              float u0 = acc[2 + i][j] * rw, u1 = acc[2 + i][j + 1] * rw;
+              round2(g0, g1, p.mid_dtype);
+              round2(u0, u1, p.mid_dtype);
+              float y0 = silu_fast(g0) * u0, y1 = silu_fast(g1) * u1;
+              round2(y0, y1, p.mid_dtype);
+              acc[i][j] = y0;
+              acc[i][j + 1] = y1;
+              amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
             }
           }
           if (EPI == BOLT_EPI_SILU_MUL) {
@@ -602,25 +681,34 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (!ok) break;
             amax = fmaxf(amax, xbuf[(h ^ 1) * 128 + row_in_tile]);
             xph ^= 1;
-            const float dmax = p.c_dtype == BOLT_INT8 ? 127.0f : 448.0f;
-            const float scale = __fdiv_rn(fmaxf(amax, 1.0e-10f), dmax);
+            const bool to_i8 = p.c_dtype == BOLT_INT8;
+            const float scale = __fdiv_rn(fmaxf(amax, 1.0e-10f), to_i8 ? 127.0f : 448.0f);
             const float inv = __frcp_rn(scale);
             if (live) {
               uint8_t* dst = static_cast<uint8_t*>(p.c) + row_off + tc.n_blk * 128 + 64 * h;
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
                 uint32_t w[8];
+                if (!to_i8) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  uint32_t x = 0;
-#pragma unroll
-                  for (int b = 0; b < 4; ++b) {
-                    const float y = acc[i][4 * j + b] * inv;
-                    const uint32_t byte = p.c_dtype == BOLT_INT8 ? (uint32_t)(uint8_t)f32_to_i8(y)
-                                                                 : (uint32_t)f32_to_e4m3(y);
-                    x |= byte << (8 * b);
+                  for (int j = 0; j < 8; ++j) {
+                    const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                        make_float2(acc[i][4 * j] * inv, acc[i][4 * j + 1] * inv), __NV_SATFINITE,
+                        __NV_E4M3);
+                    const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                        make_float2(acc[i][4 * j + 2] * inv, acc[i][4 * j + 3] * inv),
+                        __NV_SATFINITE, __NV_E4M3);
+                    w[j] = lo | (hi << 16);
                   }
-                  w[j] = x;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    uint32_t x = 0;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                      x |= (uint32_t)(uint8_t)f32_to_i8(acc[i][4 * j + b] * inv) << (8 * b);
+                    w[j] = x;
+                  }
                 }
                 *reinterpret_cast<uint4*>(dst + 32 * i) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(dst + 32 * i + 16) = make_uint4(w[4], w[5], w[6], w[7]);
