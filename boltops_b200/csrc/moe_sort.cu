@@ -409,6 +409,54 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
   return run_sort(p, workspace, workspace_bytes, st);
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the CK-format sort.
+//
+// Scratch for the multi-CTA path lives in a fixed array inside the library image
+// instead of a caller-provided workspace.  The array's name is only a host-side
+// stand-in in host code, so its device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and passed to the kernels.
+// ---------------------------------------------------------------------------
+namespace bolt {
+namespace {
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_sort_scratch[kStaticScratchBytes];
+void* g_sort_scratch_ptr[64] = {nullptr};  // per-device address of g_sort_scratch
+}  // namespace
+}  // namespace bolt
+
+extern "C" size_t bolt_moe_sort_static_scratch_bytes(void) { return bolt::kStaticScratchBytes; }
+
+extern "C" int bolt_moe_sort_ck_static(const int32_t* topk_ids, const float* topk_weights,
+                                       const int32_t* local_expert_mask, int num_tokens, int topk,
+                                       int num_experts, int unit_size, int32_t* sorted_ids,
+                                       float* sorted_weights, int32_t* sorted_expert_ids,
+                                       int32_t* tokens_positions_per_expert,
+                                       int32_t* num_valid_ids, void* stream) {
+  using namespace bolt;
+  BOLT_REQUIRE(num_tokens >= 0 && topk > 0 && num_experts > 0, "moe sort (static): bad sizes");
+  const size_t need = workspace_bytes_for((int64_t)num_tokens * topk, num_experts);
+  BOLT_REQUIRE(need <= kStaticScratchBytes,
+               "moe sort (static): %d tokens x top-%d over %d experts needs %zu bytes of scratch, "
+               "the built-in array holds %zu; use bolt_moe_sort_ck with a caller workspace",
+               num_tokens, topk, num_experts, need, kStaticScratchBytes);
+  int dev = 0;
+  BOLT_CUDA(cudaGetDevice(&dev));
+  BOLT_REQUIRE(dev >= 0 && dev < 64, "moe sort (static): device index %d out of range", dev);
+  if (g_sort_scratch_ptr[dev] == nullptr) {
+    // one-time set-up for this device: resolve the array's device address
+    void* ptr = nullptr;
+    BOLT_CUDA(cudaGetSymbolAddress(&ptr, g_sort_scratch));
+    g_sort_scratch_ptr[dev] = ptr;
+  }
+  // No entry of the scratch has to start at zero: the count kernel writes every
+  // per-CTA histogram entry and the scan kernel every offset before it is read.
+  return bolt_moe_sort_ck(topk_ids, topk_weights, local_expert_mask, num_tokens, topk,
+                          num_experts, unit_size, sorted_ids, sorted_weights, sorted_expert_ids,
+                          tokens_positions_per_expert, num_valid_ids, nullptr, 0,
+                          g_sort_scratch_ptr[dev], kStaticScratchBytes, stream);
+}
+
 extern "C" int bolt_moe_align_block_size(const int32_t* topk_ids, int numel, int num_experts,
                                          int block_size, const int32_t* expert_map,
                                          int32_t* sorted_ids, int32_t* expert_ids,

@@ -101,6 +101,40 @@ int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weights,
                      void* moe_buf, size_t moe_buf_bytes, void* workspace,
                      size_t workspace_bytes, void* stream);
 
+/* Allocation-free CK-format sort.  Same outputs as bolt_moe_sort_ck, but the scratch
+ * memory of the multi-block path is a fixed 1 MiB array inside the library image
+ * (bolt_moe_sort_static_scratch_bytes()), so the caller passes inputs and outputs
+ * only and no device memory is allocated by anyone.
+ *
+ * Written for callers that cannot allocate on the device when they reach this call:
+ * a serving engine that gave the whole device heap to its own pools at start-up (a
+ * late cudaMalloc there fails or stalls the device), or a host-language binding that
+ * owns no device allocator at all and can only hand over the buffers it was given.
+ *
+ * It has no counterpart in the reference, whose sorter always receives a workspace
+ * tensor from torch.
+ *
+ * Limits and rules:
+ *  - Requests whose scratch need (bolt_moe_sort_workspace_bytes) exceeds the array are
+ *    refused with BOLT_ERR_INVALID and a message; use bolt_moe_sort_ck then.
+ *  - The first call on each device resolves the array's device address (a
+ *    cudaGetSymbolAddress look-up, with that device current).  Make that first call
+ *    during start-up, before any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's
+ *    contents.  Nothing in it has to be cleared between calls (every entry is written
+ *    before it is read), but two calls that overlap on the GPU -- different streams,
+ *    or different host threads -- race on it; keep calls on one device in stream order.
+ *  - Every GPU that loads the library holds the 1 MiB until the process exits.
+ *  - moe_buf zeroing is not offered here.
+ */
+size_t bolt_moe_sort_static_scratch_bytes(void);
+int bolt_moe_sort_ck_static(const int32_t* topk_ids, const float* topk_weights,
+                            const int32_t* local_expert_mask, int num_tokens, int topk,
+                            int num_experts, int unit_size, int32_t* sorted_ids,
+                            float* sorted_weights, int32_t* sorted_expert_ids,
+                            int32_t* tokens_positions_per_expert, int32_t* num_valid_ids,
+                            void* stream);
+
 /* Token-to-expert sort, vLLM format.
  * Replaces moe_align_block_size (boltops/fused_moe/triton/fused_moe.py:330-439,
  * stages :194-327): sorted_ids = flat route index, whole capacity
