@@ -262,17 +262,22 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (0 = workload default)")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="shrink the expert count (profiling captures of a reduced case)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
     cfg = dict(WORKLOADS[args.workload])
+    if args.experts:
+        cfg["E"] = args.experts
     m = args.tokens or cfg["M"]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     warmup = max(args.warmup, 3)
-    config = dict(workload=f"{args.workload}_M{m}", experts=cfg["E"], topk=cfg["K"],
+    config = dict(workload=f"{args.workload}_M{m}" + (f"_E{cfg['E']}" if args.experts else ""),
+                  experts=cfg["E"], topk=cfg["K"],
                   hidden=cfg["H"], intermediate=cfg["I"], tokens_per_gpu=m,
                   parallelism=f"ep{world}" if world > 1 else "single",
                   l2="inputs larger than L2 (weights stream from HBM every step)")
