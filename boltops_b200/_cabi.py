@@ -81,6 +81,8 @@ _SIGNATURES = {
                                  C.c_void_p]),
     "bolt_moe_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int,
                                C.c_int, C.c_float, C.c_void_p, C.c_void_p]),
+    "bolt_moe_gather_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
+                                      C.c_int, C.c_int, C.c_void_p]),
     "bolt_grouped_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
 }
 

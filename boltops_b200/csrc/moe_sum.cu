@@ -40,6 +40,57 @@ __global__ void __launch_bounds__(256) k_moe_sum(const TIn* __restrict__ in, TOu
   }
 }
 
+// out[m, :] = cast(sum_j f32(src[pos[m, j], :])) over pos[m, j] >= 0, j ascending.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) k_gather_sum(const T* __restrict__ src,
+                                                    const int32_t* __restrict__ pos,
+                                                    T* __restrict__ out, int64_t num_tokens,
+                                                    int slots, int n) {
+  using V = Vec<T, VEC>;
+  const int nvec = n / VEC;
+  const int64_t total = num_tokens * nvec;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = idx / nvec;
+    const int c = (int)(idx - m * nvec) * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    for (int j = 0; j < slots; ++j) {
+      const int r = pos[m * slots + j];
+      if (r < 0) continue;
+      const V v = *reinterpret_cast<const V*>(src + (int64_t)r * n + c);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] += to_f32(v.v[i]);
+    }
+    V o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o.v[i] = from_f32<T>(acc[i]);
+    *reinterpret_cast<V*>(out + m * (int64_t)n + c) = o;
+  }
+}
+
+template <typename T>
+int launch_gather_sum(const void* src, const int32_t* pos, void* out, int64_t num_tokens,
+                      int slots, int n, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(T);
+  const bool vec_ok = (n % VEC == 0) && (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
+                      (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+  const int64_t total = vec_ok ? num_tokens * (n / VEC) : num_tokens * n;
+  if (total == 0) return BOLT_OK;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 32;
+  if (blocks > cap) blocks = cap;
+  if (vec_ok)
+    k_gather_sum<T, VEC><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const T*>(src), pos, static_cast<T*>(out), num_tokens, slots, n);
+  else
+    k_gather_sum<T, 1><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const T*>(src), pos, static_cast<T*>(out), num_tokens, slots, n);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
 template <typename TIn, typename TOut>
 int launch_sum(const void* in, void* out, int64_t num_tokens, int topk, int n, float scale,
                const float* weights, cudaStream_t st) {
@@ -91,5 +142,19 @@ extern "C" int bolt_moe_sum(const void* in, int in_dtype, void* out, int out_dty
     case BOLT_F32:
       return dispatch_out<float>(in, out, out_dtype, num_tokens, topk, n, scale, weights, st);
     default: set_error("moe_sum: unsupported input dtype %d", in_dtype); return BOLT_ERR_INVALID;
+  }
+}
+
+extern "C" int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* out,
+                                   int64_t num_tokens, int slots, int n, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(num_tokens >= 0 && slots > 0 && n > 0, "gather_sum: bad shape");
+  BOLT_REQUIRE(num_tokens == 0 || (pos && out), "gather_sum: null pointer");
+  switch (dtype) {
+    case BOLT_BF16: return launch_gather_sum<__nv_bfloat16>(src, pos, out, num_tokens, slots, n, st);
+    case BOLT_F16: return launch_gather_sum<__half>(src, pos, out, num_tokens, slots, n, st);
+    case BOLT_F32: return launch_gather_sum<float>(src, pos, out, num_tokens, slots, n, st);
+    default: set_error("gather_sum: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
   }
 }

@@ -1,0 +1,113 @@
+"""Expert parallelism for the fused-MoE layer on one NVLink/NVSwitch box.
+
+Experts are sharded contiguously over the ranks of a process group (rank r owns
+experts ``[r*E/R, (r+1)*E/R)``; weights never move); every rank brings its own
+tokens.  One exchange each way:
+
+* dispatch: a token row travels once to every rank that owns at least one of its
+  top-k experts (not once per route), together with its full top-k ids/weights;
+* the owning rank runs the local layer in the reference's masked mode
+  (``expert_map``; boltops/fused_moe/triton/fused_moe.py:1374-1377,1439-1443 in
+  the reference project) and returns ONE partial row per received token;
+* combine: the source rank adds the partial rows of a token in ascending rank
+  order with an fp32 accumulator (``bolt_moe_gather_sum``).
+
+The reference has no collective of its own: it leaves the cross-rank reduction to
+the caller.  The exchange here is ``all_to_all_single`` (NCCL over NVLink on GPUs,
+gloo in the CPU tests); index construction is device-agnostic torch so the same
+code runs under both.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class ExpertParallelMoE:
+    """Dispatch → local experts → combine for one process group.
+
+    ``local_fn(hidden, w1, w2, topk_weights, topk_ids, expert_map=..., global_num_experts=...,
+    **kw)`` computes the masked local layer (default: ``fused_experts``);
+    ``combine_fn(src, pos, out)`` the gather-sum (default: the CUDA kernel).
+    """
+
+    def __init__(self, group, num_experts: int, device,
+                 local_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not shard evenly over {self.world} ranks")
+        self.num_experts = num_experts
+        self.per_rank = num_experts // self.world
+        self.device = torch.device(device)
+        emap = torch.full((num_experts,), -1, dtype=torch.int32)
+        lo = self.rank * self.per_rank
+        emap[lo:lo + self.per_rank] = torch.arange(self.per_rank, dtype=torch.int32)
+        self.expert_map = emap.to(self.device)
+        if local_fn is None:
+            from . import fused_experts as local_fn
+        if combine_fn is None:
+            from .ops import gather_sum as combine_fn
+        self.local_fn = local_fn
+        self.combine_fn = combine_fn
+        self.last_stats = {}
+
+    # -- index construction ---------------------------------------------------------------
+    def plan(self, topk_ids: torch.Tensor):
+        """Which token goes to which rank.  Returns ``(tok_idx [S], send_counts [R],
+        pos [M, R])``: rows to send ordered by (rank, token); ``pos[m, r]`` = row of token
+        m's partial result in the returned buffer, -1 if rank r owns none of its experts."""
+        m = topk_ids.shape[0]
+        dest = torch.div(topk_ids.long(), self.per_rank, rounding_mode="floor")
+        valid = (topk_ids >= 0) & (topk_ids < self.num_experts)
+        hit = torch.zeros((m, self.world + 1), dtype=torch.bool, device=topk_ids.device)
+        hit.scatter_(1, torch.where(valid, dest, torch.full_like(dest, self.world)), True)
+        hit = hit[:, :self.world]
+        rank_idx, tok_idx = hit.t().nonzero(as_tuple=True)          # sorted by rank, then token
+        send_counts = hit.sum(dim=0)
+        pos = torch.full((m, self.world), -1, dtype=torch.int32, device=topk_ids.device)
+        pos[tok_idx, rank_idx] = torch.arange(tok_idx.numel(), dtype=torch.int32,
+                                              device=topk_ids.device)
+        return tok_idx, send_counts, pos
+
+    def _exchange_counts(self, send_counts: torch.Tensor):
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        return send_counts.tolist(), recv_counts.tolist()
+
+    # -- the layer ----------------------------------------------------------------------------
+    def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
+        m, h = hidden_states.shape
+        k = topk_ids.shape[1]
+        tok_idx, send_counts, pos = self.plan(topk_ids)
+        send_split, recv_split = self._exchange_counts(send_counts)
+        n_recv = int(sum(recv_split))
+
+        send_x = hidden_states.index_select(0, tok_idx)
+        meta = torch.cat([topk_ids.to(torch.int32),
+                          topk_weights.to(torch.float32).view(torch.int32)], dim=1)
+        send_meta = meta.index_select(0, tok_idx)
+        recv_x = torch.empty((n_recv, h), dtype=hidden_states.dtype, device=hidden_states.device)
+        recv_meta = torch.empty((n_recv, 2 * k), dtype=torch.int32, device=hidden_states.device)
+        dist.all_to_all_single(recv_x, send_x, recv_split, send_split, group=self.group)
+        dist.all_to_all_single(recv_meta, send_meta, recv_split, send_split, group=self.group)
+
+        r_ids = recv_meta[:, :k].contiguous()
+        r_w = recv_meta[:, k:].contiguous().view(torch.float32)
+        if n_recv:
+            partial = self.local_fn(recv_x, w1_local, w2_local, r_w, r_ids,
+                                    expert_map=self.expert_map,
+                                    global_num_experts=self.num_experts, **kwargs)
+        else:
+            partial = recv_x
+        back = torch.empty_like(send_x)
+        dist.all_to_all_single(back, partial.contiguous(), send_split, recv_split,
+                               group=self.group)
+        out = torch.empty((m, h), dtype=hidden_states.dtype, device=hidden_states.device)
+        self.combine_fn(back, pos, out)
+        self.last_stats = dict(rows_sent=int(sum(send_split)), rows_received=n_recv,
+                               routes=m * k)
+        return out

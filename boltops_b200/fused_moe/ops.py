@@ -217,6 +217,20 @@ def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
     return output_tensor
 
 
+def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[m] = cast(sum_j f32(src[pos[m, j]]))`` over ``pos[m, j] >= 0`` (j ascending)."""
+    _require_cuda(src, pos, out)
+    lib = _cabi.load()
+    m, slots = pos.shape
+    assert pos.dtype == torch.int32 and pos.is_contiguous()
+    assert src.is_contiguous() and out.is_contiguous() and src.dtype == out.dtype
+    with torch.cuda.device(out.device):
+        check(lib.bolt_moe_gather_sum(ptr(src), dtype_code(src.dtype), ptr(pos), ptr(out), m, slots,
+                                      out.shape[1], stream_of(out)))
+    _count()
+    return out
+
+
 # ---------------------------------------------------------------------------
 # grouped GEMM
 # ---------------------------------------------------------------------------

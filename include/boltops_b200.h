@@ -201,6 +201,16 @@ int bolt_act_quant(const void* in, int dtype, int64_t rows, int n_out, int activ
 int bolt_moe_sum(const void* in, int in_dtype, void* out, int out_dtype, int64_t num_tokens,
                  int topk, int n, float scale, const float* weights, void* stream);
 
+/* Expert-parallel combine on the source rank:
+ *   out[m, :] = cast(sum over j in [0, slots) with pos[m, j] >= 0 of f32(src[pos[m, j], :]))
+ * (j ascending, fp32 accumulator).  `src` holds the partial layer outputs that came back
+ * from the ranks owning a token's experts, `pos` [num_tokens, slots] their row numbers.
+ * No counterpart in the reference, which leaves the cross-rank reduction to its caller
+ * (boltops/fused_moe/triton/fused_moe.py:1374-1377 documents the partial-sum contract).
+ */
+int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* out,
+                        int64_t num_tokens, int slots, int n, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Grouped expert GEMM (tcgen05 / TMEM / TMA, persistent).
  * Replaces moe_op.fused_moe + fused_moe_kernel
