@@ -395,6 +395,15 @@ def main():
         layer.STAGE_TIMER = None
         stage_ms = timer.summary()
 
+    ep_stats = None
+    if world > 1:
+        ep.profile = True
+        layer.STAGE_TIMER = layer.StageTimer()
+        step(hidden, wts, ids)
+        ep_stats = dict(ep.last_stats)
+        ep_stats["local_stage_ms"] = layer.STAGE_TIMER.summary()
+        layer.STAGE_TIMER = None
+        ep.profile = False
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -413,6 +422,8 @@ def main():
                          h2d_bytes_per_step=(hidden_h.numel() * 2 + wts_h.numel() * 4
                                              + ids_h.numel() * 4) * world,
                          d2h_bytes_per_step=out_host.numel() * 2 * world))
+    if ep_stats is not None:
+        line["ep_rank0"] = ep_stats
     if stage_ms is not None:
         line["stage_ms"] = stage_ms
         active = int(torch.unique(ids_h).numel())

@@ -60,8 +60,8 @@ _SIGNATURES = {
     "bolt_moe_sort_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "bolt_moe_sort_ck": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                    C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                   C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t,
-                                   C.c_void_p]),
+                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
+                                   C.c_size_t, C.c_void_p]),
     "bolt_moe_sort_static_scratch_bytes": (C.c_size_t, []),
     "bolt_moe_sort_ck_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                           C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -81,8 +81,8 @@ _SIGNATURES = {
                                  C.c_void_p]),
     "bolt_moe_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int,
                                C.c_int, C.c_float, C.c_void_p, C.c_void_p]),
-    "bolt_moe_gather_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
-                                      C.c_int, C.c_int, C.c_void_p]),
+    "bolt_moe_gather_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                      C.c_int64, C.c_int, C.c_int, C.c_float, C.c_void_p]),
     "bolt_grouped_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
 }
 

@@ -33,6 +33,7 @@ struct SortParams {
   int32_t* expert_ids;       // per block
   int32_t* positions;        // [2E] (CK) or nullptr
   int32_t* num_valid;        // [1]
+  int32_t* route_pos;        // [R] sorted position of every route (optional, pre-filled with -1)
   int32_t* cta_counts;       // scratch [G][E]: counts, then exclusive offsets
   int32_t* expert_start;     // scratch [E+1]: padded start per expert, -1 if none
   int R, E, topk, tokens, unit;
@@ -196,6 +197,7 @@ __device__ void cta_scatter(const SortParams& p, int cta, int* warp_cnt, const i
         const int token = r / p.topk, slot = r - token * p.topk;
         p.sorted_ids[dst] = (int32_t)((uint32_t)token | ((uint32_t)slot << 24));
         p.sorted_weights[dst] = p.weights[r];
+        if (p.route_pos != nullptr) p.route_pos[r] = dst;
       }
     }
   }
@@ -375,8 +377,8 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
                                 int num_experts, int unit_size, int32_t* sorted_ids,
                                 float* sorted_weights, int32_t* sorted_expert_ids,
                                 int32_t* tokens_positions_per_expert, int32_t* num_valid_ids,
-                                void* moe_buf, size_t moe_buf_bytes, void* workspace,
-                                size_t workspace_bytes, void* stream) {
+                                int32_t* route_pos, void* moe_buf, size_t moe_buf_bytes,
+                                void* workspace, size_t workspace_bytes, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "moe sort: num_tokens %d out of range",
@@ -396,6 +398,7 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
   p.expert_ids = sorted_expert_ids;
   p.positions = tokens_positions_per_expert;
   p.num_valid = num_valid_ids;
+  p.route_pos = route_pos;
   p.R = num_tokens * topk;
   p.E = num_experts;
   p.topk = topk;
@@ -406,6 +409,8 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
   p.vllm = 0;
   if (moe_buf != nullptr && moe_buf_bytes > 0)
     BOLT_CUDA(cudaMemsetAsync(moe_buf, 0, moe_buf_bytes, st));
+  if (route_pos != nullptr && p.R > 0)   // routes of masked / out-of-range experts stay -1
+    BOLT_CUDA(cudaMemsetAsync(route_pos, 0xFF, (size_t)p.R * sizeof(int32_t), st));
   return run_sort(p, workspace, workspace_bytes, st);
 }
 
@@ -453,7 +458,7 @@ extern "C" int bolt_moe_sort_ck_static(const int32_t* topk_ids, const float* top
   // per-CTA histogram entry and the scan kernel every offset before it is read.
   return bolt_moe_sort_ck(topk_ids, topk_weights, local_expert_mask, num_tokens, topk,
                           num_experts, unit_size, sorted_ids, sorted_weights, sorted_expert_ids,
-                          tokens_positions_per_expert, num_valid_ids, nullptr, 0,
+                          tokens_positions_per_expert, num_valid_ids, nullptr, nullptr, 0,
                           g_sort_scratch_ptr[dev], kStaticScratchBytes, stream);
 }
 

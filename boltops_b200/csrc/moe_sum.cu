@@ -40,13 +40,14 @@ __global__ void __launch_bounds__(256) k_moe_sum(const TIn* __restrict__ in, TOu
   }
 }
 
-// out[m, :] = cast(sum_j f32(src[pos[m, j], :])) over pos[m, j] >= 0, j ascending.
-template <typename T, int VEC>
+// out[m, :] = cast(scale * sum_j f32(src[pos[m, j], :])) over pos[m, j] >= 0, j ascending.
+template <typename T, typename TOut, int VEC>
 __global__ void __launch_bounds__(256) k_gather_sum(const T* __restrict__ src,
                                                     const int32_t* __restrict__ pos,
-                                                    T* __restrict__ out, int64_t num_tokens,
-                                                    int slots, int n) {
+                                                    TOut* __restrict__ out, int64_t num_tokens,
+                                                    int slots, int n, float scale) {
   using V = Vec<T, VEC>;
+  using VO = Vec<TOut, VEC>;
   const int nvec = n / VEC;
   const int64_t total = num_tokens * nvec;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -57,23 +58,23 @@ __global__ void __launch_bounds__(256) k_gather_sum(const T* __restrict__ src,
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
     for (int j = 0; j < slots; ++j) {
-      const int r = pos[m * slots + j];
+      const int r = __ldg(pos + m * slots + j);
       if (r < 0) continue;
       const V v = *reinterpret_cast<const V*>(src + (int64_t)r * n + c);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[i] += to_f32(v.v[i]);
     }
-    V o;
+    VO o;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) o.v[i] = from_f32<T>(acc[i]);
-    *reinterpret_cast<V*>(out + m * (int64_t)n + c) = o;
+    for (int i = 0; i < VEC; ++i) o.v[i] = from_f32<TOut>(acc[i] * scale);
+    *reinterpret_cast<VO*>(out + m * (int64_t)n + c) = o;
   }
 }
 
-template <typename T>
+template <typename T, typename TOut>
 int launch_gather_sum(const void* src, const int32_t* pos, void* out, int64_t num_tokens,
-                      int slots, int n, cudaStream_t st) {
-  constexpr int VEC = 16 / sizeof(T);
+                      int slots, int n, float scale, cudaStream_t st) {
+  constexpr int VEC = 16 / (sizeof(T) > sizeof(TOut) ? sizeof(T) : sizeof(TOut));
   const bool vec_ok = (n % VEC == 0) && (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
                       (reinterpret_cast<uintptr_t>(out) % 16 == 0);
   const int64_t total = vec_ok ? num_tokens * (n / VEC) : num_tokens * n;
@@ -82,13 +83,25 @@ int launch_gather_sum(const void* src, const int32_t* pos, void* out, int64_t nu
   const int64_t cap = (int64_t)sm_count_of_current_device() * 32;
   if (blocks > cap) blocks = cap;
   if (vec_ok)
-    k_gather_sum<T, VEC><<<(unsigned)blocks, 256, 0, st>>>(
-        static_cast<const T*>(src), pos, static_cast<T*>(out), num_tokens, slots, n);
+    k_gather_sum<T, TOut, VEC><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const T*>(src), pos, static_cast<TOut*>(out), num_tokens, slots, n, scale);
   else
-    k_gather_sum<T, 1><<<(unsigned)blocks, 256, 0, st>>>(
-        static_cast<const T*>(src), pos, static_cast<T*>(out), num_tokens, slots, n);
+    k_gather_sum<T, TOut, 1><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const T*>(src), pos, static_cast<TOut*>(out), num_tokens, slots, n, scale);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
+}
+
+template <typename T>
+int dispatch_gather_out(const void* src, const int32_t* pos, void* out, int out_dtype,
+                        int64_t num_tokens, int slots, int n, float scale, cudaStream_t st) {
+  switch (out_dtype) {
+    case BOLT_BF16:
+      return launch_gather_sum<T, __nv_bfloat16>(src, pos, out, num_tokens, slots, n, scale, st);
+    case BOLT_F16: return launch_gather_sum<T, __half>(src, pos, out, num_tokens, slots, n, scale, st);
+    case BOLT_F32: return launch_gather_sum<T, float>(src, pos, out, num_tokens, slots, n, scale, st);
+    default: set_error("gather_sum: unsupported output dtype %d", out_dtype); return BOLT_ERR_INVALID;
+  }
 }
 
 template <typename TIn, typename TOut>
@@ -146,15 +159,19 @@ extern "C" int bolt_moe_sum(const void* in, int in_dtype, void* out, int out_dty
 }
 
 extern "C" int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* out,
-                                   int64_t num_tokens, int slots, int n, void* stream) {
+                                   int out_dtype, int64_t num_tokens, int slots, int n, float scale,
+                                   void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(num_tokens >= 0 && slots > 0 && n > 0, "gather_sum: bad shape");
   BOLT_REQUIRE(num_tokens == 0 || (pos && out), "gather_sum: null pointer");
   switch (dtype) {
-    case BOLT_BF16: return launch_gather_sum<__nv_bfloat16>(src, pos, out, num_tokens, slots, n, st);
-    case BOLT_F16: return launch_gather_sum<__half>(src, pos, out, num_tokens, slots, n, st);
-    case BOLT_F32: return launch_gather_sum<float>(src, pos, out, num_tokens, slots, n, st);
+    case BOLT_BF16:
+      return dispatch_gather_out<__nv_bfloat16>(src, pos, out, out_dtype, num_tokens, slots, n, scale, st);
+    case BOLT_F16:
+      return dispatch_gather_out<__half>(src, pos, out, out_dtype, num_tokens, slots, n, scale, st);
+    case BOLT_F32:
+      return dispatch_gather_out<float>(src, pos, out, out_dtype, num_tokens, slots, n, scale, st);
     default: set_error("gather_sum: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
   }
 }

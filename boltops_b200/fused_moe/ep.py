@@ -54,6 +54,7 @@ class ExpertParallelMoE:
         self.local_fn = local_fn
         self.combine_fn = combine_fn
         self.last_stats = {}
+        self.profile = False      # set True to fill last_stats["ms"] with CUDA-event stage times
 
     # -- index construction ---------------------------------------------------------------
     def plan(self, topk_ids: torch.Tensor):
@@ -82,9 +83,19 @@ class ExpertParallelMoE:
     def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
         m, h = hidden_states.shape
         k = topk_ids.shape[1]
+        marks = []
+
+        def mark(name):
+            if self.profile and hidden_states.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         tok_idx, send_counts, pos = self.plan(topk_ids)
         send_split, recv_split = self._exchange_counts(send_counts)
         n_recv = int(sum(recv_split))
+        mark("plan+counts")
 
         send_x = hidden_states.index_select(0, tok_idx)
         meta = torch.cat([topk_ids.to(torch.int32),
@@ -94,6 +105,7 @@ class ExpertParallelMoE:
         recv_meta = torch.empty((n_recv, 2 * k), dtype=torch.int32, device=hidden_states.device)
         dist.all_to_all_single(recv_x, send_x, recv_split, send_split, group=self.group)
         dist.all_to_all_single(recv_meta, send_meta, recv_split, send_split, group=self.group)
+        mark("dispatch")
 
         r_ids = recv_meta[:, :k].contiguous()
         r_w = recv_meta[:, k:].contiguous().view(torch.float32)
@@ -103,11 +115,18 @@ class ExpertParallelMoE:
                                     global_num_experts=self.num_experts, **kwargs)
         else:
             partial = recv_x
+        mark("experts")
         back = torch.empty_like(send_x)
         dist.all_to_all_single(back, partial.contiguous(), send_split, recv_split,
                                group=self.group)
+        mark("return")
         out = torch.empty((m, h), dtype=hidden_states.dtype, device=hidden_states.device)
         self.combine_fn(back, pos, out)
+        mark("combine")
         self.last_stats = dict(rows_sent=int(sum(send_split)), rows_received=n_recv,
                                routes=m * k)
+        if marks:
+            torch.cuda.synchronize()
+            self.last_stats["ms"] = {b[0]: a[1].elapsed_time(b[1])
+                                     for a, b in zip(marks[:-1], marks[1:])}
         return out

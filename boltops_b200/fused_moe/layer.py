@@ -230,10 +230,13 @@ def fused_experts_impl(
         wts = topk_weights[begin:end]
 
         # ---- sort -----------------------------------------------------------------------
+        route_pos = None
+        if not no_combine:
+            route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
         with _Stage("sort"):
             sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
                 ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
-                alloc_moe_buf=False)
+                alloc_moe_buf=False, route_pos=route_pos)
         cap = sorted_ids.shape[0]
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
@@ -299,24 +302,25 @@ def fused_experts_impl(
             else:
                 act = act_f
 
-        # ---- GEMM2 (router weight in the epilogue, scattered to [m, topk, H]) -------------
-        if expert_map is not None:
-            c3 = torch.zeros((m, topk, model_dim), device=dev, dtype=output_dtype)
-        elif no_combine:
-            c3 = out[begin:end]
-        else:
-            c3 = torch.empty((m, topk, model_dim), device=dev, dtype=output_dtype)
-        with _Stage("gemm2"):
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2,
-                             c=c3.view(m * topk, model_dim), a_scale=act_scale, a_scale_ld=cap,
-                             b_scale=w2_scale_c, bias=b2, scatter=True,
-                             mul_routed_weight=needs_router_weight, **common)
-
-        # ---- combine ----------------------------------------------------------------------------
+        # ---- GEMM2 (router weight in the epilogue) + combine --------------------------------
         if no_combine:
-            if c3.data_ptr() != out[begin:end].data_ptr():
-                out[begin:end].copy_(c3)
+            # the caller wants [m, topk, H]: scatter rows to their route slots
+            c3 = out[begin:end]
+            if expert_map is not None:
+                c3.zero_()
+            with _Stage("gemm2"):
+                ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2,
+                                 c=c3.view(m * topk, model_dim), a_scale=act_scale,
+                                 a_scale_ld=cap, b_scale=w2_scale_c, bias=b2, scatter=True,
+                                 mul_routed_weight=needs_router_weight, **common)
         else:
+            # rows stay in sorted order; the combine gathers each token's routes through the
+            # inverse permutation (k ascending, fp32), so no [m, topk, H] intermediate exists
+            c_sorted = torch.empty((cap, model_dim), device=dev, dtype=output_dtype)
+            with _Stage("gemm2"):
+                ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2, c=c_sorted,
+                                 a_scale=act_scale, a_scale_ld=cap, b_scale=w2_scale_c, bias=b2,
+                                 scatter=False, mul_routed_weight=needs_router_weight, **common)
             with _Stage("combine"):
-                ops.moe_sum(c3, out[begin:end], routed_scaling_factor)
+                ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
     return out

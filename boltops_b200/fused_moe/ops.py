@@ -49,12 +49,14 @@ def ceil_to(x: int, m: int) -> int:
 def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
                    model_dim: Optional[int] = None, moebuf_dtype: Optional[torch.dtype] = None,
                    block_size: int = 32, expert_mask: Optional[torch.Tensor] = None,
-                   alloc_moe_buf: bool = True):
+                   alloc_moe_buf: bool = True, route_pos: Optional[torch.Tensor] = None):
     """CK-format sort.  Returns ``(sorted_ids, sorted_weights, sorted_expert_ids,
     num_valid_ids, tokens_positions_per_expert, moe_buf)`` like the reference.
 
     ``sorted_ids``/``sorted_weights`` are allocated with the capacity rounded up to
     a multiple of ``block_size`` so that the last row tile is always addressable.
+    ``route_pos`` (optional int32 ``[tokens, topk]``) receives every route's position in
+    the sorted order (-1 for routes to masked experts).
     """
     _require_cuda(topk_ids, topk_weights, expert_mask)
     if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape:
@@ -87,10 +89,10 @@ def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_exper
         check(lib.bolt_moe_sort_ck(
             ptr(topk_ids), ptr(topk_weights), ptr(expert_mask), m, topk, num_experts, block_size,
             ptr(sorted_ids), ptr(sorted_weights), ptr(sorted_expert_ids), ptr(positions),
-            ptr(num_valid), ptr(moe_buf),
+            ptr(num_valid), ptr(route_pos), ptr(moe_buf),
             0 if moe_buf is None else moe_buf.numel() * moe_buf.element_size(),
             ptr(ws), ws_bytes, stream_of(topk_ids)))
-    _count(1 if ws_bytes <= 16 else 3)
+    _count((1 if ws_bytes <= 16 else 3) + (1 if route_pos is not None else 0))
     return sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf
 
 
@@ -217,16 +219,18 @@ def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
     return output_tensor
 
 
-def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out[m] = cast(sum_j f32(src[pos[m, j]]))`` over ``pos[m, j] >= 0`` (j ascending)."""
+def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
+               scale: float = 1.0) -> torch.Tensor:
+    """``out[m] = cast(scale * sum_j f32(src[pos[m, j]]))`` over ``pos[m, j] >= 0`` (j ascending)."""
     _require_cuda(src, pos, out)
     lib = _cabi.load()
     m, slots = pos.shape
     assert pos.dtype == torch.int32 and pos.is_contiguous()
-    assert src.is_contiguous() and out.is_contiguous() and src.dtype == out.dtype
+    assert src.is_contiguous() and out.is_contiguous()
     with torch.cuda.device(out.device):
-        check(lib.bolt_moe_gather_sum(ptr(src), dtype_code(src.dtype), ptr(pos), ptr(out), m, slots,
-                                      out.shape[1], stream_of(out)))
+        check(lib.bolt_moe_gather_sum(ptr(src), dtype_code(src.dtype), ptr(pos), ptr(out),
+                                      dtype_code(out.dtype), m, slots, out.shape[1], float(scale),
+                                      stream_of(out)))
     _count()
     return out
 

@@ -88,6 +88,9 @@ int bolt_abi_version(void);
  *   tokens_positions_per_expert: [0,E) route counts, [E,2E) padded start offsets
  *                     (-1 for masked experts)
  *   num_valid_ids[0] = padded total
+ *   route_pos (optional, may be NULL): [num_tokens*topk] position of every route in the
+ *                     sorted order, -1 for routes to masked or out-of-range experts (an
+ *                     addition of this library: the inverse permutation the combine uses)
  *   moe_buf (optional, may be NULL): zero-filled, moe_buf_bytes long.
  *   workspace: bolt_moe_sort_workspace_bytes() bytes, 16-byte aligned; contents
  *   are scratch and need no initialisation.
@@ -98,7 +101,7 @@ int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weights,
                      int num_experts, int unit_size, int32_t* sorted_ids,
                      float* sorted_weights, int32_t* sorted_expert_ids,
                      int32_t* tokens_positions_per_expert, int32_t* num_valid_ids,
-                     void* moe_buf, size_t moe_buf_bytes, void* workspace,
+                     int32_t* route_pos, void* moe_buf, size_t moe_buf_bytes, void* workspace,
                      size_t workspace_bytes, void* stream);
 
 /* Allocation-free CK-format sort.  Same outputs as bolt_moe_sort_ck, but the scratch
@@ -202,14 +205,17 @@ int bolt_moe_sum(const void* in, int in_dtype, void* out, int out_dtype, int64_t
                  int topk, int n, float scale, const float* weights, void* stream);
 
 /* Expert-parallel combine on the source rank:
- *   out[m, :] = cast(sum over j in [0, slots) with pos[m, j] >= 0 of f32(src[pos[m, j], :]))
+ *   out[m, :] = cast(scale * sum over j in [0, slots) with pos[m, j] >= 0 of f32(src[pos[m, j], :]))
  * (j ascending, fp32 accumulator).  `src` holds the partial layer outputs that came back
  * from the ranks owning a token's experts, `pos` [num_tokens, slots] their row numbers.
- * No counterpart in the reference, which leaves the cross-rank reduction to its caller
+ * With pos = route_pos of bolt_moe_sort_ck and src = the down-GEMM output in sorted row
+ * order this is the layer's top-k combine (same summation order as bolt_moe_sum, without the
+ * [M, topk, H] intermediate).  No counterpart in the reference, which scatters to [M, topk, H]
+ * and leaves the cross-rank reduction to its caller
  * (boltops/fused_moe/triton/fused_moe.py:1374-1377 documents the partial-sum contract).
  */
-int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* out,
-                        int64_t num_tokens, int slots, int n, void* stream);
+int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* out, int out_dtype,
+                        int64_t num_tokens, int slots, int n, float scale, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Grouped expert GEMM (tcgen05 / TMEM / TMA, persistent).

@@ -113,3 +113,28 @@ def test_align_block_size(numel_shape, E, block, use_map):
     assert int(n.item()) == total
     assert np.array_equal(s.cpu().numpy(), ref_ids)
     assert np.array_equal(e.cpu().numpy(), ref_e)
+
+
+@pytest.mark.parametrize("tokens,E,topk,use_mask", [(64, 8, 2, False), (3000, 128, 8, True)])
+def test_sort_ck_route_positions_are_the_inverse_permutation(tokens, E, topk, use_mask):
+    from boltops_b200.fused_moe import ops
+    rng = np.random.default_rng(tokens)
+    ids = np.argsort(rng.random((tokens, E)), axis=1)[:, :topk].astype(np.int32)
+    w = rng.random((tokens, topk), dtype=np.float32)
+    mask = None
+    if use_mask:
+        mask = np.ones(E, np.int32)
+        mask[1::4] = 0
+    pos = torch.full((tokens, topk), 12345, dtype=torch.int32, device="cuda")
+    s_ids, _, _, nv, _, _ = ops.moe_sorting_ck(
+        torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E, None, None, 128,
+        None if mask is None else torch.from_numpy(mask).cuda(), route_pos=pos)
+    torch.cuda.synchronize()
+    pos_h, ids_h = pos.cpu().numpy(), s_ids.cpu().numpy().astype(np.int64) & 0xFFFFFFFF
+    on = np.ones(E, bool) if mask is None else mask != 0
+    live = on[ids]
+    assert (pos_h[~live] == -1).all()
+    assert (pos_h[live] >= 0).all() and (pos_h[live] < int(nv.item())).all()
+    tok, slot = np.nonzero(live)
+    packed = ids_h[pos_h[tok, slot]]
+    assert np.array_equal(packed & 0xFFFFFF, tok) and np.array_equal(packed >> 24, slot)
