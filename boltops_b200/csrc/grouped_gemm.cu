@@ -9,11 +9,13 @@
 // never synchronises.
 //
 // Roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4).., column half (w-4)/4).
+// warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4).., accumulator half (w-4)/4).
 //
 // Tile: 128 rows x 256 accumulator columns, K step = 128 bytes (one 128B-swizzle
-// atom: 64 x 16-bit or 128 x 8-bit).  For the gated epilogue the 256 columns are
-// 128 gate columns + the matching 128 up columns (B rows n0.. and N/2+n0..), so
+// atom: 64 x 16-bit or 128 x 8-bit).  The 256 columns are two halves of 128, each
+// drained by its own four epilogue warps.  For the gated epilogue each half holds
+// 64 gate columns and the matching 64 up columns (B rows n0.. and N/2+n0.., loaded
+// as four 64-row TMA boxes stacked in one operand tile), so
 // SiLU(gate)*up, the rounding steps of the unfused reference path and the 1x128
 // group quantisation of the result all happen in registers.
 //
@@ -35,6 +37,7 @@ constexpr int kThreads = 384;
 constexpr int kStages = 4;
 constexpr int kBM = 128;
 constexpr int kAccCols = 256;           // accumulator columns per tile
+constexpr int kHalfCols = 128;          // columns of one independently scheduled half
 constexpr int kTmemCols = 512;          // two accumulator stages
 constexpr int kABytes = kBM * 128;      // 16 KiB
 constexpr int kBBytes = kAccCols * 128; // 32 KiB
@@ -104,7 +107,7 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   return ok;
 }
 
-// Bounded wait: gives up after ~2 s of cycles or as soon as another role aborted.
+// Bounded wait: gives up after ~0.5 s of cycles or as soon as another role aborted.
 // Returns false on expiry (status word and abort flag are set).
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int32_t* status, int code) {
@@ -113,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
     for (int i = 0; i < 256; ++i)
       if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > 4000000000ll) {
+    if (clock64() - t0 > 1000000000ll) {
       *abort_flag = 1;
       if (status != nullptr) atomicCAS(status, 0, code);
       return false;
@@ -286,22 +289,54 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int tiles_n
 // ---------------------------------------------------------------------------
 // Kernel
 // ---------------------------------------------------------------------------
-// fast fp32 helpers for the epilogues (results are rounded to 16 bits right after)
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// ---------------------------------------------------------------------------
+// Epilogue arithmetic helpers
+// ---------------------------------------------------------------------------
+// silu(x) = x / (1 + 2^(-x*log2 e)) with the hardware approximations; the result is
+// rounded to 16 bits right afterwards.
+__device__ __forceinline__ float silu_fast(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
+}
 
-// Round two floats through the 16-bit storage type `dt` (BOLT_F32: unchanged).
-__device__ __forceinline__ void round2(float& a, float& b, int dt) {
-  if (dt == BOLT_BF16) {
+// Round two floats through the 16-bit storage type MID (BOLT_F32: unchanged).
+template <int MID>
+__device__ __forceinline__ void round2(float& a, float& b) {
+  if (MID == BOLT_BF16) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     const uint32_t u = *reinterpret_cast<const uint32_t*>(&h);
     a = __uint_as_float(u << 16);
     b = __uint_as_float(u & 0xFFFF0000u);
-  } else if (dt == BOLT_F16) {
-    const __half2 h = __floats2half2_rn(a, b);
-    const float2 f = __half22float2(h);
+  } else if (MID == BOLT_F16) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
     a = f.x;
     b = f.y;
   }
+}
+
+// y[j] = round(silu(round(g[j])) * round(u[j])) for 32 columns; returns max |y|.
+template <int MID>
+__device__ __forceinline__ float silu_mul32(float (&g)[32], const float (&u)[32]) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float g0 = g[j], g1 = g[j + 1], u0 = u[j], u1 = u[j + 1];
+    round2<MID>(g0, g1);
+    round2<MID>(u0, u1);
+    float y0 = silu_fast(g0) * u0, y1 = silu_fast(g1) * u1;
+    round2<MID>(y0, y1);
+    g[j] = y0;
+    g[j + 1] = y1;
+    amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
+  }
+  return amax;
+}
+__device__ __forceinline__ float silu_mul32_dyn(float (&g)[32], const float (&u)[32], int mid) {
+  if (mid == BOLT_BF16) return silu_mul32<BOLT_BF16>(g, u);
+  if (mid == BOLT_F16) return silu_mul32<BOLT_F16>(g, u);
+  return silu_mul32<BOLT_F32>(g, u);
 }
 
 // Per-row tile metadata, fetched one tile ahead of its use.
@@ -312,6 +347,15 @@ struct RowMeta {
   float a_s;  // channel kinds: row scale; block kinds: scale of K block 0
 };
 
+// ---------------------------------------------------------------------------
+// Kernel
+// ---------------------------------------------------------------------------
+// Accumulator layout.  A tile has 256 accumulator columns (one M128 x N256 MMA per 32-byte
+// K step; TMEM stage t at column 256*t) split into two halves of 128, half h being drained
+// by epilogue warps 4+4h .. 7+4h.
+//   STORE : half h = output columns 256*n_blk + 128*h + [0,128)   (B rows n0 + 128*h ..)
+//   GATED : half h = gate columns [0,64) and up columns [64,128) of output columns
+//           128*n_blk + 64*h + [0,64)  (B rows n0+64h.. and N/2+n0+64h..)
 template <int OPK, bool BS, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -324,17 +368,17 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* ctrl = smem + kStages * kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[S], empty[S], tfull[2], tempty[2], x
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 132);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 260);
   float* amax_x = reinterpret_cast<float*>(ctrl + 1024);  // [2 tile parities][2 halves][128 rows]
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_full = smem_u32(bars);
-  const uint32_t bar_empty = bar_full + 8 * kStages;
-  const uint32_t bar_tfull = bar_empty + 8 * kStages;
-  const uint32_t bar_tempty = bar_tfull + 16;
-  const uint32_t bar_x = bar_tempty + 16;  // absmax exchange between the two column halves
+  const uint32_t bar_full = smem_u32(bars);              // [kStages]
+  const uint32_t bar_empty = bar_full + 8 * kStages;     // [kStages]
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;    // [2 TMEM stages]
+  const uint32_t bar_tempty = bar_tfull + 16;            // [2 TMEM stages]
+  const uint32_t bar_x = bar_tempty + 16;                // absmax exchange between the halves
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -344,11 +388,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(bar_tfull + 8 * t, 1);
-      mbar_init(bar_tempty + 8 * t, 8);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_tfull + 8 * i, 1);
+      mbar_init(bar_tempty + 8 * i, 8);
     }
-    mbar_init(bar_x, 256);
+    mbar_init(bar_x, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -387,8 +431,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (tile + stride < total_tiles)
             expert_next = p.expert_ids[tile_coord(tile + stride, num_m, p.tiles_n, p.group_m).m_blk];
           if (expert < 0 || expert >= p.num_experts) continue;
-          const int n0 = GATED ? tc.n_blk * 128 : tc.n_blk * 256;
-          const int n1 = GATED ? p.n_half + tc.n_blk * 128 : n0 + 128;
+          // B rows of the four 64-row boxes of a stage
+          int brow[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            brow[j] = GATED ? ((j & 1) ? p.n_half : 0) + tc.n_blk * 128 + (j >> 1) * 64
+                            : tc.n_blk * 256 + j * 64;
           for (int kb = 0; kb < p.num_kb; ++kb) {
             ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1);
             if (!ok) break;
@@ -396,8 +444,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             const uint32_t sa = smem_base + s * kStageBytes;
             mbar_expect_tx(full, kStageBytes);
             tma_load_2d(sa, &tma_a, full, kb * kBKElems, tc.m_blk * kBM);
-            tma_load_3d(sa + kABytes, &tma_b, full, kb * kBKElems, n0, expert);
-            tma_load_3d(sa + kABytes + kBBytes / 2, &tma_b, full, kb * kBKElems, n1, expert);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              tma_load_3d(sa + kABytes + j * (kBBytes / 4), &tma_b, full, kb * kBKElems, brow[j],
+                          expert);
             if (++s == kStages) { s = 0; ph ^= 1; }
           }
         }
@@ -417,16 +467,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (tile + stride < total_tiles)
             expert_next = p.expert_ids[tile_coord(tile + stride, num_m, p.tiles_n, p.group_m).m_blk];
           if (expert < 0 || expert >= p.num_experts) continue;
-          if (!BS) {
-            ok = mbar_wait(bar_tempty + 8 * t, tph ^ 1, abort_flag, p.status, 2);
-            if (!ok) break;
-            tc_fence_after();
-          }
           for (int kb = 0; kb < p.num_kb; ++kb) {
-            if (BS) {
+            if (BS || kb == 0) {
               ok = mbar_wait(bar_tempty + 8 * t, tph ^ 1, abort_flag, p.status, 2);
               if (!ok) break;
-              tc_fence_after();
             }
             ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
             if (!ok) break;
@@ -458,18 +502,17 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     // ------------------------------ epilogue -----------------------------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int q = warp & 3;            // TMEM lane quarter
-    const int h = (warp - 4) >> 2;     // column half
+    const int h = (warp - 4) >> 2;     // accumulator half owned by this warp
     const int row_in_tile = 32 * q + lane;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * q) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * q) << 16) + h * kHalfCols;
     const bool has_ids = p.sorted_ids != nullptr;
     const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
     int t = 0;
     uint32_t tph = 0, xph = 0;
     bool ok = true;
 
-    auto fetch_meta = [&](int tile_idx) {
+    auto fetch_meta = [&](const TileCoord& c) {
       RowMeta m;
-      const TileCoord c = tile_coord(tile_idx, num_m, p.tiles_n, p.group_m);
       const int r = c.m_blk * kBM + row_in_tile;
       m.expert = p.expert_ids[c.m_blk];
       m.sid = has_ids ? p.sorted_ids[r] : 0;
@@ -477,16 +520,46 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       m.a_s = (OPK != OP_F16) ? p.a_scale[r] : 1.0f;
       return m;
     };
+    // b-scale row pointers of a tile (block-scaled kinds)
+    auto bscale_ptrs = [&](int expert, int n_blk, const float*& b0, const float*& b1) {
+      const int nb0 = GATED ? n_blk : min(2 * n_blk + h, p.n / 128 - 1);
+      const int nb1 = GATED ? p.n_half / 128 + n_blk : nb0;
+      b0 = p.b_scale + ((int64_t)expert * (p.n / 128) + nb0) * p.kb_scale_cols;
+      b1 = p.b_scale + ((int64_t)expert * (p.n / 128) + nb1) * p.kb_scale_cols;
+    };
 
     int tile = blockIdx.x;
+    TileCoord tc_next{0, 0};
     RowMeta next{};
-    if (tile < total_tiles) next = fetch_meta(tile);
+    float b0_first = 0.f, b1_first = 0.f;  // b scales of K block 0 of the next tile
+    if (tile < total_tiles) {
+      tc_next = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+      next = fetch_meta(tc_next);
+      if (BS && next.expert >= 0 && next.expert < p.num_experts) {
+        const float *b0, *b1;
+        bscale_ptrs(next.expert, tc_next.n_blk, b0, b1);
+        b0_first = __ldg(b0);
+        b1_first = __ldg(b1);
+      }
+    }
     for (; ok && tile < total_tiles; tile += stride) {
-      const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+      const TileCoord tc = tc_next;
       const RowMeta cur = next;
-      if (tile + stride < total_tiles) next = fetch_meta(tile + stride);
+      const bool more = tile + stride < total_tiles;
+      if (more) {
+        tc_next = tile_coord(tile + stride, num_m, p.tiles_n, p.group_m);
+        next = fetch_meta(tc_next);
+      }
       const int expert = cur.expert;
-      if (expert < 0 || expert >= p.num_experts) continue;
+      if (expert < 0 || expert >= p.num_experts) {
+        if (BS && more && next.expert >= 0 && next.expert < p.num_experts) {
+          const float *b0, *b1;
+          bscale_ptrs(next.expert, tc_next.n_blk, b0, b1);
+          b0_first = __ldg(b0);
+          b1_first = __ldg(b1);
+        }
+        continue;
+      }
       const int row = tc.m_blk * kBM + row_in_tile;
       const int token = cur.sid & 0xFFFFFF;
       const bool live = token < p.num_tokens;
@@ -495,10 +568,9 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (p.scatter) out_row = (int64_t)token * p.topk + ((uint32_t)cur.sid >> 24);
       const int64_t row_off = out_row * p.c_ld;
       const int64_t brow = (int64_t)expert * p.n;  // first bias / channel-scale entry of the expert
+      // first output column of this thread's half
+      const int ocol = GATED ? tc.n_blk * 128 + 64 * h : tc.n_blk * 256 + 128 * h;
 
-      // Column ownership of this thread (four 32-column chunks):
-      //   STORE : acc cols 128h + 32i                        -> out col 256*n_blk + 128h + 32i
-      //   GATED : gate cols 64h + 32i (i<2), up cols 128 + 64h + 32(i-2) -> out col 128*n_blk + 64h + 32i
       if (!BS) {
         ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
         if (!ok) break;
@@ -510,9 +582,9 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll 1
           for (int i = 0; i < 4; ++i) {
             uint32_t raw[32];
-            tmem_ld32(tbase + 128 * h + 32 * i, raw);
+            tmem_ld32(tbase + 32 * i, raw);
             tmem_ld_wait();
-            const int col0 = tc.n_blk * 256 + 128 * h + 32 * i;
+            const int col0 = ocol + 32 * i;
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = acc_to_f32<OPK>(raw[j]);
@@ -526,18 +598,20 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               for (int j = 0; j < 32; ++j)
                 v[j] += load_bias(p.bias, p.bias_dtype, brow + min(col0 + j, ncols - 1));
             }
+            if (has_rw) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= rw;
+              for (int j = 0; j < 32; ++j) v[j] *= rw;
+            }
             if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, v);
           }
         } else {
 #pragma unroll 1
           for (int i = 0; i < 2; ++i) {
             uint32_t rg[32], ru[32];
-            tmem_ld32(tbase + 64 * h + 32 * i, rg);
-            tmem_ld32(tbase + 128 + 64 * h + 32 * i, ru);
+            tmem_ld32(tbase + 32 * i, rg);
+            tmem_ld32(tbase + 64 + 32 * i, ru);
             tmem_ld_wait();
-            const int col0 = tc.n_blk * 128 + 64 * h + 32 * i;
+            const int col0 = ocol + 32 * i;
             float g[32], u[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -560,14 +634,14 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                 u[j] += load_bias(p.bias, p.bias_dtype, brow + p.n_half + col);
               }
             }
+            if (has_rw) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              float g0 = g[j] * rw, g1 = g[j + 1] * rw, u0 = u[j] * rw, u1 = u[j + 1] * rw;
-              round2(g0, g1, p.mid_dtype);
-              round2(u0, u1, p.mid_dtype);
-              g[j] = silu_fast(g0) * u0;
-              g[j + 1] = silu_fast(g1) * u1;
+              for (int j = 0; j < 32; ++j) {
+                g[j] *= rw;
+                u[j] *= rw;
+              }
             }
+            silu_mul32_dyn(g, u, p.mid_dtype);
             if (live) store_row32(p.c, p.c_dtype, row_off, col0, p.n_half, g);
           }
         }
@@ -577,24 +651,31 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (++t == 2) { t = 0; tph ^= 1; }
       } else {
         // ---- block-scaled: promote every K block into fp32 registers ----
-        float acc[4][32];
+        // acc[i] = 32 columns as 16 packed pairs; chunks 0,1 scale with b0, chunks 2,3 with b1
+        float2 acc[4][16];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[i][j] = 0.f;
-        const int nb0 = GATED ? tc.n_blk : min(2 * tc.n_blk + h, p.n / 128 - 1);  // chunks 0,1 (+2,3 if STORE)
-        const int nb1 = GATED ? p.n_half / 128 + tc.n_blk : nb0;                  // chunks 2,3 when gated
-        const float* bs0 = p.b_scale + ((int64_t)expert * (p.n / 128) + nb0) * p.kb_scale_cols;
-        const float* bs1 = p.b_scale + ((int64_t)expert * (p.n / 128) + nb1) * p.kb_scale_cols;
+          for (int j = 0; j < 16; ++j) acc[i][j] = make_float2(0.f, 0.f);
+        const float *bs0, *bs1;
+        bscale_ptrs(expert, tc.n_blk, bs0, bs1);
         float as_next = cur.a_s;
-        float b0_next = __ldg(bs0), b1_next = __ldg(bs1);
+        float b0_next = b0_first, b1_next = b1_first;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           const float s0 = as_next * b0_next;
-          const float s1 = as_next * b1_next;
+          const float s1 = GATED ? as_next * b1_next : s0;
           if (kb + 1 < p.num_kb) {
             as_next = p.a_scale[(int64_t)(kb + 1) * p.a_scale_ld + row];
             b0_next = __ldg(bs0 + kb + 1);
             b1_next = __ldg(bs1 + kb + 1);
+          }
+          if (kb == (p.num_kb > 1 ? 1 : 0) && more && next.expert >= 0 &&
+              next.expert < p.num_experts) {
+            // the next tile's expert id has arrived by now: fetch its first b scales early
+            const float *n0, *n1;
+            bscale_ptrs(next.expert, tc_next.n_blk, n0, n1);
+            b0_first = __ldg(n0);
+            b1_first = __ldg(n1);
           }
           ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
           if (!ok) break;
@@ -603,80 +684,89 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int pair = 0; pair < 2; ++pair) {
             uint32_t r0[32], r1[32];
-            const int i0 = 2 * pair, i1 = 2 * pair + 1;
-            const uint32_t c0 = GATED ? (i0 < 2 ? 64 * h + 32 * i0 : 128 + 64 * h + 32 * (i0 - 2))
-                                      : 128 * h + 32 * i0;
-            const uint32_t c1 = GATED ? (i1 < 2 ? 64 * h + 32 * i1 : 128 + 64 * h + 32 * (i1 - 2))
-                                      : 128 * h + 32 * i1;
-            tmem_ld32(tbase + c0, r0);
-            tmem_ld32(tbase + c1, r1);
+            tmem_ld32(tbase + 64 * pair, r0);
+            tmem_ld32(tbase + 64 * pair + 32, r1);
             tmem_ld_wait();
-            const float sc = (GATED && pair == 1) ? s1 : s0;
+            if (pair == 1) {
+              // everything of this stage is in registers: hand it back before the last FMAs
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_tempty + 8 * t);
+            }
+            const float sc = pair == 0 ? s0 : s1;
+            const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              acc[i0][j] = fmaf(acc_to_f32<OPK>(r0[j]), sc, acc[i0][j]);
-              acc[i1][j] = fmaf(acc_to_f32<OPK>(r1[j]), sc, acc[i1][j]);
+            for (int j = 0; j < 16; ++j) {
+              acc[2 * pair][j] = __ffma2_rn(
+                  make_float2(acc_to_f32<OPK>(r0[2 * j]), acc_to_f32<OPK>(r0[2 * j + 1])), sc2,
+                  acc[2 * pair][j]);
+              acc[2 * pair + 1][j] = __ffma2_rn(
+                  make_float2(acc_to_f32<OPK>(r1[2 * j]), acc_to_f32<OPK>(r1[2 * j + 1])), sc2,
+                  acc[2 * pair + 1][j]);
             }
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tempty + 8 * t);
           if (++t == 2) { t = 0; tph ^= 1; }
         }
         if (!ok) break;
         // ---- finalise ----
+        float v[4][32];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            v[i][2 * j] = acc[i][j].x;
+            v[i][2 * j + 1] = acc[i][j].y;
+          }
         if (!GATED) {
           const int ncols = p.n;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const int col0 = tc.n_blk * 256 + 128 * h + 32 * i;
+            const int col0 = ocol + 32 * i;
             if (p.bias) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                acc[i][j] += load_bias(p.bias, p.bias_dtype, brow + min(col0 + j, ncols - 1));
+                v[i][j] += load_bias(p.bias, p.bias_dtype, brow + min(col0 + j, ncols - 1));
             }
+            if (has_rw) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[i][j] *= rw;
-            if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, acc[i]);
+              for (int j = 0; j < 32; ++j) v[i][j] *= rw;
+            }
+            if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, v[i]);
           }
         } else {
+          // chunks 0,1 = gate, chunks 2,3 = up of output columns ocol + [0,64)
           float amax = 0.f;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            const int col0 = tc.n_blk * 128 + 64 * h + 32 * i;
+            const int col0 = ocol + 32 * i;
             if (p.bias) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 const int col = min(col0 + j, p.n_half - 1);
-                acc[i][j] += load_bias(p.bias, p.bias_dtype, brow + col);
-                acc[2 + i][j] += load_bias(p.bias, p.bias_dtype, brow + p.n_half + col);
+                v[i][j] += load_bias(p.bias, p.bias_dtype, brow + col);
+                v[2 + i][j] += load_bias(p.bias, p.bias_dtype, brow + p.n_half + col);
               }
             }
+            if (has_rw) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              float g0 = acc[i][j] * rw, g1 = acc[i][j + 1] * rw;
-              float u0 = acc[2 + i][j] * rw, u1 = acc[2 + i][j + 1] * rw;
-              round2(g0, g1, p.mid_dtype);
-              round2(u0, u1, p.mid_dtype);
-              float y0 = silu_fast(g0) * u0, y1 = silu_fast(g1) * u1;
-              round2(y0, y1, p.mid_dtype);
-              acc[i][j] = y0;
-              acc[i][j + 1] = y1;
-              amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
+              for (int j = 0; j < 32; ++j) {
+                v[i][j] *= rw;
+                v[2 + i][j] *= rw;
+              }
             }
+            amax = fmaxf(amax, silu_mul32_dyn(v[i], v[2 + i], p.mid_dtype));
           }
           if (EPI == BOLT_EPI_SILU_MUL) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const int col0 = tc.n_blk * 128 + 64 * h + 32 * i;
-              if (live) store_row32(p.c, p.c_dtype, row_off, col0, p.n_half, acc[i]);
-            }
+            for (int i = 0; i < 2; ++i)
+              if (live) store_row32(p.c, p.c_dtype, row_off, ocol + 32 * i, p.n_half, v[i]);
           } else {
-            // 1x128 group quantisation: the two column halves exchange their absmax
-            // (double-buffered by tile parity; the barrier wait is bounded like all others)
+            // 1x128 group quantisation: the two halves exchange their absmax through shared
+            // memory (double-buffered by tile parity; the barrier wait is bounded)
             float* xbuf = amax_x + xph * 256;
             xbuf[h * 128 + row_in_tile] = amax;
-            mbar_arrive(bar_x);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_x);
             ok = mbar_wait(bar_x, xph, abort_flag, p.status, 5);
             if (!ok) break;
             amax = fmaxf(amax, xbuf[(h ^ 1) * 128 + row_in_tile]);
@@ -685,7 +775,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             const float scale = __fdiv_rn(fmaxf(amax, 1.0e-10f), to_i8 ? 127.0f : 448.0f);
             const float inv = __frcp_rn(scale);
             if (live) {
-              uint8_t* dst = static_cast<uint8_t*>(p.c) + row_off + tc.n_blk * 128 + 64 * h;
+              uint8_t* dst = static_cast<uint8_t*>(p.c) + row_off + ocol;
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
                 uint32_t w[8];
@@ -693,11 +783,11 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
                   for (int j = 0; j < 8; ++j) {
                     const uint32_t lo = __nv_cvt_float2_to_fp8x2(
-                        make_float2(acc[i][4 * j] * inv, acc[i][4 * j + 1] * inv), __NV_SATFINITE,
+                        make_float2(v[i][4 * j] * inv, v[i][4 * j + 1] * inv), __NV_SATFINITE,
                         __NV_E4M3);
                     const uint32_t hi = __nv_cvt_float2_to_fp8x2(
-                        make_float2(acc[i][4 * j + 2] * inv, acc[i][4 * j + 3] * inv),
-                        __NV_SATFINITE, __NV_E4M3);
+                        make_float2(v[i][4 * j + 2] * inv, v[i][4 * j + 3] * inv), __NV_SATFINITE,
+                        __NV_E4M3);
                     w[j] = lo | (hi << 16);
                   }
                 } else {
@@ -706,7 +796,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                     uint32_t x = 0;
 #pragma unroll
                     for (int b = 0; b < 4; ++b)
-                      x |= (uint32_t)(uint8_t)f32_to_i8(acc[i][4 * j + b] * inv) << (8 * b);
+                      x |= (uint32_t)(uint8_t)f32_to_i8(v[i][4 * j + b] * inv) << (8 * b);
                     w[j] = x;
                   }
                 }
@@ -860,7 +950,7 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   {
     cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
     cuuint64_t strides[2] = {(cuuint64_t)a->k * elem, (cuuint64_t)a->k * elem * a->n};
-    cuuint32_t box[3] = {bk, 128, 1};
+    cuuint32_t box[3] = {bk, 64, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = encode(&mb, dt, 3, const_cast<void*>(a->b), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

@@ -55,6 +55,7 @@ class ExpertParallelMoE:
         self.combine_fn = combine_fn
         self.last_stats = {}
         self.profile = False      # set True to fill last_stats["ms"] with CUDA-event stage times
+        self.quantize_dispatch = True   # w8a8 experts: send 8-bit codes + scales, not 16-bit rows
 
     # -- index construction ---------------------------------------------------------------
     def plan(self, topk_ids: torch.Tensor):
@@ -97,30 +98,54 @@ class ExpertParallelMoE:
         n_recv = int(sum(recv_split))
         mark("plan+counts")
 
-        send_x = hidden_states.index_select(0, tok_idx)
-        meta = torch.cat([topk_ids.to(torch.int32),
-                          topk_weights.to(torch.float32).view(torch.int32)], dim=1)
+        # Quantise before the wire when the experts are w8a8: the rows then cross NVLink as
+        # 8-bit codes + scales instead of 16-bit values, and the local layer takes them as
+        # pre-quantised input (same codes it would have produced itself).
+        out_dtype = kwargs.get("output_dtype") or hidden_states.dtype
+        x, x_scale = hidden_states, None
+        w8a8 = kwargs.get("use_fp8_w8a8") or kwargs.get("use_int8_w8a8")
+        if (self.quantize_dispatch and w8a8 and hidden_states.is_cuda
+                and hidden_states.dtype in (torch.float16, torch.bfloat16)
+                and not kwargs.get("use_ue8m0")):
+            from . import ops
+            qd = torch.float8_e4m3fn if kwargs.get("use_fp8_w8a8") else torch.int8
+            if kwargs.get("per_channel_quant"):
+                x, x_scale = ops.per_token_quant(hidden_states, quant_dtype=qd)
+            elif kwargs.get("block_shape") is not None:
+                x, x_scale = ops.per_block_quant(hidden_states, kwargs["block_shape"][1], qd)
+        dev = hidden_states.device
+        meta_cols = [topk_ids.to(torch.int32), topk_weights.to(torch.float32).view(torch.int32)]
+        if x_scale is not None:
+            meta_cols.append(x_scale.reshape(m, -1).view(torch.int32))
+        meta = torch.cat(meta_cols, dim=1)
         send_meta = meta.index_select(0, tok_idx)
-        recv_x = torch.empty((n_recv, h), dtype=hidden_states.dtype, device=hidden_states.device)
-        recv_meta = torch.empty((n_recv, 2 * k), dtype=torch.int32, device=hidden_states.device)
+        send_x = x.view(torch.uint8).index_select(0, tok_idx) if x_scale is not None \
+            else x.index_select(0, tok_idx)
+        recv_x = torch.empty((n_recv, send_x.shape[1]), dtype=send_x.dtype, device=dev)
+        recv_meta = torch.empty((n_recv, meta.shape[1]), dtype=torch.int32, device=dev)
         dist.all_to_all_single(recv_x, send_x, recv_split, send_split, group=self.group)
         dist.all_to_all_single(recv_meta, send_meta, recv_split, send_split, group=self.group)
         mark("dispatch")
 
         r_ids = recv_meta[:, :k].contiguous()
-        r_w = recv_meta[:, k:].contiguous().view(torch.float32)
+        r_w = recv_meta[:, k:2 * k].contiguous().view(torch.float32)
+        local_kwargs = dict(kwargs)
+        if x_scale is not None:
+            recv_x = recv_x.view(x.dtype)
+            local_kwargs["a1_scale"] = recv_meta[:, 2 * k:].contiguous().view(torch.float32)
+            local_kwargs["output_dtype"] = out_dtype
         if n_recv:
             partial = self.local_fn(recv_x, w1_local, w2_local, r_w, r_ids,
                                     expert_map=self.expert_map,
-                                    global_num_experts=self.num_experts, **kwargs)
+                                    global_num_experts=self.num_experts, **local_kwargs)
         else:
-            partial = recv_x
+            partial = torch.empty((0, h), dtype=out_dtype, device=dev)
         mark("experts")
-        back = torch.empty_like(send_x)
+        back = torch.empty((tok_idx.numel(), h), dtype=out_dtype, device=dev)
         dist.all_to_all_single(back, partial.contiguous(), send_split, recv_split,
                                group=self.group)
         mark("return")
-        out = torch.empty((m, h), dtype=hidden_states.dtype, device=hidden_states.device)
+        out = torch.empty((m, h), dtype=out_dtype, device=dev)
         self.combine_fn(back, pos, out)
         mark("combine")
         self.last_stats = dict(rows_sent=int(sum(send_split)), rows_received=n_recv,
