@@ -42,7 +42,8 @@ constexpr int kTmemCols = 512;          // two accumulator stages
 constexpr int kABytes = kBM * 128;      // 16 KiB
 constexpr int kBBytes = kAccCols * 128; // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kCtrlBytes = 4096;
+constexpr int kScaleSlots = 8;           // ring of per-K-block activation-scale rows (512 B each)
+constexpr int kCtrlBytes = 4096 + kScaleSlots * 512;
 constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;  // +1024 alignment slack
 
 enum OpKind { OP_F16 = 0, OP_F8 = 1, OP_I8 = 2 };
@@ -143,6 +144,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
       "{%3, %4, %5}], [%2];" ::"r"(dst),
       "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (16-byte granularity).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
 
@@ -344,7 +354,7 @@ struct RowMeta {
   int expert;
   int sid;
   float rw;
-  float a_s;  // channel kinds: row scale; block kinds: scale of K block 0
+  float a_s;  // channel kinds: row scale
 };
 
 // ---------------------------------------------------------------------------
@@ -372,6 +382,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 260);
   float* amax_x = reinterpret_cast<float*>(ctrl + 1024);  // [2 tile parities][2 halves][128 rows]
+  float* as_ring = reinterpret_cast<float*>(ctrl + 4096); // [kScaleSlots][128 rows]
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars);              // [kStages]
@@ -419,7 +430,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       // ------------------------------ TMA producer ------------------------------
       if (lane == 0) {
         int s = 0;
-        uint32_t ph = 0;
+        uint32_t ph = 0, kbi = 0;
         bool ok = true;
         int tile = blockIdx.x;
         int expert_next = -1;
@@ -442,7 +453,15 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (!ok) break;
             const uint32_t full = bar_full + 8 * s;
             const uint32_t sa = smem_base + s * kStageBytes;
-            mbar_expect_tx(full, kStageBytes);
+            mbar_expect_tx(full, kStageBytes + (BS ? 512 : 0));
+            if (BS) {
+              // activation scales of this K block for the tile's 128 rows.  Ring slot reuse is
+              // safe without a barrier of its own: this copy is issued at most kStages K blocks
+              // ahead of the MMA and the MMA runs at most 2 ahead of the epilogue that reads it.
+              bulk_load(smem_u32(as_ring) + (kbi % kScaleSlots) * 512,
+                        p.a_scale + (int64_t)kb * p.a_scale_ld + tc.m_blk * kBM, 512, full);
+              ++kbi;
+            }
             tma_load_2d(sa, &tma_a, full, kb * kBKElems, tc.m_blk * kBM);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -508,7 +527,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const bool has_ids = p.sorted_ids != nullptr;
     const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
     int t = 0;
-    uint32_t tph = 0, xph = 0;
+    uint32_t tph = 0, xph = 0, kbi = 0;
     bool ok = true;
 
     auto fetch_meta = [&](const TileCoord& c) {
@@ -517,7 +536,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       m.expert = p.expert_ids[c.m_blk];
       m.sid = has_ids ? p.sorted_ids[r] : 0;
       m.rw = has_rw ? p.sorted_weights[r] : 1.0f;
-      m.a_s = (OPK != OP_F16) ? p.a_scale[r] : 1.0f;
+      m.a_s = CHANNEL ? p.a_scale[r] : 1.0f;
       return m;
     };
     // b-scale row pointers of a tile (block-scaled kinds)
@@ -659,13 +678,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int j = 0; j < 16; ++j) acc[i][j] = make_float2(0.f, 0.f);
         const float *bs0, *bs1;
         bscale_ptrs(expert, tc.n_blk, bs0, bs1);
-        float as_next = cur.a_s;
         float b0_next = b0_first, b1_next = b1_first;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          const float s0 = as_next * b0_next;
-          const float s1 = GATED ? as_next * b1_next : s0;
+          const float b0_cur = b0_next, b1_cur = b1_next;
           if (kb + 1 < p.num_kb) {
-            as_next = p.a_scale[(int64_t)(kb + 1) * p.a_scale_ld + row];
             b0_next = __ldg(bs0 + kb + 1);
             b1_next = __ldg(bs1 + kb + 1);
           }
@@ -680,6 +696,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
           if (!ok) break;
           tc_fence_after();
+          // the scale row landed (same transaction barrier as the operand tiles) before the MMA
+          // whose completion was just observed was even issued
+          const float a_s = as_ring[(kbi % kScaleSlots) * 128 + row_in_tile];
+          ++kbi;
+          const float s0 = a_s * b0_cur;
+          const float s1 = GATED ? a_s * b1_cur : s0;
           const uint32_t tbase = lane_addr + t * kAccCols;
 #pragma unroll
           for (int pair = 0; pair < 2; ++pair) {
