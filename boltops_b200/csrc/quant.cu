@@ -153,6 +153,50 @@ __global__ void __launch_bounds__(256) k_quant_row_vec(const TIn* __restrict__ x
   if (threadIdx.x == 0) scales[g] = scale;
 }
 
+// ---- one warp per group (mid-sized rows: the row lives in the warp's registers) -----
+template <typename TIn, int QT, bool POW2, int NV>
+__global__ void __launch_bounds__(256) k_quant_row_warp(const TIn* __restrict__ x,
+                                                        typename QTraits<QT>::type* __restrict__ q,
+                                                        float* __restrict__ scales,
+                                                        int64_t num_groups, int group) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  using VIn = Vec<TIn, VEC>;
+  using VOut = Vec<typename QTraits<QT>::type, VEC>;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int nvec = group / VEC;
+  for (int64_t g = warp0; g < num_groups; g += nwarps) {
+    const VIn* xr = reinterpret_cast<const VIn*>(x + g * (int64_t)group);
+    VOut* qr = reinterpret_cast<VOut*>(q + g * (int64_t)group);
+    VIn cache[NV];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        cache[j] = xr[i];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(to_f32(cache[j].v[e])));
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float scale, inv;
+    scale_from_amax<QT, POW2>(amax, scale, inv);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        VOut o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o.v[e] = quant_one<QT, POW2>(to_f32(cache[j].v[e]), inv);
+        qr[i] = o;
+      }
+    }
+    if (lane == 0) scales[g] = scale;
+  }
+}
+
 template <typename TIn, int QT, bool POW2>
 int launch_quant(const void* x, int64_t rows, int cols, int group, void* q, float* scales,
                  cudaStream_t st) {
@@ -170,6 +214,13 @@ int launch_quant(const void* x, int64_t rows, int cols, int group, void* q, floa
     const int64_t blocks = (threads + 255) / 256;
     k_quant_group<TIn, QT, POW2><<<(unsigned)blocks, 256, 0, st>>>(
         static_cast<const TIn*>(x), static_cast<QTy*>(q), scales, num_groups, tpg);
+  } else if (aligned && group / VEC <= 8 * 32) {
+    // up to 8 vectors per lane: one warp per row, rows strided over a capped grid
+    int64_t blocks = (num_groups + 7) / 8;
+    const int64_t cap = (int64_t)sm_count_of_current_device() * 32;
+    if (blocks > cap) blocks = cap;
+    k_quant_row_warp<TIn, QT, POW2, 8><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const TIn*>(x), static_cast<QTy*>(q), scales, num_groups, group);
   } else if (aligned) {
     k_quant_row_vec<TIn, QT, POW2, 4><<<(unsigned)num_groups, 256, 0, st>>>(
         static_cast<const TIn*>(x), static_cast<QTy*>(q), scales, group);
