@@ -45,7 +45,11 @@ DEFAULT_WORKLOAD = "deepseek_v3_fp8_block"
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), keyed by
 # (workload, tokens); None when no capture exists for that case.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/grouped_gemm_fp8_block_dsv3_E64_M1024.md: 2.196 GB per launch at E=64 (same rows per
+    # expert), scaled by 256/64 -- DRAM traffic of this kernel is proportional to the expert count
+    ("deepseek_v3_fp8_block", 4096): 8.78e9,
+}
 
 
 def load_peaks():
