@@ -18,7 +18,8 @@ BOLT_OK = 0
 # enum bolt_dtype
 BF16, F16, F32, FP8_E4M3, INT8 = 0, 1, 2, 3, 4
 # enum bolt_activation
-ACT_SILU, ACT_GELU, ACT_GELU_TANH, ACT_RELU2, ACT_SWIGLU_OAI, ACT_SWIGLU_STEP, ACT_SILU_CLAMP = range(7)
+(ACT_SILU, ACT_GELU, ACT_GELU_TANH, ACT_RELU2, ACT_SWIGLU_OAI, ACT_SWIGLU_STEP, ACT_SILU_CLAMP,
+ ACT_SWIGLU_OAI_INTERLEAVED, ACT_SITU) = range(9)
 # enum bolt_gemm_kind
 GEMM_BF16, GEMM_F16, GEMM_FP8_BLOCK, GEMM_INT8_CHANNEL, GEMM_FP8_CHANNEL, GEMM_INT8_BLOCK = range(6)
 # enum bolt_gemm_epilogue
@@ -69,6 +70,8 @@ _SIGNATURES = {
     "bolt_moe_align_block_size": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_size_t, C.c_void_p]),
+    "bolt_fused_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
+                                  C.c_void_p, C.c_void_p, C.c_void_p]),
     "bolt_quant_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "bolt_gather_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,

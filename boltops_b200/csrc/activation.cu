@@ -41,6 +41,18 @@ __device__ __forceinline__ float act_pair(const ActParams& p, float g, float u) 
       a = silu_f32(fminf(g, p.limit));
       u = fminf(fmaxf(u, -p.limit), p.limit);
       break;
+    case BOLT_ACT_SWIGLU_OAI_INTERLEAVED: {
+      const float gc = fminf(g, p.limit);
+      const float uc = fminf(fmaxf(u, -p.limit), p.limit);
+      return gc * (1.0f / (1.0f + expf(-p.alpha * gc))) * (uc + 1.0f);
+    }
+    case BOLT_ACT_SITU: {
+      // tanh(x) = 2*sigmoid(2x) - 1, the reference's form
+      const float tg = 2.0f / (1.0f + expf(-2.0f * (g / p.alpha))) - 1.0f;
+      a = p.alpha * tg * (1.0f / (1.0f + expf(-g)));
+      if (p.limit > 0.f) u = p.limit * (2.0f / (1.0f + expf(-2.0f * (u / p.limit))) - 1.0f);
+      break;
+    }
     default: a = g; break;
   }
   return p.gated ? a * u : a;
@@ -71,10 +83,37 @@ __global__ void __launch_bounds__(256) k_activation(const T* __restrict__ in, T*
   }
 }
 
+// interleaved gate/up layout: out[r, c] = act(in[r, 2c], in[r, 2c+1])
+template <typename T>
+__global__ void __launch_bounds__(256) k_activation_interleaved(const T* __restrict__ in,
+                                                                T* __restrict__ out, int64_t rows,
+                                                                int n_out, ActParams p,
+                                                                const int32_t* __restrict__ rows_dev) {
+  if (rows_dev != nullptr) rows = min(rows, (int64_t)*rows_dev);
+  const int64_t total = rows * n_out;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const float g = to_f32(in[2 * idx]);
+    const float u = to_f32(in[2 * idx + 1]);
+    out[idx] = from_f32<T>(act_pair(p, g, u));
+  }
+}
+
 template <typename T>
 int launch_activation(const void* in, void* out, int64_t rows, int n_out, ActParams p,
                       const int32_t* rows_dev, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(T);
+  if (p.kind == BOLT_ACT_SWIGLU_OAI_INTERLEAVED) {
+    const int64_t n = rows * n_out;
+    if (n == 0) return BOLT_OK;
+    int64_t nb = (n + 255) / 256;
+    const int64_t nb_cap = (int64_t)sm_count_of_current_device() * 32;
+    if (nb > nb_cap) nb = nb_cap;
+    k_activation_interleaved<T><<<(unsigned)nb, 256, 0, st>>>(
+        static_cast<const T*>(in), static_cast<T*>(out), rows, n_out, p, rows_dev);
+    BOLT_LAUNCH_CHECK();
+    return BOLT_OK;
+  }
   const bool vec_ok = (n_out % VEC == 0) && (reinterpret_cast<uintptr_t>(in) % 16 == 0) &&
                       (reinterpret_cast<uintptr_t>(out) % 16 == 0);
   const int64_t total = vec_ok ? rows * (n_out / VEC) : rows * n_out;
@@ -160,10 +199,11 @@ int launch_act_quant(const void* in, int64_t rows, int n_out, ActParams p, int q
 }
 
 int check_act(int activation, int gated) {
-  BOLT_REQUIRE(activation >= BOLT_ACT_SILU && activation <= BOLT_ACT_SILU_CLAMP,
+  BOLT_REQUIRE(activation >= BOLT_ACT_SILU && activation <= BOLT_ACT_SITU,
                "activation: unknown kind %d", activation);
   const bool needs_gate = activation == BOLT_ACT_SWIGLU_OAI || activation == BOLT_ACT_SWIGLU_STEP ||
-                          activation == BOLT_ACT_SILU_CLAMP;
+                          activation == BOLT_ACT_SILU_CLAMP ||
+                          activation == BOLT_ACT_SWIGLU_OAI_INTERLEAVED || activation == BOLT_ACT_SITU;
   BOLT_REQUIRE(!needs_gate || gated, "activation: kind %d requires gated mode", activation);
   BOLT_REQUIRE(!(activation == BOLT_ACT_RELU2 && gated), "activation: relu2 is not gated");
   return BOLT_OK;

@@ -89,10 +89,13 @@ def resolve_kernel(activation: str, is_gated: bool, gemm1_alpha: Optional[float]
                 raise ValueError("gemm1_alpha/gemm1_limit are not supported for SITU")
             if activation_situ_beta is None:
                 raise ValueError("SITU requires activation_situ_beta")
-            raise NotImplementedError("activation 'situ' is not built in boltops_b200 yet")
+            lin = 0.0 if activation_situ_linear_beta is None else float(activation_situ_linear_beta)
+            return _cabi.ACT_SITU, float(activation_situ_beta), lin
         if activation == "swigluoai":
-            raise NotImplementedError(
-                "activation 'swigluoai' (interleaved gate/up layout) is not built in boltops_b200 yet")
+            # interleaved [g0, u0, g1, u1, ...] layout, defaults alpha 1.702 / limit 7
+            alpha = 1.702 if gemm1_alpha is None else float(gemm1_alpha)
+            limit = 7.0 if gemm1_limit is None else float(gemm1_limit)
+            return _cabi.ACT_SWIGLU_OAI_INTERLEAVED, alpha, limit
         raise ValueError(f"Unsupported gated activation: {activation}")
     if activation in ("silu", "silu_no_mul"):
         return _cabi.ACT_SILU, 0.0, 0.0

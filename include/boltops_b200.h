@@ -50,7 +50,10 @@ enum bolt_activation {
   BOLT_ACT_RELU2 = 3,
   BOLT_ACT_SWIGLU_OAI = 4,   /* gate'*sigmoid(alpha*gate')*(up'+1), chunked layout */
   BOLT_ACT_SWIGLU_STEP = 5,  /* min(silu(gate),limit)*clamp(up,+-limit)            */
-  BOLT_ACT_SILU_CLAMP = 6    /* silu(min(gate,limit))*clamp(up,+-limit)            */
+  BOLT_ACT_SILU_CLAMP = 6,   /* silu(min(gate,limit))*clamp(up,+-limit)            */
+  BOLT_ACT_SWIGLU_OAI_INTERLEAVED = 7, /* as SWIGLU_OAI on the [g0,u0,g1,u1,...] layout   */
+  BOLT_ACT_SITU = 8          /* beta*tanh(gate/beta)*sigmoid(gate) * up', with alpha = beta and
+                                up' = limit*tanh(up/limit) when limit > 0, else up  */
 };
 
 /* grouped-GEMM operand kinds */
@@ -149,6 +152,16 @@ int bolt_moe_align_block_size(const int32_t* topk_ids, int numel, int num_expert
                               int32_t* sorted_ids, int32_t* expert_ids,
                               int32_t* num_tokens_post_pad, void* workspace,
                               size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Router front-end (the step right before the sort).  Replaces fused_topk
+ * (boltops/tools/fused_moe_triton_tune/routing.py:10-35): scores = softmax (or sigmoid)
+ * of the fp32 logits, top-k, optional renormalisation; fp32 weights, int32 ids.
+ * gating [num_tokens, num_experts] bf16/f16/f32, num_experts <= 1024, topk <= 32.
+ */
+int bolt_fused_topk(const void* gating, int dtype, int64_t num_tokens, int num_experts, int topk,
+                    int renormalize, int is_softmax, float* topk_weights, int32_t* topk_ids,
+                    void* stream);
 
 /* ---------------------------------------------------------------------------
  * Dynamic activation quantisation.

@@ -226,11 +226,23 @@ def group_quant_fp8_power2(x: torch.Tensor, group: Optional[int] = None):
 # kernel math boltops/fused_moe/triton/moe_activation.py:70-128)
 # ---------------------------------------------------------------------------
 def activation_ref(x: torch.Tensor, activation: str = "silu", is_gated: bool = True,
-                   limit: Optional[float] = None, alpha: Optional[float] = None):
-    """fp32 math on the [gate | up] chunked layout; caller casts."""
+                   limit: Optional[float] = None, alpha: Optional[float] = None,
+                   situ_beta: Optional[float] = None, situ_linear_beta: Optional[float] = None,
+                   interleaved: bool = False):
+    """fp32 math on the [gate | up] chunked layout (``interleaved``: [g0,u0,g1,u1,...], the
+    layout of the reference's swigluoai kernel, moe_activation.py:869-925); caller casts."""
     xf = x.float()
     if is_gated:
-        gate, up = xf.chunk(2, dim=-1)
+        if interleaved:
+            gate, up = xf[..., 0::2], xf[..., 1::2]
+        else:
+            gate, up = xf.chunk(2, dim=-1)
+        if activation == "situ":
+            # moe_activation.py:958-1010 / tools common.py:139-150
+            act = situ_beta * torch.tanh(gate / situ_beta) * torch.sigmoid(gate)
+            if situ_linear_beta is not None:
+                up = situ_linear_beta * torch.tanh(up / situ_linear_beta)
+            return act * up
         if activation == "silu":
             if limit is not None and alpha is None:
                 gate = gate.clamp(max=limit)

@@ -140,3 +140,39 @@ def test_moe_sum_topk8_random():
     out32 = torch.empty(100, 2048, dtype=torch.float32, device="cuda")
     ops.moe_sum(x.cuda(), out32, 1.0)
     assert torch.equal(out32.cpu(), O.moe_sum(x, 1.0, out_dtype=torch.float32))
+
+
+def test_moe_activation_swigluoai_interleaved_and_situ():
+    from boltops_b200.fused_moe import moe_activation
+    torch.manual_seed(21)
+    x = (torch.randn(33, 512) * 3).bfloat16()
+    out = torch.empty(33, 256, dtype=torch.bfloat16, device="cuda")
+    moe_activation(out, x.cuda(), "swigluoai")
+    ref = O.activation_ref(x, "swigluoai", True, interleaved=True).bfloat16()
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    moe_activation(out, x.cuda(), "swigluoai", gemm1_alpha=1.2, gemm1_limit=3.0)
+    ref = O.activation_ref(x, "swigluoai", True, limit=3.0, alpha=1.2, interleaved=True).bfloat16()
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    for lin in (None, 5.0):
+        moe_activation(out, x.cuda(), "situ", activation_situ_beta=6.0,
+                       activation_situ_linear_beta=lin)
+        ref = O.activation_ref(x, "situ", True, situ_beta=6.0, situ_linear_beta=lin).bfloat16()
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    with pytest.raises(ValueError):
+        moe_activation(out, x.cuda(), "situ")
+
+
+@pytest.mark.parametrize("m,e,k,softmax,renorm,dtype", [
+    (13, 16, 4, True, True, torch.float32), (4096, 256, 8, True, True, torch.float32),
+    (300, 128, 8, True, False, torch.bfloat16), (77, 8, 2, False, True, torch.float32),
+    (1, 384, 6, True, True, torch.float16),
+])
+def test_fused_topk(m, e, k, softmax, renorm, dtype):
+    from boltops_b200.fused_moe.routing import fused_topk
+    g = torch.Generator().manual_seed(m + e)
+    logits = torch.randn(m, e, generator=g).to(dtype)
+    w_ref, i_ref = O.fused_topk(logits, k, renorm, softmax)
+    w, i = fused_topk(torch.zeros(m, 4), logits.cuda(), k, renorm, is_softmax=softmax)
+    assert i.dtype == torch.int32 and w.dtype == torch.float32
+    assert torch.equal(i.cpu(), i_ref)
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=1e-5, atol=1e-7)
