@@ -174,5 +174,12 @@ def test_fused_topk(m, e, k, softmax, renorm, dtype):
     w_ref, i_ref = O.fused_topk(logits, k, renorm, softmax)
     w, i = fused_topk(torch.zeros(m, 4), logits.cuda(), k, renorm, is_softmax=softmax)
     assert i.dtype == torch.int32 and w.dtype == torch.float32
-    assert torch.equal(i.cpu(), i_ref)
     torch.testing.assert_close(w.cpu(), w_ref, rtol=1e-5, atol=1e-7)
+    # ids: identical unless logits tie (16-bit logits tie often; either expert is a valid pick):
+    # the chosen experts must carry exactly the reference's scores, without repeats
+    scores = torch.softmax(logits.float(), -1) if softmax else logits.float().sigmoid()
+    picked = scores.gather(1, i.cpu().long())
+    torch.testing.assert_close(picked, scores.gather(1, i_ref.long()), rtol=1e-6, atol=0)
+    assert all(len(set(row)) == k for row in i.cpu().tolist())
+    if dtype == torch.float32:
+        assert torch.equal(i.cpu(), i_ref)
