@@ -270,6 +270,8 @@ def main():
                     help="shrink the expert count (profiling captures of a reduced case)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="1 GPU only: replay the layer from a CUDA graph in the device-resident timing")
     args = ap.parse_args()
 
     cfg = dict(WORKLOADS[args.workload])
@@ -370,8 +372,19 @@ def main():
     if rank == 0:
         sampler.start()
     launches0 = ops.launch_count()
-    ms = timed(lambda: step(hidden, wts, ids), args.steps)
-    launches = (ops.launch_count() - launches0) // max(args.steps, 1)
+    if args.graph and world == 1:
+        step(hidden, wts, ids)
+        launches = ops.launch_count() - launches0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = step(hidden, wts, ids)
+        for _ in range(3):
+            graph.replay()
+        ms = timed(graph.replay, args.steps)
+        config["cuda_graph"] = True
+    else:
+        ms = timed(lambda: step(hidden, wts, ids), args.steps)
+        launches = (ops.launch_count() - launches0) // max(args.steps, 1)
 
     # ---- end to end through the public API with host buffers ----------------------------
     def e2e_step():

@@ -220,3 +220,30 @@ def test_layer_argument_errors():
         fused_experts(hid, w1, w2, wts[:, :0], ids)
     with pytest.raises(NotImplementedError):
         fused_experts(hid, w1, w2, wts, ids, use_int4_w4a16=True)
+
+
+def test_layer_is_cuda_graph_capturable():
+    """No step of the layer synchronises the host, so it captures into a CUDA graph
+    (the reference benchmarks its layer under graphs, test/fused_moe/test_fused_moe.py:1317-1324)."""
+    from boltops_b200.fused_moe import fused_experts
+    hidden, w1q, w2q, w1s, w2s, wts, ids = _fp8_block_case(64, 8, 2, 512, 256, 21)
+    d = _dev(hidden, w1q, w2q, wts, ids)
+    kw = dict(use_fp8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128])
+    eager = _finish(fused_experts(*d, **kw))
+    static_in = d[0].clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fused_experts(static_in, d[1], d[2], d[3], d[4], **kw)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = fused_experts(static_in, d[1], d[2], d[3], d[4], **kw)
+    graph.replay()
+    assert torch.equal(_finish(static_out), eager)
+    static_in.copy_(d[0] * 0.5)            # new input, same graph
+    graph.replay()
+    again = _finish(static_out)
+    expect = _finish(fused_experts(d[0] * 0.5, d[1], d[2], d[3], d[4], **kw))
+    assert torch.equal(again, expect)
