@@ -186,3 +186,27 @@ def test_gemm_per_channel(qdtype):
             torch.testing.assert_close(got[row:row + 1].float(), ref.float(), rtol=2 ** -7, atol=1e-6)
         else:
             torch.testing.assert_close(got[row:row + 1].float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("m,n,k,qdtype", [(300, 512, 1024, FP8), (128, 256, 384, torch.int8),
+                                          (1, 128, 128, FP8)])
+def test_dense_block_scaled_gemm(m, n, k, qdtype):
+    from boltops_b200.fused_moe import ops
+    from boltops_b200.gemm import gemm_a8w8_blockscale, w8a8_block_scaled_mm
+    torch.manual_seed(m + n)
+    x = (torch.randn(m, k) / 2).bfloat16()
+    if qdtype == FP8:
+        w = (torch.randn(n, k) * 40).clamp(-448, 448).to(FP8)
+    else:
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8)
+    w_s = torch.rand(n // 128, k // 128) * 1e-2
+    x_q, x_s = ops.per_block_quant(x.cuda(), 128, qdtype)
+    y = gemm_a8w8_blockscale(x_q, w.cuda(), x_s, w_s.cuda())
+    torch.cuda.synchronize()
+    ops.check_device_status(y.device)
+    ref = O.block_scaled_matmul(x_q.cpu(), w, x_s.cpu(), w_s, (128, 128), torch.bfloat16)
+    assert y.shape == (m, n) and y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    y2 = w8a8_block_scaled_mm(x_q, w.cuda(), x_s, w_s.cuda(), [128, 128], torch.float16)
+    assert y2.dtype == torch.float16
+    torch.testing.assert_close(y2.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
