@@ -132,3 +132,21 @@ def test_oracle_kernel_quantiser_matches_clamped_oracle_on_benign_inputs():
     assert torch.equal(s1, s2)
     assert (q1.float() - q2.float()).abs().max() <= 32     # at most one e4m3 step at the top binade
     assert (q1.view(torch.uint8) != q2.view(torch.uint8)).float().mean() < 0.02
+
+
+def test_custom_op_fake_impl_shapes():
+    """The registered torch op reports output shapes under FakeTensorMode without a kernel
+    (the reference checks its meta function the same way, test_fused_moe.py:1715-1769)."""
+    import boltops_b200.fused_moe.custom_op  # noqa: F401  (registers the op)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        hid = torch.empty(5, 128, dtype=torch.bfloat16)
+        w1 = torch.empty(4, 256, 128, dtype=torch.bfloat16)
+        w2 = torch.empty(4, 128, 128, dtype=torch.bfloat16)
+        wts = torch.empty(5, 2)
+        ids = torch.empty(5, 2, dtype=torch.int32)
+        out = torch.ops.boltops_b200.fused_experts_impl(hid, w1, w2, wts, ids)
+        assert out.shape == (5, 128) and out.dtype == torch.bfloat16
+        out = torch.ops.boltops_b200.fused_experts_impl(hid, w1, w2, wts, ids, no_combine=True,
+                                                        output_dtype=torch.float16)
+        assert out.shape == (5, 2, 128) and out.dtype == torch.float16
