@@ -247,3 +247,66 @@ def test_layer_is_cuda_graph_capturable():
     again = _finish(static_out)
     expect = _finish(fused_experts(d[0] * 0.5, d[1], d[2], d[3], d[4], **kw))
     assert torch.equal(again, expect)
+
+
+def test_layer_edge_cases_empty_single_duplicates_chunks(monkeypatch):
+    from boltops_b200.fused_moe import fused_experts
+    g = torch.Generator().manual_seed(31)
+    e, topk, h, i = 16, 4, 256, 128
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, i, generator=g) * 0.05).bfloat16()
+    d1, d2 = w1.cuda(), w2.cuda()
+    # empty batch
+    out = fused_experts(torch.empty(0, h, dtype=torch.bfloat16, device="cuda"), d1, d2,
+                        torch.empty(0, topk, device="cuda"),
+                        torch.empty(0, topk, dtype=torch.int32, device="cuda"))
+    assert out.shape == (0, h)
+    # one token: most experts receive nothing
+    hidden = torch.randn(1, h, generator=g).bfloat16()
+    wts, ids = O.make_routing(1, e, topk, 5)
+    out = _finish(fused_experts(hidden.cuda(), d1, d2, wts.cuda(), ids.cuda()))
+    assert O.rel_l2(out, O.moe_bf16(hidden, w1, w2, wts, ids)) <= 1e-2
+    # a token that lists the same expert twice, and all tokens on one expert
+    m = 40
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    wts, ids = O.make_routing(m, e, topk, 6)
+    ids[:, 1] = ids[:, 0]
+    ids[m // 2:] = 3
+    out = _finish(fused_experts(hidden.cuda(), d1, d2, wts.cuda(), ids.cuda()))
+    assert O.rel_l2(out, O.moe_bf16(hidden, w1, w2, wts, ids)) <= 1e-2
+    # token chunking (the reference's TRITON_FUSED_MOE_CHUNK_SIZE loop), ragged last chunk
+    monkeypatch.setenv("BOLTOPS_FUSED_MOE_CHUNK_SIZE", "17")
+    wts, ids = O.make_routing(m, e, topk, 7)
+    out = _finish(fused_experts(hidden.cuda(), d1, d2, wts.cuda(), ids.cuda()))
+    assert O.rel_l2(out, O.moe_bf16(hidden, w1, w2, wts, ids)) <= 1e-2
+    monkeypatch.setenv("BOLTOPS_FUSED_MOE_CHUNK_SIZE", "0")
+    with pytest.raises(ValueError):
+        fused_experts(hidden.cuda(), d1, d2, wts.cuda(), ids.cuda())
+
+
+def test_layer_apply_router_weight_on_input_topk1_and_prequantised_input():
+    from boltops_b200.fused_moe import fused_experts, ops
+    g = torch.Generator().manual_seed(41)
+    m, e, h, i = 48, 8, 256, 128
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, i, generator=g) * 0.05).bfloat16()
+    wts, ids = O.make_routing(m, e, 1, 9)
+    wts = torch.rand(m, 1, generator=g) + 0.5
+    out = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids), apply_router_weight_on_input=True))
+    # weight applied to GEMM1's output (before the activation), nothing after GEMM2
+    rows = []
+    for t_ in range(m):
+        ex = int(ids[t_, 0])
+        c1 = ((hidden[t_].float() @ w1[ex].float().t()) * wts[t_, 0]).bfloat16()
+        act = O.activation_ref(c1[None], "silu", True).bfloat16()
+        rows.append((act.float() @ w2[ex].float().t()).bfloat16())
+    assert O.rel_l2(out, torch.cat(rows)) <= 1e-2
+    # pre-quantised fp8 hidden with a1_scale equals the layer quantising by itself
+    hq, w1q, w2q, w1s, w2s, wts, ids = _fp8_block_case(32, 8, 2, 512, 256, 17)
+    kw = dict(use_fp8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128])
+    ref = _finish(fused_experts(*_dev(hq, w1q, w2q, wts, ids), **kw))
+    x_q, x_s = ops.per_block_quant(hq.cuda(), 128, FP8)
+    out = _finish(fused_experts(x_q, w1q.cuda(), w2q.cuda(), wts.cuda(), ids.cuda(), a1_scale=x_s,
+                                output_dtype=torch.bfloat16, **kw))
+    assert torch.equal(out, ref)
