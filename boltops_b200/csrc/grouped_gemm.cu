@@ -43,7 +43,8 @@ constexpr int kABytes = kBM * 128;      // 16 KiB
 constexpr int kBBytes = kAccCols * 128; // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kScaleSlots = 8;           // ring of per-K-block activation-scale rows (512 B each)
-constexpr int kCtrlBytes = 4096 + kScaleSlots * 512;
+constexpr int kOutStageBytes = 32 * 80;   // per epilogue warp: 32 rows x (64 B + 16 B pad)
+constexpr int kCtrlBytes = 4096 + kScaleSlots * 512 + 8 * kOutStageBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;  // +1024 alignment slack
 
 enum OpKind { OP_F16 = 0, OP_F8 = 1, OP_I8 = 2 };
@@ -61,6 +62,7 @@ struct GemmParams {
   float* c_scale;
   int64_t c_scale_ld;
   int scatter, num_tokens, topk, mul_routed_weight;
+  int c_vec_ok;  // output rows are 16-byte aligned: coalesced staged stores may be used
   const int32_t* sorted_ids;
   const float* sorted_weights;
   const int32_t* expert_ids;
@@ -278,6 +280,63 @@ __device__ __forceinline__ void store_row32(void* c, int dt, int64_t row_off, in
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (col0 + j < ncols) dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+  }
+}
+
+// Pack 32 fp32 values into 64 bytes of bf16 / f16.
+__device__ __forceinline__ void pack32_16bit(const float (&v)[32], int dt, uint4 (&w)[4]) {
+  uint32_t pk[16];
+  if (dt == BOLT_BF16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      pk[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      pk[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) w[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+}
+
+// Warp-cooperative store of a 32-row x 64-byte block that is held one row per lane.
+// A direct store would touch 32 rows with 16 bytes each per instruction; staging the
+// block in shared memory (80-byte row pitch: conflict-free both ways) lets every
+// instruction write eight complete 64-byte row segments instead.
+__device__ __forceinline__ void store_rows_64B(uint8_t* stage, const uint4 (&w)[4], uint8_t* c,
+                                               int64_t row_byte_off, bool live, int lane) {
+  const unsigned live_mask = __ballot_sync(0xffffffffu, live);
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) mine[j] = w[j];
+  __syncwarp();
+  const int seg = lane & 3;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = (lane >> 2) + 8 * k;
+    const int64_t off = __shfl_sync(0xffffffffu, row_byte_off, r);
+    if ((live_mask >> r) & 1u) {
+      const uint4 x = *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
+      *reinterpret_cast<uint4*>(c + off + seg * 16) = x;
+    }
+  }
+  __syncwarp();
+}
+
+// 32 fp32 values -> c_dtype at column col0 of this lane's row: staged when possible.
+__device__ __forceinline__ void store_chunk(uint8_t* stage, const GemmParams& p, int64_t row_off,
+                                            int col0, int ncols, bool live, int lane,
+                                            const float (&v)[32]) {
+  if (p.c_vec_ok && p.c_dtype != BOLT_F32 && col0 + 32 <= ncols) {   // warp-uniform condition
+    uint4 w[4];
+    pack32_16bit(v, p.c_dtype, w);
+    store_rows_64B(stage, w, static_cast<uint8_t*>(p.c), (row_off + col0) * 2, live, lane);
+  } else if (live) {
+    store_row32(p.c, p.c_dtype, row_off, col0, ncols, v);
   }
 }
 
@@ -526,6 +585,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * q) << 16) + h * kHalfCols;
     const bool has_ids = p.sorted_ids != nullptr;
     const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
+    uint8_t* out_stage = ctrl + 4096 + kScaleSlots * 512 + (warp - 4) * kOutStageBytes;
     int t = 0;
     uint32_t tph = 0, xph = 0, kbi = 0;
     bool ok = true;
@@ -621,7 +681,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] *= rw;
             }
-            if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, v);
+            store_chunk(out_stage, p, row_off, col0, ncols, live, lane, v);
           }
         } else {
 #pragma unroll 1
@@ -661,7 +721,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
             silu_mul32_dyn(g, u, p.mid_dtype);
-            if (live) store_row32(p.c, p.c_dtype, row_off, col0, p.n_half, g);
+            store_chunk(out_stage, p, row_off, col0, p.n_half, live, lane, g);
           }
         }
         tc_fence_before();
@@ -753,7 +813,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[i][j] *= rw;
             }
-            if (live) store_row32(p.c, p.c_dtype, row_off, col0, ncols, v[i]);
+            store_chunk(out_stage, p, row_off, col0, ncols, live, lane, v[i]);
           }
         } else {
           // chunks 0,1 = gate, chunks 2,3 = up of output columns ocol + [0,64)
@@ -781,7 +841,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (EPI == BOLT_EPI_SILU_MUL) {
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-              if (live) store_row32(p.c, p.c_dtype, row_off, ocol + 32 * i, p.n_half, v[i]);
+              store_chunk(out_stage, p, row_off, ocol + 32 * i, p.n_half, live, lane, v[i]);
           } else {
             // 1x128 group quantisation: the two halves exchange their absmax through shared
             // memory (double-buffered by tile parity; the barrier wait is bounded)
@@ -796,8 +856,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             const bool to_i8 = p.c_dtype == BOLT_INT8;
             const float scale = __fdiv_rn(fmaxf(amax, 1.0e-10f), to_i8 ? 127.0f : 448.0f);
             const float inv = __frcp_rn(scale);
-            if (live) {
-              uint8_t* dst = static_cast<uint8_t*>(p.c) + row_off + ocol;
+            {
+              uint4 wq[4];
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
                 uint32_t w[8];
@@ -822,9 +882,18 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                     w[j] = x;
                   }
                 }
-                *reinterpret_cast<uint4*>(dst + 32 * i) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(dst + 32 * i + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                wq[2 * i] = make_uint4(w[0], w[1], w[2], w[3]);
+                wq[2 * i + 1] = make_uint4(w[4], w[5], w[6], w[7]);
               }
+              // 64 one-byte outputs = one 64-byte row segment, written directly (staging it
+              // through shared memory was measured slower for this small store)
+              if (live) {
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.c) + row_off + ocol);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j] = wq[j];
+              }
+            }
+            if (live) {
               if (h == 0) p.c_scale[(int64_t)tc.n_blk * p.c_scale_ld + row] = scale;
             }
           }
@@ -996,6 +1065,8 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   p.c_scale = a->c_scale;
   p.c_scale_ld = a->c_scale_ld;
   p.scatter = a->scatter;
+  p.c_vec_ok = (reinterpret_cast<uintptr_t>(a->c) % 16 == 0) &&
+               ((a->c_ld * (int64_t)dtype_bytes(a->c_dtype)) % 16 == 0);
   p.num_tokens = a->sorted_ids ? a->num_tokens : 1;
   p.topk = a->topk;
   p.mul_routed_weight = a->mul_routed_weight;
