@@ -86,6 +86,116 @@ __global__ void __launch_bounds__(256) k_fused_topk(const T* __restrict__ logits
   }
 }
 
+// Grouped gate (DeepSeek-V3 style): scores = sigmoid(logits), choice = scores + bias;
+// group score = sum of a group's two largest choices; keep the topk_group best groups;
+// top-k experts by choice inside the kept groups; weights = unbiased scores, renormalised.
+// With one fused shared expert the last slot becomes expert id `experts` with weight
+// sum(others) / routed_scaling_factor, and the normalisation excludes it.
+template <typename T>
+__global__ void __launch_bounds__(256) k_fused_gate(const T* __restrict__ logits,
+                                                    const float* __restrict__ bias, int64_t tokens,
+                                                    int experts, int num_groups, int topk_group,
+                                                    int topk, int shared, float routed_scale,
+                                                    float* __restrict__ weights,
+                                                    int32_t* __restrict__ ids) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int per_lane = (experts + 31) / 32;
+  const int per_group = experts / num_groups;
+  for (int64_t m = warp0; m < tokens; m += nwarps) {
+    const T* row = logits + m * experts;
+    float score[kMaxPerLane], choice[kMaxPerLane];
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (j < per_lane && e < experts) {
+        score[j] = 1.0f / (1.0f + expf(-to_f32(row[e])));
+        choice[j] = score[j] + bias[e];
+      } else {
+        score[j] = 0.f;
+        choice[j] = -FLT_MAX;
+      }
+    }
+    // group scores: lane g ends up holding the score of group g (num_groups <= 32)
+    float my_group_score = -FLT_MAX;
+    for (int g = 0; g < num_groups; ++g) {
+      float top1 = -FLT_MAX, top2 = -FLT_MAX;
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j) {
+        const int e = lane + 32 * j;
+        if (j < per_lane && e < experts && e / per_group == g) {
+          const float c = choice[j];
+          if (c > top1) { top2 = top1; top1 = c; } else if (c > top2) { top2 = c; }
+        }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float o1 = __shfl_xor_sync(0xffffffffu, top1, o);
+        const float o2 = __shfl_xor_sync(0xffffffffu, top2, o);
+        const float hi = fmaxf(top1, o1);
+        const float lo = fmaxf(fminf(top1, o1), fmaxf(top2, o2));
+        top1 = hi;
+        top2 = lo;
+      }
+      if (lane == g) my_group_score = top1 + top2;
+    }
+    // keep the topk_group best groups (ties: lowest group index)
+    unsigned keep = 0;
+    float gs = (lane < num_groups) ? my_group_score : -FLT_MAX;
+    for (int r = 0; r < topk_group; ++r) {
+      float best = gs;
+      int best_g = lane;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+      }
+      keep |= 1u << best_g;
+      if (lane == best_g) gs = -FLT_MAX;
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (!(j < per_lane && e < experts) || !((keep >> (e / per_group)) & 1u)) choice[j] = -FLT_MAX;
+    }
+    // top-k by choice, descending; weights are the unbiased scores
+    float my_w = 0.f;
+    int my_id = 0;
+    float total = 0.f;
+    const int routed = shared ? topk - 1 : topk;
+    for (int k = 0; k < routed; ++k) {
+      float best = -FLT_MAX, best_s = 0.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j) {
+        const int e = lane + 32 * j;
+        if (choice[j] > best) { best = choice[j]; best_e = e; best_s = score[j]; }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+      }
+      if ((best_e & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j)
+          if (lane + 32 * j == best_e) choice[j] = -FLT_MAX;
+      }
+      if (lane == k) { my_w = best_s; my_id = best_e; }
+      total += best_s;
+    }
+    if (shared && lane == topk - 1) {
+      my_w = total / routed_scale;
+      my_id = experts;
+    }
+    if (lane < topk) {
+      weights[m * topk + lane] = my_w / total;
+      ids[m * topk + lane] = my_id;
+    }
+  }
+}
+
 template <typename T>
 int launch_topk(const void* logits, int64_t tokens, int experts, int topk, int renormalize,
                 int softmax, float* weights, int32_t* ids, cudaStream_t st) {
@@ -123,4 +233,43 @@ extern "C" int bolt_fused_topk(const void* gating, int dtype, int64_t num_tokens
                                  topk_weights, topk_ids, st);
     default: set_error("fused_topk: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
   }
+}
+
+extern "C" int bolt_moe_fused_gate(const void* gating, int dtype, const float* bias,
+                                   int64_t num_tokens, int num_experts, int num_expert_group,
+                                   int topk_group, int topk, int num_fused_shared_experts,
+                                   float routed_scaling_factor, float* topk_weights,
+                                   int32_t* topk_ids, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(num_tokens >= 0 && num_experts > 0 && num_experts <= 32 * kMaxPerLane,
+               "fused_gate: bad shape");
+  BOLT_REQUIRE(num_expert_group > 0 && num_expert_group <= 32 &&
+                   num_experts % num_expert_group == 0 && num_experts / num_expert_group >= 2,
+               "fused_gate: bad expert grouping");
+  BOLT_REQUIRE(topk_group > 0 && topk_group <= num_expert_group, "fused_gate: bad topk_group");
+  BOLT_REQUIRE(num_fused_shared_experts == 0 || num_fused_shared_experts == 1,
+               "fused_gate: at most one fused shared expert");
+  BOLT_REQUIRE(topk > num_fused_shared_experts && topk <= 32 &&
+                   topk - num_fused_shared_experts <= topk_group * (num_experts / num_expert_group),
+               "fused_gate: topk %d out of range", topk);
+  BOLT_REQUIRE(num_tokens == 0 || (gating && bias && topk_weights && topk_ids),
+               "fused_gate: null pointer");
+  if (num_tokens == 0) return BOLT_OK;
+  int64_t blocks = (num_tokens + 7) / 8;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 16;
+  if (blocks > cap) blocks = cap;
+#define BOLT_GATE_LAUNCH(T)                                                                    \
+  k_fused_gate<T><<<(unsigned)blocks, 256, 0, st>>>(                                          \
+      static_cast<const T*>(gating), bias, num_tokens, num_experts, num_expert_group,          \
+      topk_group, topk, num_fused_shared_experts, routed_scaling_factor, topk_weights, topk_ids)
+  switch (dtype) {
+    case BOLT_F32: BOLT_GATE_LAUNCH(float); break;
+    case BOLT_BF16: BOLT_GATE_LAUNCH(__nv_bfloat16); break;
+    case BOLT_F16: BOLT_GATE_LAUNCH(__half); break;
+    default: set_error("fused_gate: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
+  }
+#undef BOLT_GATE_LAUNCH
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
 }

@@ -39,3 +39,27 @@ def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: i
         topk_ids.copy_(ids)
         ids = topk_ids
     return weights, ids
+
+
+def moe_fused_gate(input: torch.Tensor, bias: torch.Tensor, topk_weights: torch.Tensor,
+                   topk_ids: torch.Tensor, num_expert_group: int, topk_group: int, topk: int,
+                   num_fused_shared_experts: int, routed_scaling_factor: float = 1.0):
+    """Grouped gate with optional fused shared expert; same arguments and outputs as the
+    reference helper (boltops/tools/fused_moe_triton_tune/routing.py:38-79).  Writes into the
+    caller's ``topk_weights`` (fp32) / ``topk_ids`` (int32) and returns them as a list."""
+    if not input.is_cuda:
+        raise ValueError("boltops_b200 kernels need CUDA tensors (there is no CPU path)")
+    assert topk_weights.dtype == torch.float32 and topk_ids.dtype == torch.int32
+    assert topk_weights.is_contiguous() and topk_ids.is_contiguous()
+    lib = _cabi.load()
+    m, e = input.shape
+    x = input.contiguous()
+    b = bias.float().contiguous()
+    with torch.cuda.device(x.device):
+        check(lib.bolt_moe_fused_gate(ptr(x), dtype_code(x.dtype), ptr(b), m, e, num_expert_group,
+                                      topk_group, topk, num_fused_shared_experts,
+                                      float(routed_scaling_factor), ptr(topk_weights),
+                                      ptr(topk_ids), stream_of(x)))
+    from . import ops
+    ops._count()
+    return [topk_weights, topk_ids]

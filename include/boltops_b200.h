@@ -163,6 +163,17 @@ int bolt_fused_topk(const void* gating, int dtype, int64_t num_tokens, int num_e
                     int renormalize, int is_softmax, float* topk_weights, int32_t* topk_ids,
                     void* stream);
 
+/* Grouped gate with optional fused shared expert.  Replaces moe_fused_gate
+ * (boltops/tools/fused_moe_triton_tune/routing.py:38-79): sigmoid scores, + bias for the
+ * choice, group score = sum of the two best choices of a group, topk_group groups kept, top-k
+ * experts inside them, weights = unbiased scores renormalised; with one fused shared expert
+ * the last slot is expert id num_experts with weight sum(others)/routed_scaling_factor.
+ */
+int bolt_moe_fused_gate(const void* gating, int dtype, const float* bias, int64_t num_tokens,
+                        int num_experts, int num_expert_group, int topk_group, int topk,
+                        int num_fused_shared_experts, float routed_scaling_factor,
+                        float* topk_weights, int32_t* topk_ids, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Dynamic activation quantisation.
  * Replaces per_token_quant_triton / dynamic_per_token_quant_fp8_i8

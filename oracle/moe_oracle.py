@@ -39,6 +39,27 @@ def fused_topk(gating_output: torch.Tensor, topk: int, renormalize: bool = True,
     return weights, ids.to(torch.int32)
 
 
+def fused_gate(logits: torch.Tensor, bias: torch.Tensor, num_expert_group: int, topk_group: int,
+               topk: int, num_fused_shared_experts: int = 0, routed_scaling_factor: float = 1.0):
+    """Grouped gate (boltops/tools/fused_moe_triton_tune/routing.py:38-79)."""
+    scores = logits.float().sigmoid()
+    choice = scores + bias.float()[None]
+    m, e = scores.shape
+    gscore = choice.view(m, num_expert_group, -1).topk(2, dim=-1).values.sum(-1)
+    groups = gscore.topk(topk_group, dim=-1).indices
+    gmask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, groups, True)
+    emask = gmask[:, :, None].expand(m, num_expert_group, e // num_expert_group).reshape(m, e)
+    sel = choice.masked_fill(~emask, float("-inf")).topk(topk, dim=-1).indices
+    w = scores.gather(1, sel)
+    if num_fused_shared_experts:
+        sel[:, -1] = e
+        w[:, -1] = w[:, :-1].sum(-1) / routed_scaling_factor
+        den = w[:, :-1].sum(-1, keepdim=True)
+    else:
+        den = w.sum(-1, keepdim=True)
+    return w / den, sel.to(torch.int32)
+
+
 # ---------------------------------------------------------------------------
 # Sort contracts
 # ---------------------------------------------------------------------------

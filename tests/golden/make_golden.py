@@ -110,6 +110,21 @@ def main(ref_root: str) -> None:
     np.savez_compressed(HERE / "routing.npz", logits=logits.numpy(),
                         weights=wts.numpy(), ids=tid.numpy())
 
+    # ---- grouped gate ----------------------------------------------------------------
+    gt = load_defs(tune / "routing.py", ["moe_fused_gate"])
+    torch.manual_seed(12)
+    glog = torch.randn(11, 64)
+    gbias = torch.randn(64) * 0.1
+    gate = {"logits": glog.numpy(), "bias": gbias.numpy()}
+    for shared in (0, 1):
+        k = 6 + shared
+        gw = torch.empty(11, k)
+        gi = torch.empty(11, k, dtype=torch.int32)
+        gt["moe_fused_gate"](glog, gbias, gw, gi, 4, 2, k, shared, 2.5)
+        gate[f"w{shared}"] = gw.numpy()
+        gate[f"i{shared}"] = gi.numpy()
+    np.savez_compressed(HERE / "gate.npz", **gate)
+
     # ---- bf16 layer ------------------------------------------------------------
     tf = load_defs(tdir / "test_fused_moe.py",
                    ["_torch_moe", "_dynamic_group_quant_int8",

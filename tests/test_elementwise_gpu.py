@@ -183,3 +183,28 @@ def test_fused_topk(m, e, k, softmax, renorm, dtype):
     assert all(len(set(row)) == k for row in i.cpu().tolist())
     if dtype == torch.float32:
         assert torch.equal(i.cpu(), i_ref)
+
+
+@pytest.mark.parametrize("m,e,groups,topk_group,topk,shared", [
+    (64, 256, 8, 4, 8, 0), (33, 256, 8, 4, 9, 1), (7, 64, 4, 2, 6, 0), (5, 16, 1, 1, 4, 0),
+])
+def test_moe_fused_gate(m, e, groups, topk_group, topk, shared):
+    from boltops_b200.fused_moe.routing import moe_fused_gate
+    g = torch.Generator().manual_seed(m + e)
+    logits = torch.randn(m, e, generator=g)
+    bias = torch.randn(e, generator=g) * 0.1
+    w_ref, i_ref = O.fused_gate(logits, bias, groups, topk_group, topk, shared, 2.5)
+    w = torch.empty(m, topk, dtype=torch.float32, device="cuda")
+    i = torch.empty(m, topk, dtype=torch.int32, device="cuda")
+    out = moe_fused_gate(logits.cuda(), bias.cuda(), w, i, groups, topk_group, topk, shared, 2.5)
+    assert out[0] is w and out[1] is i
+    # the reference leaves the order of the routed experts unspecified unless a shared expert
+    # is fused; compare as sets of (id, weight) pairs, the shared slot stays last
+    for t_ in range(m):
+        got = sorted(zip(i[t_].tolist(), w[t_].tolist()))
+        exp = sorted(zip(i_ref[t_].tolist(), w_ref[t_].tolist()))
+        assert [a for a, _ in got] == [a for a, _ in exp]
+        for (_, a), (_, b) in zip(got, exp):
+            assert abs(a - b) <= 1e-5 * max(1.0, abs(b))
+    if shared:
+        assert (i[:, -1] == e).all()

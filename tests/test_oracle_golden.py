@@ -164,3 +164,17 @@ def test_moe_sum_known_answer(width):
     x = (torch.arange(3 * 2 * width).reshape(3, 2, width).float() / 256).bfloat16()
     expect = ((x[:, 0].float() + x[:, 1].float()) * 1.25).bfloat16()
     assert torch.equal(O.moe_sum(x, 1.25), expect)
+
+
+@pytest.mark.parametrize("shared", [0, 1])
+def test_grouped_gate_fixture(shared):
+    z = load_npz("gate.npz")
+    k = 6 + shared
+    w, i = O.fused_gate(t(z["logits"]), t(z["bias"]), 4, 2, k, shared, 2.5)
+    ref_w, ref_i = t(z[f"w{shared}"]), t(z[f"i{shared}"])
+    # the reference does not sort the routed experts when no shared expert is fused
+    for row in range(w.shape[0]):
+        got = sorted(zip(i[row].tolist(), w[row].tolist()))
+        exp = sorted(zip(ref_i[row].tolist(), ref_w[row].tolist()))
+        assert [a for a, _ in got] == [a for a, _ in exp]
+        assert all(abs(a - b) <= 1e-6 for (_, a), (_, b) in zip(got, exp))
