@@ -310,3 +310,28 @@ def test_layer_apply_router_weight_on_input_topk1_and_prequantised_input():
     out = _finish(fused_experts(x_q, w1q.cuda(), w2q.cuda(), wts.cuda(), ids.cuda(), a1_scale=x_s,
                                 output_dtype=torch.bfloat16, **kw))
     assert torch.equal(out, ref)
+
+
+def test_layer_special_values_stay_in_their_rows():
+    """A token with NaN / Inf inputs poisons only its own output row (rows are independent in
+    every stage), and denormal / signed-zero inputs give finite results."""
+    from boltops_b200.fused_moe import fused_experts
+    g = torch.Generator().manual_seed(51)
+    m, e, topk, h, i = 130, 8, 2, 256, 128
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, i, generator=g) * 0.05).bfloat16()
+    wts, ids = O.make_routing(m, e, topk, 52)
+    clean = _finish(fused_experts(*_dev(hidden, w1, w2, wts, ids)))
+    bad = hidden.clone()
+    bad[3, 5] = float("nan")
+    bad[77, 0] = float("inf")
+    bad[10, :] = 0.0
+    bad[10, 1] = -0.0
+    bad[11, :] = 1e-40          # flushes to a bf16 denormal / zero
+    out = _finish(fused_experts(*_dev(bad, w1, w2, wts, ids)))
+    assert torch.isnan(out[3]).any() and not torch.isfinite(out[77]).all()
+    ok_rows = [r for r in range(m) if r not in (3, 77, 10, 11)]
+    assert torch.equal(out[ok_rows], clean[ok_rows])
+    assert torch.isfinite(out[10].float()).all() and (out[10] == 0).all()
+    assert torch.isfinite(out[11].float()).all()
