@@ -56,3 +56,22 @@ def test_ep_two_gpus_matches_single_gpu_layer():
     for rank in range(world):
         # per-rank partial sums are rounded to bf16 before they cross the link
         assert ret[rank] <= 1e-2, f"rank {rank}: {ret[rank]}"
+
+
+def test_ep_plan_cuda_equals_torch_plan():
+    """The sort-based planner (no host sync) and the torch planner agree exactly."""
+    from boltops_b200.fused_moe.ep import ExpertParallelMoE
+    from oracle import moe_oracle as O
+    for world, e, k, m in [(8, 256, 8, 4096), (4, 16, 4, 37), (2, 8, 2, 1)]:
+        ep = ExpertParallelMoE.__new__(ExpertParallelMoE)
+        ep.world, ep.rank, ep.num_experts, ep.per_rank = world, 0, e, e // world
+        _, ids = O.make_routing(m, e, k, 3 + m)
+        if m > 5:
+            ids[5, 0] = -1
+        d_ids = ids.cuda()
+        tok_a, cnt_a, pos_a = ep._plan_torch(d_ids)
+        tok_b, cnt_b, pos_b = ep._plan_cuda(d_ids)
+        n = int(cnt_a.sum())
+        assert torch.equal(cnt_a.cpu(), cnt_b.cpu())
+        assert torch.equal(tok_a.cpu(), tok_b[:n].cpu())
+        assert torch.equal(pos_a.cpu(), pos_b.cpu())
