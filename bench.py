@@ -157,14 +157,58 @@ def layer_kwargs(cfg, w1s, w2s):
 # clocks
 # ---------------------------------------------------------------------------
 class ClockSampler:
+    """SM clock and throttle reasons sampled while the timed region runs.
+
+    NVML is read from a thread every few milliseconds (a timed region of a few steps lasts
+    tens of milliseconds, so a 100 ms `nvidia-smi -lms` loop would mostly see the idle GPU
+    around it); `nvidia-smi` is the fallback when the NVML binding is missing.  Read-only.
+    """
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.nvml, self.handle, self.thread, self.stop_flag = None, None, None, False
+        self.max_mhz, self.reasons = 0, set()
+
+    def _nvml_loop(self):
+        n = self.nvml
+        masks = (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown),
+                 ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                 ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown),
+                 ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap))
+        while not self.stop_flag:
+            try:
+                self.rows.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                for name, mask in masks:
+                    if bits & mask:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import pynvml as n
+            n.nvmlInit()
+            # NVML enumerates physical devices: map the CUDA ordinal through its PCI bus id
+            try:
+                import torch
+                bus = torch.cuda.get_device_properties(self.index).pci_bus_id
+                dom = torch.cuda.get_device_properties(self.index).pci_domain_id
+                dev = torch.cuda.get_device_properties(self.index).pci_device_id
+                self.handle = n.nvmlDeviceGetHandleByPciBusId(f"{dom:08x}:{bus:02x}:{dev:02x}.0")
+            except Exception:
+                self.handle = n.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM))
+            self.nvml = n
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -178,6 +222,13 @@ class ClockSampler:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            sm = [r for r in self.rows if isinstance(r, float)]
+            return dict(sm_mhz=statistics.median(sm) if sm else None,
+                        sm_min_mhz=min(sm) if sm else None, sm_max_mhz=self.max_mhz or None,
+                        reasons=sorted(self.reasons), samples=len(sm), source="nvml")
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -196,7 +247,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=mx or None,
-                    reasons=sorted(reasons), samples=len(sm))
+                    reasons=sorted(reasons), samples=len(sm), source="nvidia-smi")
 
 
 # ---------------------------------------------------------------------------

@@ -212,6 +212,32 @@ int launch_topk(const void* logits, int64_t tokens, int experts, int topk, int r
 }  // namespace
 }  // namespace bolt
 
+// ---------------------------------------------------------------------------
+// Expert-parallel dispatch: which ranks does a token go to?
+// ---------------------------------------------------------------------------
+// One thread per token: ranks hit by any of its top-k experts as a bit mask, written out as
+// routes[token][r] = r (hit) or -1 (not hit).  Fed to the stable sort with ranks as
+// "experts", this gives the (rank, token)-ordered send list, the per-rank counts and the
+// position of every (token, rank) pair in one go.
+__global__ void __launch_bounds__(256) k_dest_ranks(const int32_t* __restrict__ topk_ids,
+                                                    int64_t num_tokens, int topk, int num_experts,
+                                                    int experts_per_rank, int world,
+                                                    int32_t* __restrict__ routes) {
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < num_tokens;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    unsigned long long mask[4] = {0ull, 0ull, 0ull, 0ull};
+    for (int k = 0; k < topk; ++k) {
+      const int e = topk_ids[t * topk + k];
+      if (e >= 0 && e < num_experts) {
+        const int r = e / experts_per_rank;
+        mask[r >> 6] |= 1ull << (r & 63);
+      }
+    }
+    for (int r = 0; r < world; ++r)
+      routes[t * world + r] = ((mask[r >> 6] >> (r & 63)) & 1ull) ? r : -1;
+  }
+}
+
 extern "C" int bolt_fused_topk(const void* gating, int dtype, int64_t num_tokens, int num_experts,
                                int topk, int renormalize, int is_softmax, float* topk_weights,
                                int32_t* topk_ids, void* stream) {
@@ -270,6 +296,28 @@ extern "C" int bolt_moe_fused_gate(const void* gating, int dtype, const float* b
     default: set_error("fused_gate: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
   }
 #undef BOLT_GATE_LAUNCH
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+extern "C" int bolt_ep_dest_ranks(const int32_t* topk_ids, int64_t num_tokens, int topk,
+                                  int num_experts, int experts_per_rank, int world,
+                                  int32_t* routes, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(num_tokens >= 0 && topk > 0 && num_experts > 0 && experts_per_rank > 0,
+               "ep_dest_ranks: bad shape");
+  BOLT_REQUIRE(world > 0 && world <= 255 &&
+                   (int64_t)world * experts_per_rank >= num_experts,
+               "ep_dest_ranks: world %d x %d experts per rank does not cover %d experts (max 255 ranks)",
+               world, experts_per_rank, num_experts);
+  BOLT_REQUIRE(num_tokens == 0 || (topk_ids && routes), "ep_dest_ranks: null pointer");
+  if (num_tokens == 0) return BOLT_OK;
+  int64_t blocks = (num_tokens + 255) / 256;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 8;
+  if (blocks > cap) blocks = cap;
+  k_dest_ranks<<<(unsigned)blocks, 256, 0, st>>>(topk_ids, num_tokens, topk, num_experts,
+                                                 experts_per_rank, world, routes);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }

@@ -73,13 +73,8 @@ class ExpertParallelMoE:
         inverse permutation, ``pos``."""
         from . import ops
         m = topk_ids.shape[0]
-        dest = torch.div(topk_ids.long(), self.per_rank, rounding_mode="floor")
-        valid = (topk_ids >= 0) & (topk_ids < self.num_experts)
-        hit = torch.zeros((m, self.world + 1), dtype=torch.bool, device=topk_ids.device)
-        hit.scatter_(1, torch.where(valid, dest, torch.full_like(dest, self.world)), True)
-        ranks = torch.arange(self.world, dtype=torch.int32, device=topk_ids.device)
-        routes = torch.where(hit[:, :self.world], ranks, torch.full_like(ranks, -1)).contiguous()
-        dummy_w = torch.zeros((m, self.world), dtype=torch.float32, device=topk_ids.device)
+        routes = ops.ep_dest_ranks(topk_ids, self.num_experts, self.per_rank, self.world)
+        dummy_w = torch.empty((m, self.world), dtype=torch.float32, device=topk_ids.device)
         pos = torch.empty((m, self.world), dtype=torch.int32, device=topk_ids.device)
         sorted_ids, _, _, _, counts, _ = ops.moe_sorting_ck(
             routes, dummy_w, self.world, None, None, 1, None, alloc_moe_buf=False, route_pos=pos)
@@ -103,9 +98,12 @@ class ExpertParallelMoE:
         return tok_idx, send_counts, pos
 
     def _exchange_counts(self, send_counts: torch.Tensor):
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        return send_counts.tolist(), recv_counts.tolist()
+        both = torch.empty((2, send_counts.numel()), dtype=send_counts.dtype,
+                           device=send_counts.device)
+        both[0].copy_(send_counts)
+        dist.all_to_all_single(both[1], both[0], group=self.group)
+        send_split, recv_split = both.tolist()          # one host synchronisation for both
+        return send_split, recv_split
 
     # -- the layer ----------------------------------------------------------------------------
     def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):

@@ -235,6 +235,22 @@ def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
     return out
 
 
+def ep_dest_ranks(topk_ids: torch.Tensor, num_experts: int, experts_per_rank: int,
+                  world: int) -> torch.Tensor:
+    """``routes[t, r] = r`` if one of token t's experts lives on rank r, else -1 (int32 [M, world])."""
+    _require_cuda(topk_ids)
+    lib = _cabi.load()
+    ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+    ids = ids.contiguous()
+    m, k = ids.shape
+    routes = torch.empty((m, world), dtype=torch.int32, device=ids.device)
+    with torch.cuda.device(ids.device):
+        check(lib.bolt_ep_dest_ranks(ptr(ids), m, k, num_experts, experts_per_rank, world,
+                                     ptr(routes), stream_of(ids)))
+    _count()
+    return routes
+
+
 # ---------------------------------------------------------------------------
 # grouped GEMM
 # ---------------------------------------------------------------------------

@@ -174,6 +174,16 @@ int bolt_moe_fused_gate(const void* gating, int dtype, const float* bias, int64_
                         int num_fused_shared_experts, float routed_scaling_factor,
                         float* topk_weights, int32_t* topk_ids, void* stream);
 
+/* Expert-parallel dispatch helper (no reference counterpart: the reference leaves expert
+ * parallelism to the serving engine and only takes its expert_map,
+ * boltops/fused_moe/__init__.py:127-133).  routes[t][r] = r when one of token t's experts
+ * lives on rank r (experts sharded contiguously, experts_per_rank each), else -1; ids outside
+ * [0, num_experts) hit no rank.  Sorting these routes with bolt_moe_sort_ck (ranks as experts,
+ * unit 1) yields the send order, the per-rank counts and the inverse permutation.
+ */
+int bolt_ep_dest_ranks(const int32_t* topk_ids, int64_t num_tokens, int topk, int num_experts,
+                       int experts_per_rank, int world, int32_t* routes, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Dynamic activation quantisation.
  * Replaces per_token_quant_triton / dynamic_per_token_quant_fp8_i8
