@@ -642,6 +642,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int row = tc.m_blk * kBM + row_in_tile;
       const int token = cur.sid & 0xFFFFFF;
       const bool live = token < p.num_tokens;
+      // Gated epilogues feed the next GEMM: padding rows are written as zeros rather than left
+      // as stale memory, because operand rows full of arbitrary bits cost tensor-core power
+      // (and with it SM clock) in the GEMM that streams them.
+      const bool wr = live || (GATED && !p.scatter);
       const float rw = cur.rw;
       int64_t out_row = row;
       if (p.scatter) out_row = (int64_t)token * p.topk + ((uint32_t)cur.sid >> 24);
@@ -694,8 +698,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             float g[32], u[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              g[j] = acc_to_f32<OPK>(rg[j]);
-              u[j] = acc_to_f32<OPK>(ru[j]);
+              g[j] = live ? acc_to_f32<OPK>(rg[j]) : 0.f;
+              u[j] = live ? acc_to_f32<OPK>(ru[j]) : 0.f;
             }
             if (CHANNEL) {
 #pragma unroll
@@ -721,7 +725,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
             silu_mul32_dyn(g, u, p.mid_dtype);
-            store_chunk(out_stage, p, row_off, col0, p.n_half, live, lane, g);
+            store_chunk(out_stage, p, row_off, col0, p.n_half, wr, lane, g);
           }
         }
         tc_fence_before();
@@ -818,6 +822,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         } else {
           // chunks 0,1 = gate, chunks 2,3 = up of output columns ocol + [0,64)
           float amax = 0.f;
+          if (!live) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[i][j] = 0.f;
+          }
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             const int col0 = ocol + 32 * i;
@@ -841,7 +851,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (EPI == BOLT_EPI_SILU_MUL) {
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-              store_chunk(out_stage, p, row_off, ocol + 32 * i, p.n_half, live, lane, v[i]);
+              store_chunk(out_stage, p, row_off, ocol + 32 * i, p.n_half, wr, lane, v[i]);
           } else {
             // 1x128 group quantisation: the two halves exchange their absmax through shared
             // memory (double-buffered by tile parity; the barrier wait is bounded)
@@ -887,14 +897,14 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
               // 64 one-byte outputs = one 64-byte row segment, written directly (staging it
               // through shared memory was measured slower for this small store)
-              if (live) {
+              if (wr) {
                 uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.c) + row_off + ocol);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) dst[j] = wq[j];
               }
             }
-            if (live) {
-              if (h == 0) p.c_scale[(int64_t)tc.n_blk * p.c_scale_ld + row] = scale;
+            if (wr) {
+              if (h == 0) p.c_scale[(int64_t)tc.n_blk * p.c_scale_ld + row] = live ? scale : 0.f;
             }
           }
         }

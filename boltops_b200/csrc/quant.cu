@@ -255,9 +255,22 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint4* __restrict__ s
   const int valid = min(*num_valid, capacity);
   for (int row = blockIdx.x; row < valid; row += gridDim.x) {
     const int token = sorted_ids[row] & 0xFFFFFF;
-    if (token >= num_tokens) continue;  // pad row: never consumed, left untouched
-    const uint4* s = src + (int64_t)token * row_vecs;
     uint4* d = dst + (int64_t)row * row_vecs;
+    if (token >= num_tokens) {
+      // pad row inside a tile: its results are never consumed, but the GEMM streams it through
+      // the tensor cores, and zeros cost less power there than stale memory does
+      for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (src_scale != nullptr) {
+        if (groups == 1) {
+          if (threadIdx.x == 0) dst_scale[row] = 0.f;
+        } else {
+          for (int g = threadIdx.x; g < groups; g += blockDim.x)
+            dst_scale[(int64_t)g * dst_scale_ld + row] = 0.f;
+        }
+      }
+      continue;
+    }
+    const uint4* s = src + (int64_t)token * row_vecs;
     for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = __ldg(s + i);
     if (src_scale != nullptr) {
       if (groups == 1) {
