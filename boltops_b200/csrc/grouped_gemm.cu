@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded; on expiry the kernel records a status
 // word, stops issuing work, drains and frees its TMEM before returning.
 #include <cuda.h>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -34,7 +35,7 @@ namespace bolt {
 namespace {
 
 constexpr int kThreads = 384;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kBM = 128;
 constexpr int kAccCols = 256;           // accumulator columns per tile
 constexpr int kHalfCols = 128;          // columns of one independently scheduled half
@@ -43,7 +44,9 @@ constexpr int kABytes = kBM * 128;      // 16 KiB
 constexpr int kBBytes = kAccCols * 128; // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kScaleSlots = 8;           // ring of per-K-block activation-scale rows (512 B each)
-constexpr int kOutStageBytes = 32 * 80;   // per epilogue warp: 32 rows x (64 B + 16 B pad)
+constexpr int kOutSlotBytes = 32 * 64;    // one 32-row x 64-byte block as a bulk store reads it
+constexpr int kOutStageBytes = 4 * kOutSlotBytes;  // per epilogue warp: one slot per 32-column chunk
+                                                   // (the padded 32 x 80 B staging layout fits in it too)
 constexpr int kCtrlBytes = 4096 + kScaleSlots * 512 + 8 * kOutStageBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;  // +1024 alignment slack
 
@@ -63,6 +66,7 @@ struct GemmParams {
   int64_t c_scale_ld;
   int scatter, num_tokens, topk, mul_routed_weight;
   int c_vec_ok;  // output rows are 16-byte aligned: coalesced staged stores may be used
+  int c_tma_ok;  // a tensor map over the 16-bit output exists: whole 32-row blocks go out by TMA
   const int32_t* sorted_ids;
   const float* sorted_weights;
   const int32_t* expert_ids;
@@ -156,6 +160,28 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
           "r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// Bulk tensor store shared -> global (2-D tile), tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+      "r"(src), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// all earlier bulk stores of this thread have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// ... and have fully completed
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -310,6 +336,8 @@ __device__ __forceinline__ void pack32_16bit(const float (&v)[32], int dt, uint4
 __device__ __forceinline__ void store_rows_64B(uint8_t* stage, const uint4 (&w)[4], uint8_t* c,
                                                int64_t row_byte_off, bool live, int lane) {
   const unsigned live_mask = __ballot_sync(0xffffffffu, live);
+  if (lane == 0) bulk_wait_read();   // a bulk store of an earlier block may still read the buffer
+  __syncwarp();
   uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
 #pragma unroll
   for (int j = 0; j < 4; ++j) mine[j] = w[j];
@@ -327,11 +355,39 @@ __device__ __forceinline__ void store_rows_64B(uint8_t* stage, const uint4 (&w)[
   __syncwarp();
 }
 
-// 32 fp32 values -> c_dtype at column col0 of this lane's row: staged when possible.
-__device__ __forceinline__ void store_chunk(uint8_t* stage, const GemmParams& p, int64_t row_off,
-                                            int col0, int ncols, bool live, int lane,
-                                            const float (&v)[32]) {
-  if (p.c_vec_ok && p.c_dtype != BOLT_F32 && col0 + 32 <= ncols) {   // warp-uniform condition
+// Warp-cooperative store of a 32-row x 64-byte block (one row per lane, rows row0 .. row0+31 of
+// the output) by one bulk tensor copy.  The block is laid out in shared memory the way a
+// 64-byte-swizzled tensor map expects it (16-byte chunk index XOR bits 1-2 of the row), which
+// also makes the per-lane 16-byte writes conflict-free.  The copy runs asynchronously; every
+// chunk of a tile has a slot of its own, and the slots are reclaimed once per tile (the caller
+// waits for the previous tile's copies to have read them before the first chunk).
+__device__ __forceinline__ void store_rows_tma(uint8_t* stage, const uint4 (&w)[4],
+                                               const CUtensorMap* map, int col0, int row0,
+                                               int lane) {
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ sw) << 4)) = w[j];
+  fence_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map, smem_u32(stage), col0, row0);
+    bulk_commit();
+  }
+}
+
+// 32 fp32 values -> c_dtype at column col0 of this lane's row: by TMA when the whole 32-row
+// block is written, else staged through shared memory when possible.  tile_row0 = output row
+// of lane 0 (only meaningful when rows are not scattered).
+__device__ __forceinline__ void store_chunk(uint8_t* stage, int slot, const GemmParams& p,
+                                            const CUtensorMap* map_c, int tile_row0,
+                                            int64_t row_off, int col0, int ncols, bool live,
+                                            int lane, const float (&v)[32]) {
+  if (p.c_tma_ok && col0 < ncols && __all_sync(0xffffffffu, live)) {   // warp-uniform
+    uint4 w[4];
+    pack32_16bit(v, p.c_dtype, w);
+    store_rows_tma(stage + slot * kOutSlotBytes, w, map_c, col0, tile_row0, lane);
+  } else if (p.c_vec_ok && p.c_dtype != BOLT_F32 && col0 + 32 <= ncols) {   // warp-uniform
     uint4 w[4];
     pack32_16bit(v, p.c_dtype, w);
     store_rows_64B(stage, w, static_cast<uint8_t*>(p.c), (row_off + col0) * 2, live, lane);
@@ -428,7 +484,7 @@ struct RowMeta {
 template <int OPK, bool BS, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   constexpr bool GATED = EPI != BOLT_EPI_STORE;
   constexpr int kBKElems = OPK == OP_F16 ? 64 : 128;
   constexpr bool CHANNEL = (OPK != OP_F16) && !BS;
@@ -640,6 +696,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         continue;
       }
       const int row = tc.m_blk * kBM + row_in_tile;
+      const int tile_row0 = tc.m_blk * kBM + 32 * q;   // output row of lane 0 (sorted layout)
       const int token = cur.sid & 0xFFFFFF;
       const bool live = token < p.num_tokens;
       // Gated epilogues feed the next GEMM: padding rows are written as zeros rather than left
@@ -658,6 +715,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
         if (!ok) break;
         tc_fence_after();
+        if (lane == 0) bulk_wait_read();   // the previous tile's bulk stores have left the slots
+        __syncwarp();
         const uint32_t tbase = lane_addr + t * kAccCols;
         const float a_s = cur.a_s;
         if (!GATED) {
@@ -685,7 +744,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] *= rw;
             }
-            store_chunk(out_stage, p, row_off, col0, ncols, live, lane, v);
+            store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v);
           }
         } else {
 #pragma unroll 1
@@ -725,7 +784,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
             silu_mul32_dyn(g, u, p.mid_dtype);
-            store_chunk(out_stage, p, row_off, col0, p.n_half, wr, lane, g);
+            store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, col0, p.n_half, wr, lane, g);
           }
         }
         tc_fence_before();
@@ -743,6 +802,21 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         const float *bs0, *bs1;
         bscale_ptrs(expert, tc.n_blk, bs0, bs1);
         float b0_next = b0_first, b1_next = b1_first;
+        // Software-pipelined promotion: 32-column loads, two staging buffers, one load always in
+        // flight while the previous chunk is being accumulated; the first chunk of the next K
+        // block is requested before the last chunk of this one is consumed.
+        auto fma_chunk = [&](float2 (&a)[16], const uint32_t (&r)[32], float sc) {
+          const float2 sc2 = make_float2(sc, sc);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            a[j] = __ffma2_rn(
+                make_float2(acc_to_f32<OPK>(r[2 * j]), acc_to_f32<OPK>(r[2 * j + 1])), sc2, a[j]);
+        };
+        uint32_t ra[32], rb[32];
+        ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(lane_addr + t * kAccCols, ra);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           const float b0_cur = b0_next, b1_cur = b1_next;
           if (kb + 1 < p.num_kb) {
@@ -751,50 +825,43 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           }
           if (kb == (p.num_kb > 1 ? 1 : 0) && more && next.expert >= 0 &&
               next.expert < p.num_experts) {
-            // the next tile's expert id has arrived by now: fetch its first b scales early
             const float *n0, *n1;
             bscale_ptrs(next.expert, tc_next.n_blk, n0, n1);
             b0_first = __ldg(n0);
             b1_first = __ldg(n1);
           }
-          ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
-          if (!ok) break;
-          tc_fence_after();
-          // the scale row landed (same transaction barrier as the operand tiles) before the MMA
-          // whose completion was just observed was even issued
+          // this K block's completion was observed before its first load was issued
           const float a_s = as_ring[(kbi % kScaleSlots) * 128 + row_in_tile];
           ++kbi;
           const float s0 = a_s * b0_cur;
           const float s1 = GATED ? a_s * b1_cur : s0;
           const uint32_t tbase = lane_addr + t * kAccCols;
-#pragma unroll
-          for (int pair = 0; pair < 2; ++pair) {
-            uint32_t r0[32], r1[32];
-            tmem_ld32(tbase + 64 * pair, r0);
-            tmem_ld32(tbase + 64 * pair + 32, r1);
-            tmem_ld_wait();
-            if (pair == 1) {
-              // everything of this stage is in registers: hand it back before the last FMAs
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(bar_tempty + 8 * t);
-            }
-            const float sc = pair == 0 ? s0 : s1;
-            const float2 sc2 = make_float2(sc, sc);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              acc[2 * pair][j] = __ffma2_rn(
-                  make_float2(acc_to_f32<OPK>(r0[2 * j]), acc_to_f32<OPK>(r0[2 * j + 1])), sc2,
-                  acc[2 * pair][j]);
-              acc[2 * pair + 1][j] = __ffma2_rn(
-                  make_float2(acc_to_f32<OPK>(r1[2 * j]), acc_to_f32<OPK>(r1[2 * j + 1])), sc2,
-                  acc[2 * pair + 1][j]);
-            }
-          }
+          tmem_ld_wait();
+          tmem_ld32(tbase + 32, rb);
+          fma_chunk(acc[0], ra, s0);
+          tmem_ld_wait();
+          tmem_ld32(tbase + 64, ra);
+          fma_chunk(acc[1], rb, s0);
+          tmem_ld_wait();
+          tmem_ld32(tbase + 96, rb);
+          fma_chunk(acc[2], ra, s1);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * t);
           if (++t == 2) { t = 0; tph ^= 1; }
+          if (kb + 1 < p.num_kb) {
+            ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag, p.status, 4);
+            if (!ok) break;
+            tc_fence_after();
+            tmem_ld32(lane_addr + t * kAccCols, ra);
+          }
+          fma_chunk(acc[3], rb, s1);
         }
         if (!ok) break;
         // ---- finalise ----
+        if (lane == 0) bulk_wait_read();   // the previous tile's bulk stores have left the slots
+        __syncwarp();
         float v[4][32];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -817,7 +884,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[i][j] *= rw;
             }
-            store_chunk(out_stage, p, row_off, col0, ncols, live, lane, v[i]);
+            store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v[i]);
           }
         } else {
           // chunks 0,1 = gate, chunks 2,3 = up of output columns ocol + [0,64)
@@ -851,7 +918,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (EPI == BOLT_EPI_SILU_MUL) {
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-              store_chunk(out_stage, p, row_off, ocol + 32 * i, p.n_half, wr, lane, v[i]);
+              store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n_half, wr,
+                          lane, v[i]);
           } else {
             // 1x128 group quantisation: the two halves exchange their absmax through shared
             // memory (double-buffered by tile parity; the barrier wait is bounded)
@@ -913,6 +981,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 
   // ------------------------------ teardown ------------------------------------
+  if (warp >= 4 && lane == 0) bulk_wait_all();   // bulk stores of this warp's last blocks
   __syncwarp();
   if (*abort_flag) {
     // let bulk copies that are still in flight land before the CTA's memory is released
@@ -950,27 +1019,27 @@ EncodeTiledFn get_encode_fn() {
 }
 
 template <int OPK, bool BS, int EPI>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid,
-           cudaStream_t st) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+           const GemmParams& p, int grid, cudaStream_t st) {
   auto kfn = k_grouped_gemm<OPK, BS, EPI>;
   static bool configured = false;
   if (!configured) {
     BOLT_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured = true;
   }
-  kfn<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, p);
+  kfn<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mc, p);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }
 
 template <int OPK, bool BS>
-int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid,
-               cudaStream_t st) {
+int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+               const GemmParams& p, int grid, cudaStream_t st) {
   switch (epi) {
-    case BOLT_EPI_STORE: return launch<OPK, BS, BOLT_EPI_STORE>(ma, mb, p, grid, st);
-    case BOLT_EPI_SILU_MUL: return launch<OPK, BS, BOLT_EPI_SILU_MUL>(ma, mb, p, grid, st);
+    case BOLT_EPI_STORE: return launch<OPK, BS, BOLT_EPI_STORE>(ma, mb, mc, p, grid, st);
+    case BOLT_EPI_SILU_MUL: return launch<OPK, BS, BOLT_EPI_SILU_MUL>(ma, mb, mc, p, grid, st);
     case BOLT_EPI_SILU_MUL_QUANT:
-      if constexpr (BS) return launch<OPK, true, BOLT_EPI_SILU_MUL_QUANT>(ma, mb, p, grid, st);
+      if constexpr (BS) return launch<OPK, true, BOLT_EPI_SILU_MUL_QUANT>(ma, mb, mc, p, grid, st);
       set_error("grouped_gemm: fused group quantisation needs a block-scaled kind");
       return BOLT_ERR_UNSUPPORTED;
     default: set_error("grouped_gemm: unknown epilogue %d", epi); return BOLT_ERR_INVALID;
@@ -1077,6 +1146,22 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   p.scatter = a->scatter;
   p.c_vec_ok = (reinterpret_cast<uintptr_t>(a->c) % 16 == 0) &&
                ((a->c_ld * (int64_t)dtype_bytes(a->c_dtype)) % 16 == 0);
+  // 16-bit output in sorted row order: blocks of 32 rows x 32 columns leave by bulk tensor
+  // stores (64-byte-swizzled shared-memory source) instead of per-thread stores
+  CUtensorMap mc;
+  memset(&mc, 0, sizeof(mc));
+  p.c_tma_ok = 0;
+  if (p.c_vec_ok && !a->scatter && (a->c_dtype == BOLT_BF16 || a->c_dtype == BOLT_F16)) {
+    const int64_t out_cols = gated ? a->n / 2 : a->n;
+    cuuint64_t dims[2] = {(cuuint64_t)out_cols, (cuuint64_t)a->capacity};
+    cuuint64_t strides[1] = {(cuuint64_t)a->c_ld * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&mc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a->c, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    p.c_tma_ok = (r == CUDA_SUCCESS) ? 1 : 0;   // on failure the per-thread store paths remain
+  }
   p.num_tokens = a->sorted_ids ? a->num_tokens : 1;
   p.topk = a->topk;
   p.mul_routed_weight = a->mul_routed_weight;
@@ -1106,11 +1191,11 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
 
   switch (a->kind) {
     case BOLT_GEMM_BF16:
-    case BOLT_GEMM_F16: return launch_epi<OP_F16, false>(a->epilogue, ma, mb, p, grid, st);
-    case BOLT_GEMM_FP8_BLOCK: return launch_epi<OP_F8, true>(a->epilogue, ma, mb, p, grid, st);
-    case BOLT_GEMM_FP8_CHANNEL: return launch_epi<OP_F8, false>(a->epilogue, ma, mb, p, grid, st);
-    case BOLT_GEMM_INT8_CHANNEL: return launch_epi<OP_I8, false>(a->epilogue, ma, mb, p, grid, st);
-    case BOLT_GEMM_INT8_BLOCK: return launch_epi<OP_I8, true>(a->epilogue, ma, mb, p, grid, st);
+    case BOLT_GEMM_F16: return launch_epi<OP_F16, false>(a->epilogue, ma, mb, mc, p, grid, st);
+    case BOLT_GEMM_FP8_BLOCK: return launch_epi<OP_F8, true>(a->epilogue, ma, mb, mc, p, grid, st);
+    case BOLT_GEMM_FP8_CHANNEL: return launch_epi<OP_F8, false>(a->epilogue, ma, mb, mc, p, grid, st);
+    case BOLT_GEMM_INT8_CHANNEL: return launch_epi<OP_I8, false>(a->epilogue, ma, mb, mc, p, grid, st);
+    case BOLT_GEMM_INT8_BLOCK: return launch_epi<OP_I8, true>(a->epilogue, ma, mb, mc, p, grid, st);
     default: break;
   }
   set_error("grouped_gemm: unsupported kind %d", a->kind);

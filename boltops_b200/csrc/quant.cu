@@ -283,6 +283,118 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint4* __restrict__ s
   }
 }
 
+// ---- quantise a token once, write it to every sorted row that holds one of its routes -----
+// Same arithmetic as k_quant_group (TPG threads share a 1 x group block of one token row); the
+// 8-bit codes and the scale then go straight to rows route_pos[token][k] >= 0 of the
+// expert-sorted layout (scales group-major, [groups, dst_scale_ld]), so the quantised
+// activations never exist in token order.  The tail of the kernel zero-fills the rows below
+// num_valid that hold no token (tile padding).
+template <typename TIn, int QT, bool POW2>
+__global__ void __launch_bounds__(256) k_quant_scatter(
+    const TIn* __restrict__ x, int64_t num_tokens, int cols, int tpg,
+    const int32_t* __restrict__ route_pos, int slots, const int32_t* __restrict__ sorted_ids,
+    const int32_t* __restrict__ num_valid, int capacity,
+    typename QTraits<QT>::type* __restrict__ dst, float* __restrict__ dst_scale,
+    int64_t dst_scale_ld, int64_t quant_blocks) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  using VIn = Vec<TIn, VEC>;
+  using VOut = Vec<typename QTraits<QT>::type, VEC>;
+  const int row_vecs = cols / VEC;
+  if (blockIdx.x < quant_blocks) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t token = tid / row_vecs;
+    const int vec_in_row = (int)(tid - token * row_vecs);
+    const bool live = token < num_tokens;
+    VIn v;
+    float amax = 0.f;
+    if (live) {
+      v = reinterpret_cast<const VIn*>(x)[tid];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(to_f32(v.v[i])));
+    }
+    for (int o = tpg >> 1; o > 0; o >>= 1)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!live) return;
+    float scale, inv;
+    scale_from_amax<QT, POW2>(amax, scale, inv);
+    VOut o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o.v[i] = quant_one<QT, POW2>(to_f32(v.v[i]), inv);
+    const bool leader = (vec_in_row % tpg) == 0;
+    const int grp = vec_in_row / tpg;
+    // eight routes at a time: all positions first, then the independent stores
+    for (int k0 = 0; k0 < slots; k0 += 8) {
+      int pos[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        pos[j] = (k0 + j < slots) ? __ldg(route_pos + token * slots + k0 + j) : -1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (pos[j] < 0 || pos[j] >= capacity) continue;
+        reinterpret_cast<VOut*>(dst)[(int64_t)pos[j] * row_vecs + vec_in_row] = o;
+        if (leader) dst_scale[(int64_t)grp * dst_scale_ld + pos[j]] = scale;
+      }
+    }
+    return;
+  }
+  // padding rows
+  const int valid = min(*num_valid, capacity);
+  const int groups = row_vecs / tpg;
+  const int pad_blocks = gridDim.x - (int)quant_blocks;
+  VOut zero;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) zero.v[i] = 0;
+  for (int row = blockIdx.x - (int)quant_blocks; row < valid; row += pad_blocks) {
+    const int token = sorted_ids[row] & 0xFFFFFF;
+    if (token < num_tokens) continue;
+    VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)row * row_vecs;
+    for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = zero;
+    for (int g = threadIdx.x; g < groups; g += blockDim.x)
+      dst_scale[(int64_t)g * dst_scale_ld + row] = 0.f;
+  }
+}
+
+template <typename TIn, int QT, bool POW2>
+int launch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group,
+                         const int32_t* route_pos, int slots, const int32_t* sorted_ids,
+                         const int32_t* num_valid, int capacity, void* dst, float* dst_scale,
+                         int64_t dst_scale_ld, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  const int tpg = group / VEC;
+  const int64_t threads = num_tokens * (cols / VEC);
+  const int64_t quant_blocks = (threads + 255) / 256;
+  const int pad_blocks = 148 * 4;
+  BOLT_REQUIRE(quant_blocks + pad_blocks < (int64_t)1 << 31, "quant_scatter: too many elements");
+  k_quant_scatter<TIn, QT, POW2><<<(unsigned)(quant_blocks + pad_blocks), 256, 0, st>>>(
+      static_cast<const TIn*>(x), num_tokens, cols, tpg, route_pos, slots, sorted_ids, num_valid,
+      capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale, dst_scale_ld,
+      quant_blocks);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+template <typename TIn>
+int dispatch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group, int q_dtype,
+                           int power2, const int32_t* route_pos, int slots,
+                           const int32_t* sorted_ids, const int32_t* num_valid, int capacity,
+                           void* dst, float* dst_scale, int64_t dst_scale_ld, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  const int tpg = group / VEC;
+  BOLT_REQUIRE(group % VEC == 0 && tpg >= 1 && tpg <= 32 && (tpg & (tpg - 1)) == 0,
+               "quant_scatter: group %d must be a power-of-two multiple of %d elements up to %d",
+               group, VEC, 32 * VEC);
+#define BOLT_QS(QT, P2)                                                                         \
+  return launch_quant_scatter<TIn, QT, P2>(x, num_tokens, cols, group, route_pos, slots,        \
+                                           sorted_ids, num_valid, capacity, dst, dst_scale,     \
+                                           dst_scale_ld, st)
+  if (q_dtype == BOLT_FP8_E4M3) {
+    if (power2) BOLT_QS(BOLT_FP8_E4M3, true);
+    BOLT_QS(BOLT_FP8_E4M3, false);
+  }
+  BOLT_QS(BOLT_INT8, false);
+#undef BOLT_QS
+}
+
 }  // namespace
 }  // namespace bolt
 
@@ -329,4 +441,46 @@ extern "C" int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
                                       static_cast<uint4*>(dst), dst_scale, dst_scale_ld);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
+}
+
+extern "C" int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_tokens, int cols,
+                                       int group, int q_dtype, int power2,
+                                       const int32_t* route_pos, int slots,
+                                       const int32_t* sorted_ids, const int32_t* num_valid_ids,
+                                       int capacity, void* dst, float* dst_scale,
+                                       int64_t dst_scale_ld, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(num_tokens >= 0 && cols > 0 && capacity >= 0 && slots > 0,
+               "quant_scatter: bad shape");
+  BOLT_REQUIRE(group > 0 && cols % group == 0, "quant_scatter: group %d does not divide cols %d",
+               group, cols);
+  BOLT_REQUIRE(q_dtype == BOLT_FP8_E4M3 || q_dtype == BOLT_INT8, "quant_scatter: bad q_dtype %d",
+               q_dtype);
+  BOLT_REQUIRE(!power2 || q_dtype == BOLT_FP8_E4M3,
+               "quant_scatter: power-of-two scales need e4m3");
+  BOLT_REQUIRE(dst_scale_ld >= capacity, "quant_scatter: dst_scale_ld too small");
+  if (capacity == 0) return BOLT_OK;
+  BOLT_REQUIRE(dst && dst_scale && sorted_ids && num_valid_ids &&
+                   (num_tokens == 0 || (x && route_pos)),
+               "quant_scatter: null pointer");
+  BOLT_REQUIRE((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0,
+               "quant_scatter: buffers must be 16-byte aligned");
+  switch (x_dtype) {
+    case BOLT_BF16:
+      return dispatch_quant_scatter<__nv_bfloat16>(x, num_tokens, cols, group, q_dtype, power2,
+                                                   route_pos, slots, sorted_ids, num_valid_ids,
+                                                   capacity, dst, dst_scale, dst_scale_ld, st);
+    case BOLT_F16:
+      return dispatch_quant_scatter<__half>(x, num_tokens, cols, group, q_dtype, power2,
+                                            route_pos, slots, sorted_ids, num_valid_ids, capacity,
+                                            dst, dst_scale, dst_scale_ld, st);
+    case BOLT_F32:
+      return dispatch_quant_scatter<float>(x, num_tokens, cols, group, q_dtype, power2, route_pos,
+                                           slots, sorted_ids, num_valid_ids, capacity, dst,
+                                           dst_scale, dst_scale_ld, st);
+    default:
+      set_error("quant_scatter: unsupported input dtype %d", x_dtype);
+      return BOLT_ERR_INVALID;
+  }
 }

@@ -230,9 +230,9 @@ def fused_experts_impl(
         wts = topk_weights[begin:end]
 
         # ---- sort -----------------------------------------------------------------------
-        route_pos = None
-        if not no_combine:
-            route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
+        # inverse permutation of the sort: the combine gathers through it, and the block
+        # quantiser scatters through it
+        route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
         with _Stage("sort"):
             sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
                 ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
@@ -241,7 +241,14 @@ def fused_experts_impl(
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
         a_scale = None
-        if quantised:
+        if (quantised and block_mode
+                and x.dtype in (torch.float16, torch.bfloat16, torch.float32)):
+            # quantise each token once and write it straight to its sorted rows
+            with _Stage("quant_a1"):
+                a_sorted, a_scale = ops.quant_scatter_rows(
+                    x, 128, q_dtype, route_pos, sorted_ids, num_valid, cap,
+                    scale_ue8m0=use_ue8m0)
+        elif quantised:
             with _Stage("quant_a1"):
                 if x.dtype in (torch.float16, torch.bfloat16, torch.float32):
                     if block_mode:

@@ -196,6 +196,29 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Te
     return dst, dst_scale
 
 
+def quant_scatter_rows(x: torch.Tensor, group: int, q_dtype: torch.dtype, route_pos: torch.Tensor,
+                       sorted_ids: torch.Tensor, num_valid: torch.Tensor, capacity: int,
+                       scale_ue8m0: bool = False):
+    """Quantise ``x`` [M, cols] per 1 x ``group`` block and write every token to the sorted rows
+    ``route_pos[m, k] >= 0`` in one pass.  Returns ``(dst [capacity, cols], dst_scale
+    [cols/group, capacity])``; tile-padding rows are zero."""
+    _require_cuda(x, route_pos, sorted_ids, num_valid)
+    lib = _cabi.load()
+    x = x.contiguous()
+    m, cols = x.shape
+    assert route_pos.dtype == torch.int32 and route_pos.is_contiguous() and route_pos.shape[0] == m
+    dst = torch.empty((capacity, cols), dtype=q_dtype, device=x.device)
+    dst_scale = torch.empty((cols // group, capacity), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.bolt_quant_scatter_rows(ptr(x), dtype_code(x.dtype), m, cols, group,
+                                          dtype_code(q_dtype), int(scale_ue8m0), ptr(route_pos),
+                                          route_pos.shape[1], ptr(sorted_ids), ptr(num_valid),
+                                          capacity, ptr(dst), ptr(dst_scale), capacity,
+                                          stream_of(x)))
+    _count()
+    return dst, dst_scale
+
+
 def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
             routed_scaling_factor: float = 1.0,
             router_weights: Optional[torch.Tensor] = None) -> torch.Tensor:

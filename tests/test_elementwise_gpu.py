@@ -208,3 +208,32 @@ def test_moe_fused_gate(m, e, groups, topk_group, topk, shared):
             assert abs(a - b) <= 1e-5 * max(1.0, abs(b))
     if shared:
         assert (i[:, -1] == e).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("q_dtype", [torch.float8_e4m3fn, torch.int8])
+def test_quant_scatter_equals_quant_then_gather(dtype, q_dtype):
+    """The fused quantise+scatter writes the same bytes as quantising and gathering, and zeros
+    in the rows that only pad a tile."""
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(5)
+    m, h, e, k = 77, 512, 8, 3
+    x = (torch.randn(m, h) * 3).to(dtype).cuda()
+    _, ids = O.make_routing(m, e, k, 11)
+    ids[3, 1] = -1                                   # a masked route
+    ids = ids.cuda()
+    w = torch.rand(m, k).cuda()
+    pos = torch.empty((m, k), dtype=torch.int32, device="cuda")
+    s_ids, _, _, nv, _, _ = ops.moe_sorting_ck(ids, w, e, None, None, 128, None,
+                                               alloc_moe_buf=False, route_pos=pos)
+    cap = s_ids.shape[0]
+    x_q, x_s = ops.per_block_quant(x, 128, q_dtype)
+    ref, ref_s = ops.gather_rows(x_q, s_ids, nv, cap, x_s)
+    got, got_s = ops.quant_scatter_rows(x, 128, q_dtype, pos, s_ids, nv, cap)
+    n = int(nv.item())
+    assert torch.equal(got[:n].view(torch.uint8).cpu(), ref[:n].view(torch.uint8).cpu())
+    assert torch.equal(got_s[:, :n].cpu(), ref_s[:, :n].cpu())
+    pad = ((s_ids[:n] & 0xFFFFFF) >= m).cpu()
+    assert pad.any()
+    assert (got[:n].view(torch.uint8).cpu()[pad] == 0).all()
+    assert (got_s[:, :n].cpu()[:, pad] == 0).all()
