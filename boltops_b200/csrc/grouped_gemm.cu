@@ -35,7 +35,10 @@ namespace bolt {
 namespace {
 
 constexpr int kThreads = 384;
-constexpr int kStages = 3;
+// shared-memory operand stages: the block-scaled kinds spend ~950 cycles per K block (three
+// stages cover the load latency, and the space goes to bulk-store slots); the others stream a
+// K block every ~500 cycles and need four
+constexpr int stages_of(bool block_scaled) { return block_scaled ? 3 : 4; }
 constexpr int kBM = 128;
 constexpr int kAccCols = 256;           // accumulator columns per tile
 constexpr int kHalfCols = 128;          // columns of one independently scheduled half
@@ -45,10 +48,15 @@ constexpr int kBBytes = kAccCols * 128; // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kScaleSlots = 8;           // ring of per-K-block activation-scale rows (512 B each)
 constexpr int kOutSlotBytes = 32 * 64;    // one 32-row x 64-byte block as a bulk store reads it
-constexpr int kOutStageBytes = 4 * kOutSlotBytes;  // per epilogue warp: one slot per 32-column chunk
-                                                   // (the padded 32 x 80 B staging layout fits in it too)
-constexpr int kCtrlBytes = 4096 + kScaleSlots * 512 + 8 * kOutStageBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;  // +1024 alignment slack
+// per epilogue warp: block-scaled kinds one slot per 32-column chunk of a tile, the others one
+// slot that is reclaimed chunk by chunk (their epilogue overlaps the next tile's MMAs anyway)
+constexpr int out_slots_of(bool block_scaled) { return block_scaled ? 4 : 1; }
+constexpr int out_stage_bytes_of(bool block_scaled) { return block_scaled ? 4 * kOutSlotBytes : 2560; }
+// (the padded 32 x 80 B layout of the staged fallback path fits in either)
+constexpr int smem_bytes_of(bool block_scaled) {
+  return stages_of(block_scaled) * kStageBytes + 4096 + kScaleSlots * 512 +
+         8 * out_stage_bytes_of(block_scaled) + 1024;  // +1024 alignment slack
+}
 
 enum OpKind { OP_F16 = 0, OP_F8 = 1, OP_I8 = 2 };
 
@@ -253,11 +261,6 @@ __device__ __forceinline__ float acc_to_f32(uint32_t raw) {
   return OPK == OP_I8 ? __int2float_rn((int)raw) : __uint_as_float(raw);
 }
 
-__device__ __forceinline__ float round_mid(float v, int dt) {
-  if (dt == BOLT_BF16) return __bfloat162float(__float2bfloat16_rn(v));
-  if (dt == BOLT_F16) return __half2float(__float2half_rn(v));
-  return v;
-}
 __device__ __forceinline__ float load_bias(const void* bias, int dt, int64_t idx) {
   if (dt == BOLT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[idx]);
   if (dt == BOLT_F16) return __half2float(static_cast<const __half*>(bias)[idx]);
@@ -379,6 +382,7 @@ __device__ __forceinline__ void store_rows_tma(uint8_t* stage, const uint4 (&w)[
 // 32 fp32 values -> c_dtype at column col0 of this lane's row: by TMA when the whole 32-row
 // block is written, else staged through shared memory when possible.  tile_row0 = output row
 // of lane 0 (only meaningful when rows are not scattered).
+template <int SLOTS>
 __device__ __forceinline__ void store_chunk(uint8_t* stage, int slot, const GemmParams& p,
                                             const CUtensorMap* map_c, int tile_row0,
                                             int64_t row_off, int col0, int ncols, bool live,
@@ -386,7 +390,11 @@ __device__ __forceinline__ void store_chunk(uint8_t* stage, int slot, const Gemm
   if (p.c_tma_ok && col0 < ncols && __all_sync(0xffffffffu, live)) {   // warp-uniform
     uint4 w[4];
     pack32_16bit(v, p.c_dtype, w);
-    store_rows_tma(stage + slot * kOutSlotBytes, w, map_c, col0, tile_row0, lane);
+    if (SLOTS == 1) {   // single slot: wait until the previous chunk's copy has read it
+      if (lane == 0) bulk_wait_read();
+      __syncwarp();
+    }
+    store_rows_tma(stage + (SLOTS == 1 ? 0 : slot) * kOutSlotBytes, w, map_c, col0, tile_row0, lane);
   } else if (p.c_vec_ok && p.c_dtype != BOLT_F32 && col0 + 32 <= ncols) {   // warp-uniform
     uint4 w[4];
     pack32_16bit(v, p.c_dtype, w);
@@ -488,6 +496,8 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   constexpr bool GATED = EPI != BOLT_EPI_STORE;
   constexpr int kBKElems = OPK == OP_F16 ? 64 : 128;
   constexpr bool CHANNEL = (OPK != OP_F16) && !BS;
+  constexpr int kStages = stages_of(BS);
+  constexpr int kSlots = out_slots_of(BS);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -641,7 +651,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * q) << 16) + h * kHalfCols;
     const bool has_ids = p.sorted_ids != nullptr;
     const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
-    uint8_t* out_stage = ctrl + 4096 + kScaleSlots * 512 + (warp - 4) * kOutStageBytes;
+    uint8_t* out_stage = ctrl + 4096 + kScaleSlots * 512 + (warp - 4) * out_stage_bytes_of(BS);
     int t = 0;
     uint32_t tph = 0, xph = 0, kbi = 0;
     bool ok = true;
@@ -744,7 +754,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] *= rw;
             }
-            store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v);
+            store_chunk<kSlots>(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v);
           }
         } else {
 #pragma unroll 1
@@ -784,7 +794,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
             silu_mul32_dyn(g, u, p.mid_dtype);
-            store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, col0, p.n_half, wr, lane, g);
+            store_chunk<kSlots>(out_stage, i, p, &tma_c, tile_row0, row_off, col0, p.n_half, wr, lane, g);
           }
         }
         tc_fence_before();
@@ -884,7 +894,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[i][j] *= rw;
             }
-            store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v[i]);
+            store_chunk<kSlots>(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v[i]);
           }
         } else {
           // chunks 0,1 = gate, chunks 2,3 = up of output columns ocol + [0,64)
@@ -918,7 +928,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (EPI == BOLT_EPI_SILU_MUL) {
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-              store_chunk(out_stage, i, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n_half, wr,
+              store_chunk<kSlots>(out_stage, i, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n_half, wr,
                           lane, v[i]);
           } else {
             // 1x128 group quantisation: the two halves exchange their absmax through shared
@@ -1024,10 +1034,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
   auto kfn = k_grouped_gemm<OPK, BS, EPI>;
   static bool configured = false;
   if (!configured) {
-    BOLT_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    BOLT_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   smem_bytes_of(BS)));
     configured = true;
   }
-  kfn<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mc, p);
+  kfn<<<grid, kThreads, smem_bytes_of(BS), st>>>(ma, mb, mc, p);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }
