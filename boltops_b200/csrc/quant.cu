@@ -283,34 +283,69 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint4* __restrict__ s
   }
 }
 
+// Zero-fill the rows below num_valid that hold no token (tile padding).  Warp-granular: every
+// lane tests one row of a 32-row window, the warp then clears the rows that were flagged, so no
+// thread walks the id list serially.  `pad_warp` / `pad_warps` = this warp's index / count among
+// the warps doing this job.
+template <typename QTy, int VEC>
+__device__ __forceinline__ void zero_pad_rows(const int32_t* __restrict__ sorted_ids,
+                                              int64_t num_tokens, int valid, int row_vecs,
+                                              int groups, QTy* __restrict__ dst,
+                                              float* __restrict__ dst_scale, int64_t dst_scale_ld,
+                                              int pad_warp, int pad_warps) {
+  using VOut = Vec<QTy, VEC>;
+  const int lane = threadIdx.x & 31;
+  VOut zero;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) zero.v[i] = 0;
+  for (int row0 = pad_warp * 32; row0 < valid; row0 += pad_warps * 32) {
+    const int row = row0 + lane;
+    const bool is_pad = row < valid && (sorted_ids[row] & 0xFFFFFF) >= num_tokens;
+    unsigned mask = __ballot_sync(0xffffffffu, is_pad);
+    while (mask) {
+      const int r = row0 + __ffs(mask) - 1;
+      mask &= mask - 1;
+      VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)r * row_vecs;
+      for (int i = lane; i < row_vecs; i += 32) d[i] = zero;
+      for (int g = lane; g < groups; g += 32) dst_scale[(int64_t)g * dst_scale_ld + r] = 0.f;
+    }
+  }
+}
+
 // ---- quantise a token once, write it to every sorted row that holds one of its routes -----
 // Same arithmetic as k_quant_group (TPG threads share a 1 x group block of one token row); the
 // 8-bit codes and the scale then go straight to rows route_pos[token][k] >= 0 of the
 // expert-sorted layout (scales group-major, [groups, dst_scale_ld]), so the quantised
 // activations never exist in token order.  The tail of the kernel zero-fills the rows below
 // num_valid that hold no token (tile padding).
-template <typename TIn, int QT, bool POW2>
+template <typename TIn, int QT, bool POW2, int W>
 __global__ void __launch_bounds__(256) k_quant_scatter(
     const TIn* __restrict__ x, int64_t num_tokens, int cols, int tpg,
     const int32_t* __restrict__ route_pos, int slots, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_valid, int capacity,
     typename QTraits<QT>::type* __restrict__ dst, float* __restrict__ dst_scale,
     int64_t dst_scale_ld, int64_t quant_blocks) {
+  // a thread owns W input vectors = EPT consecutive elements (EPT = 16: one 16-byte store per
+  // route); tpg threads share a group
   constexpr int VEC = 16 / sizeof(TIn);
+  constexpr int EPT = VEC * W;
   using VIn = Vec<TIn, VEC>;
-  using VOut = Vec<typename QTraits<QT>::type, VEC>;
-  const int row_vecs = cols / VEC;
+  using VOut = Vec<typename QTraits<QT>::type, EPT>;
+  const int row_units = cols / EPT;
   if (blockIdx.x < quant_blocks) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t token = tid / row_vecs;
-    const int vec_in_row = (int)(tid - token * row_vecs);
+    const int64_t token = tid / row_units;
+    const int unit_in_row = (int)(tid - token * row_units);
     const bool live = token < num_tokens;
-    VIn v;
+    VIn v[W];
     float amax = 0.f;
     if (live) {
-      v = reinterpret_cast<const VIn*>(x)[tid];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(to_f32(v.v[i])));
+      for (int w = 0; w < W; ++w) {
+        v[w] = reinterpret_cast<const VIn*>(x)[tid * W + w];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(to_f32(v[w].v[i])));
+      }
     }
     for (int o = tpg >> 1; o > 0; o >>= 1)
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -319,9 +354,12 @@ __global__ void __launch_bounds__(256) k_quant_scatter(
     scale_from_amax<QT, POW2>(amax, scale, inv);
     VOut o;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) o.v[i] = quant_one<QT, POW2>(to_f32(v.v[i]), inv);
-    const bool leader = (vec_in_row % tpg) == 0;
-    const int grp = vec_in_row / tpg;
+    for (int w = 0; w < W; ++w)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)
+        o.v[w * VEC + i] = quant_one<QT, POW2>(to_f32(v[w].v[i]), inv);
+    const bool leader = (unit_in_row % tpg) == 0;
+    const int grp = unit_in_row / tpg;
     // eight routes at a time: all positions first, then the independent stores
     for (int k0 = 0; k0 < slots; k0 += 8) {
       int pos[8];
@@ -331,27 +369,88 @@ __global__ void __launch_bounds__(256) k_quant_scatter(
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (pos[j] < 0 || pos[j] >= capacity) continue;
-        reinterpret_cast<VOut*>(dst)[(int64_t)pos[j] * row_vecs + vec_in_row] = o;
+        reinterpret_cast<VOut*>(dst)[(int64_t)pos[j] * row_units + unit_in_row] = o;
         if (leader) dst_scale[(int64_t)grp * dst_scale_ld + pos[j]] = scale;
       }
     }
     return;
   }
   // padding rows
-  const int valid = min(*num_valid, capacity);
-  const int groups = row_vecs / tpg;
   const int pad_blocks = gridDim.x - (int)quant_blocks;
-  VOut zero;
+  zero_pad_rows<typename QTraits<QT>::type, EPT>(
+      sorted_ids, num_tokens, min(*num_valid, capacity), row_units, row_units / tpg, dst,
+      dst_scale, dst_scale_ld, (int)(blockIdx.x - quant_blocks) * 8 + (threadIdx.x >> 5),
+      pad_blocks * 8);
+}
+
+// Same for groups that span up to 8 x 32 vectors (per-token quantisation of mid-sized rows): one
+// warp owns a group, keeps it in registers between the absmax pass and the stores.
+template <typename TIn, int QT, bool POW2, int NV>
+__global__ void __launch_bounds__(256) k_quant_scatter_warp(
+    const TIn* __restrict__ x, int64_t num_tokens, int cols, int group,
+    const int32_t* __restrict__ route_pos, int slots, const int32_t* __restrict__ sorted_ids,
+    const int32_t* __restrict__ num_valid, int capacity,
+    typename QTraits<QT>::type* __restrict__ dst, float* __restrict__ dst_scale,
+    int64_t dst_scale_ld, int quant_blocks) {
+  constexpr int VEC = 16 / sizeof(TIn);
+  using VIn = Vec<TIn, VEC>;
+  using VOut = Vec<typename QTraits<QT>::type, VEC>;
+  const int lane = threadIdx.x & 31;
+  const int groups = cols / group;
+  const int nvec = group / VEC;
+  const int row_vecs = cols / VEC;
+  if ((int)blockIdx.x < quant_blocks) {
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)quant_blocks * blockDim.x) >> 5;
+    const int64_t num_groups = num_tokens * groups;
+    for (int64_t g = warp0; g < num_groups; g += nwarps) {
+      const int64_t token = g / groups;
+      const int grp = (int)(g - token * groups);
+      const VIn* xr = reinterpret_cast<const VIn*>(x + g * (int64_t)group);
+      VIn cache[NV];
+      float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) zero.v[i] = 0;
-  for (int row = blockIdx.x - (int)quant_blocks; row < valid; row += pad_blocks) {
-    const int token = sorted_ids[row] & 0xFFFFFF;
-    if (token < num_tokens) continue;
-    VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)row * row_vecs;
-    for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = zero;
-    for (int g = threadIdx.x; g < groups; g += blockDim.x)
-      dst_scale[(int64_t)g * dst_scale_ld + row] = 0.f;
+      for (int j = 0; j < NV; ++j) {
+        const int i = lane + j * 32;
+        if (i < nvec) {
+          cache[j] = xr[i];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(to_f32(cache[j].v[e])));
+        }
+      }
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      float scale, inv;
+      scale_from_amax<QT, POW2>(amax, scale, inv);
+      VOut out[NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if (lane + j * 32 < nvec) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            out[j].v[e] = quant_one<QT, POW2>(to_f32(cache[j].v[e]), inv);
+        }
+      }
+      // lane k holds the position of route k (slots <= 32 per pass)
+      for (int k0 = 0; k0 < slots; k0 += 32) {
+        const int mine = (k0 + lane < slots) ? __ldg(route_pos + token * slots + k0 + lane) : -1;
+        const int nk = min(32, slots - k0);
+        for (int k = 0; k < nk; ++k) {
+        const int pos = __shfl_sync(0xffffffffu, mine, k);
+        if (pos < 0 || pos >= capacity) continue;
+        VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)pos * row_vecs + grp * nvec;
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+          if (lane + j * 32 < nvec) d[lane + j * 32] = out[j];
+        if (lane == 0) dst_scale[(int64_t)grp * dst_scale_ld + pos] = scale;
+        }
+      }
+    }
+    return;
   }
+  const int pad_blocks = gridDim.x - quant_blocks;
+  zero_pad_rows<typename QTraits<QT>::type, VEC>(
+      sorted_ids, num_tokens, min(*num_valid, capacity), row_vecs, groups, dst, dst_scale,
+      dst_scale_ld, ((int)blockIdx.x - quant_blocks) * 8 + (threadIdx.x >> 5), pad_blocks * 8);
 }
 
 template <typename TIn, int QT, bool POW2>
@@ -361,14 +460,39 @@ int launch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group,
                          int64_t dst_scale_ld, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(TIn);
   const int tpg = group / VEC;
-  const int64_t threads = num_tokens * (cols / VEC);
-  const int64_t quant_blocks = (threads + 255) / 256;
   const int pad_blocks = 148 * 4;
+  if (tpg > 32 || (tpg & (tpg - 1)) != 0) {
+    // a warp per group, groups strided over a capped grid
+    const int64_t num_groups = num_tokens * (cols / group);
+    int64_t qb = (num_groups + 7) / 8;
+    const int64_t cap = (int64_t)sm_count_of_current_device() * 32;
+    if (qb > cap) qb = cap;
+    if (qb < 1) qb = 1;
+    k_quant_scatter_warp<TIn, QT, POW2, 8><<<(unsigned)(qb + pad_blocks), 256, 0, st>>>(
+        static_cast<const TIn*>(x), num_tokens, cols, group, route_pos, slots, sorted_ids,
+        num_valid, capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale,
+        dst_scale_ld, (int)qb);
+    BOLT_LAUNCH_CHECK();
+    return BOLT_OK;
+  }
+  // 16 output bytes per thread when the group allows it (at least two threads per group stay)
+  constexpr int W16 = 16 / VEC;
+  const bool wide = (group % 16 == 0) && (group / 16) >= 1 && ((group / 16) & (group / 16 - 1)) == 0;
+  const int ept = wide ? 16 : VEC;
+  const int64_t threads = num_tokens * (cols / ept);
+  const int64_t quant_blocks = (threads + 255) / 256;
   BOLT_REQUIRE(quant_blocks + pad_blocks < (int64_t)1 << 31, "quant_scatter: too many elements");
-  k_quant_scatter<TIn, QT, POW2><<<(unsigned)(quant_blocks + pad_blocks), 256, 0, st>>>(
-      static_cast<const TIn*>(x), num_tokens, cols, tpg, route_pos, slots, sorted_ids, num_valid,
-      capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale, dst_scale_ld,
-      quant_blocks);
+  if (wide) {
+    k_quant_scatter<TIn, QT, POW2, W16><<<(unsigned)(quant_blocks + pad_blocks), 256, 0, st>>>(
+        static_cast<const TIn*>(x), num_tokens, cols, group / 16, route_pos, slots, sorted_ids,
+        num_valid, capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale,
+        dst_scale_ld, quant_blocks);
+  } else {
+    k_quant_scatter<TIn, QT, POW2, 1><<<(unsigned)(quant_blocks + pad_blocks), 256, 0, st>>>(
+        static_cast<const TIn*>(x), num_tokens, cols, tpg, route_pos, slots, sorted_ids,
+        num_valid, capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale,
+        dst_scale_ld, quant_blocks);
+  }
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }
@@ -380,9 +504,9 @@ int dispatch_quant_scatter(const void* x, int64_t num_tokens, int cols, int grou
                            void* dst, float* dst_scale, int64_t dst_scale_ld, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(TIn);
   const int tpg = group / VEC;
-  BOLT_REQUIRE(group % VEC == 0 && tpg >= 1 && tpg <= 32 && (tpg & (tpg - 1)) == 0,
-               "quant_scatter: group %d must be a power-of-two multiple of %d elements up to %d",
-               group, VEC, 32 * VEC);
+  BOLT_REQUIRE(group % VEC == 0 && tpg >= 1 && tpg <= 8 * 32,
+               "quant_scatter: group %d must be a multiple of %d elements, at most %d", group,
+               VEC, 8 * 32 * VEC);
 #define BOLT_QS(QT, P2)                                                                         \
   return launch_quant_scatter<TIn, QT, P2>(x, num_tokens, cols, group, route_pos, slots,        \
                                            sorted_ids, num_valid, capacity, dst, dst_scale,     \

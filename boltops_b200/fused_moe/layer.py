@@ -249,6 +249,9 @@ def fused_experts_impl(
                     x, 128, q_dtype, route_pos, sorted_ids, num_valid, cap,
                     scale_ue8m0=use_ue8m0)
         elif quantised:
+            # per-token scales: quantise, then gather (a row-centric gather writes the sorted rows
+            # faster than a token-centric scatter of whole rows; measured 0.131 vs 0.157 ms at
+            # 16384 x 2048)
             with _Stage("quant_a1"):
                 if x.dtype in (torch.float16, torch.bfloat16, torch.float32):
                     if block_mode:

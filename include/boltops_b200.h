@@ -211,10 +211,12 @@ int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
                      float* dst_scale, int64_t dst_scale_ld, void* stream);
 
 /* bolt_quant_rows and bolt_gather_rows in one pass for 1 x group quantisation (group a
- * power-of-two number of 16-byte vectors, e.g. 128): every token is quantised once and its codes
+ * multiple of the 16-byte input vector, at most 256 vectors: 128-wide blocks as well as whole
+ * rows up to 2048 bf16 / 1024 fp32 elements): every token is quantised once and its codes
  * and scales are written to the sorted rows route_pos[token][k] >= 0 (route_pos as produced by
  * bolt_moe_sort_ck, [num_tokens, slots]); rows below num_valid_ids[0] that hold no token are
- * zero-filled.  dst [capacity, cols] 8-bit, dst_scale [cols/group, dst_scale_ld] fp32.
+ * zero-filled.  dst [capacity, cols] 8-bit, dst_scale [cols/group, dst_scale_ld] fp32 (one
+ * group per row: a plain [capacity] vector).
  * Same arithmetic and the same reference functions as bolt_quant_rows.
  */
 int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_tokens, int cols, int group,

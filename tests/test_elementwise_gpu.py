@@ -212,7 +212,8 @@ def test_moe_fused_gate(m, e, groups, topk_group, topk, shared):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("q_dtype", [torch.float8_e4m3fn, torch.int8])
-def test_quant_scatter_equals_quant_then_gather(dtype, q_dtype):
+@pytest.mark.parametrize("group", [128, 512])      # 1 x 128 blocks / one scale per token
+def test_quant_scatter_equals_quant_then_gather(dtype, q_dtype, group):
     """The fused quantise+scatter writes the same bytes as quantising and gathering, and zeros
     in the rows that only pad a tile."""
     from boltops_b200.fused_moe import ops
@@ -227,9 +228,10 @@ def test_quant_scatter_equals_quant_then_gather(dtype, q_dtype):
     s_ids, _, _, nv, _, _ = ops.moe_sorting_ck(ids, w, e, None, None, 128, None,
                                                alloc_moe_buf=False, route_pos=pos)
     cap = s_ids.shape[0]
-    x_q, x_s = ops.per_block_quant(x, 128, q_dtype)
+    x_q, x_s = ops.per_block_quant(x, group, q_dtype)
     ref, ref_s = ops.gather_rows(x_q, s_ids, nv, cap, x_s)
-    got, got_s = ops.quant_scatter_rows(x, 128, q_dtype, pos, s_ids, nv, cap)
+    ref_s = ref_s.reshape(h // group, cap)
+    got, got_s = ops.quant_scatter_rows(x, group, q_dtype, pos, s_ids, nv, cap)
     n = int(nv.item())
     assert torch.equal(got[:n].view(torch.uint8).cpu(), ref[:n].view(torch.uint8).cpu())
     assert torch.equal(got_s[:, :n].cpu(), ref_s[:, :n].cpu())
