@@ -523,6 +523,13 @@ def main():
         ep_stats["local_stage_ms"] = layer.STAGE_TIMER.summary()
         layer.STAGE_TIMER = None
         ep.profile = False
+        # load balance: routes each rank's experts receive from the whole job (the Zipf workload
+        # is measured as it comes, not rebalanced)
+        owner = torch.div(ids.long(), cfg["E"] // world, rounding_mode="floor")
+        per_rank = torch.bincount(owner.flatten(), minlength=world)[:world].to(torch.float64)
+        dist.all_reduce(per_rank)
+        ep_stats["routes_per_rank"] = dict(max=float(per_rank.max()), mean=float(per_rank.mean()),
+                                           max_over_mean=float(per_rank.max() / per_rank.mean()))
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
