@@ -386,6 +386,9 @@ def main():
         from boltops_b200.fused_moe.ep import ExpertParallelMoE
 
         ep = ExpertParallelMoE(dist.group.WORLD, E, device)
+        # every rank brings the same number of tokens here, so decode-sized batches may take the
+        # replicated-token path (no host round trips); the headline batch stays on the dispatch
+        ep.replicate_below = 4096
 
         def step(h, w, i):
             return ep.forward(h, w1, w2, w, i, **kwargs)

@@ -56,6 +56,12 @@ class ExpertParallelMoE:
         self.last_stats = {}
         self.profile = False      # set True to fill last_stats["ms"] with CUDA-event stage times
         self.quantize_dispatch = True   # w8a8 experts: send 8-bit codes + scales, not 16-bit rows
+        # Small batches (decode): when every rank brings the SAME number of tokens and
+        # tokens * world <= replicate_below, skip the dispatch (two host round trips and two
+        # variable all-to-alls) and use the reference's replicated-token scheme instead:
+        # all-gather the tokens, run the masked local layer on all of them, reduce-scatter
+        # the partial outputs.  0 = never (the caller must guarantee equal token counts).
+        self.replicate_below = 0
 
     # -- index construction ---------------------------------------------------------------
     def plan(self, topk_ids: torch.Tensor):
@@ -105,9 +111,47 @@ class ExpertParallelMoE:
         send_split, recv_split = both.tolist()          # one host synchronisation for both
         return send_split, recv_split
 
+    # -- small batches: replicated tokens, no dispatch ---------------------------------------
+    def forward_replicated(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids,
+                           **kwargs):
+        """All ranks hold the same number of tokens.  Partial rows leave the local layer in the
+        output dtype (as in the dispatch path), are summed over the ranks in fp32 and rounded
+        once.  No host synchronisation."""
+        m, h = hidden_states.shape
+        world = self.world
+        dev = hidden_states.device
+        out_dtype = kwargs.get("output_dtype") or hidden_states.dtype
+
+        def gather(t):
+            t = t.contiguous()
+            full = torch.empty((world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype,
+                               device=dev)
+            dist.all_gather_into_tensor(full, t, group=self.group)
+            return full
+
+        all_h = gather(hidden_states)
+        all_w = gather(topk_weights.to(torch.float32))
+        all_i = gather(topk_ids.to(torch.int32))
+        partial = self.local_fn(all_h, w1_local, w2_local, all_w, all_i,
+                                expert_map=self.expert_map,
+                                global_num_experts=self.num_experts, **kwargs)
+        partial = partial.to(torch.float32)
+        if partial.is_cuda:
+            mine = torch.empty((m, h), dtype=torch.float32, device=dev)
+            dist.reduce_scatter_tensor(mine, partial, group=self.group)
+        else:   # gloo has no reduce-scatter
+            dist.all_reduce(partial, group=self.group)
+            mine = partial[self.rank * m:(self.rank + 1) * m]
+        self.last_stats = dict(mode="replicated", tokens=m * world)
+        return mine.to(out_dtype)
+
     # -- the layer ----------------------------------------------------------------------------
     def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
         m, h = hidden_states.shape
+        if self.replicate_below and m * self.world <= self.replicate_below \
+                and not kwargs.get("no_combine"):
+            return self.forward_replicated(hidden_states, w1_local, w2_local, topk_weights,
+                                           topk_ids, **kwargs)
         k = topk_ids.shape[1]
         marks = []
 

@@ -78,6 +78,44 @@ def test_ep_dispatch_combine_matches_single_rank(world, E, K, zipf):
         assert 0 < sent <= routes
 
 
+def _replicated_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from boltops_b200.fused_moe.ep import ExpertParallelMoE
+        E, K, H, I, M = 8, 2, 64, 32, 5
+        g = torch.Generator().manual_seed(0)
+        w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16()
+        w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
+        per = E // world
+        hidden = torch.randn(M, H, generator=torch.Generator().manual_seed(100 + rank)).bfloat16()
+        wts, ids = O.make_routing(M, E, K, 200 + rank)
+        ep = ExpertParallelMoE(dist.group.WORLD, E, "cpu", local_fn=_local_oracle,
+                               combine_fn=_cpu_gather_sum)
+        ep.replicate_below = 64          # 5 tokens x 2 ranks: the small-batch path
+        out = ep.forward(hidden, w1[rank * per:(rank + 1) * per], w2[rank * per:(rank + 1) * per],
+                         wts, ids)
+        assert ep.last_stats.get("mode") == "replicated"
+        ep.replicate_below = 0
+        ref = ep.forward(hidden, w1[rank * per:(rank + 1) * per], w2[rank * per:(rank + 1) * per],
+                         wts, ids)
+        expect = O.moe_bf16(hidden, w1, w2, wts, ids)
+        ret[rank] = (O.rel_l2(out, expect), O.rel_l2(out, ref))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ep_replicated_small_batch_matches_dispatch_and_single_rank():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_replicated_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert len(ret) == 2
+    for rank in range(2):
+        err, err_vs_dispatch = ret[rank]
+        assert err <= 1e-2 and err_vs_dispatch <= 1e-2, (rank, err, err_vs_dispatch)
+
+
 def _bad_worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

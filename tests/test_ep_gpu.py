@@ -42,7 +42,13 @@ def _worker(rank, world, port, ret):
         full = fused_experts(hidden.to(dev), fw1, fw2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
                              w1_scale=fw1s, w2_scale=fw2s, block_shape=[128, 128])
         torch.cuda.synchronize()
-        ret[rank] = O.rel_l2(out.cpu(), full.cpu())
+        # small-batch path: replicated tokens + reduce-scatter instead of the dispatch
+        ep.replicate_below = 4096
+        rep = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
+                         w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+        torch.cuda.synchronize()
+        assert ep.last_stats.get("mode") == "replicated"
+        ret[rank] = max(O.rel_l2(out.cpu(), full.cpu()), O.rel_l2(rep.cpu(), full.cpu()))
     finally:
         dist.destroy_process_group()
 
