@@ -16,6 +16,7 @@ written into this repository except the *numeric outputs* (``.npz`` files).
 from __future__ import annotations
 
 import ast
+import os
 import sys
 from pathlib import Path
 
@@ -225,4 +226,7 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and "BOLTOPS_REFERENCE" not in os.environ:
+        raise SystemExit("usage: make_golden.py <path of the reference project checkout> "
+                         "(or set BOLTOPS_REFERENCE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["BOLTOPS_REFERENCE"])
