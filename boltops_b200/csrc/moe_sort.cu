@@ -253,22 +253,40 @@ __global__ void __launch_bounds__(1024) k_sort_scan(SortParams p, int G) {
   int* tmp = start_s + p.E + 1;
   int* scratch = tmp + p.E;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  // column scan: one warp per expert, lanes across CTAs
-  for (int e = warp; e < p.E; e += nwarps) {
-    int carry = 0;
-    for (int g0 = 0; g0 < G; g0 += 32) {
-      const int g = g0 + lane;
-      const int v = (g < G) ? p.cta_counts[g * p.E + e] : 0;
-      int x = v;
+  // column scan: one warp per expert, lanes across CTAs.  A warp takes its experts four at a
+  // time and issues all their loads (G <= 128: four 32-CTA blocks each) before the first scan,
+  // so the global-memory latency is paid once per batch, not once per expert and block.
+  constexpr int EB = 4, GB = kMaxCtas / 32;
+  for (int k0 = 0; warp + k0 * nwarps < p.E; k0 += EB) {
+    int v[EB][GB];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x += y;
+    for (int j = 0; j < EB; ++j) {
+      const int e = warp + (k0 + j) * nwarps;
+#pragma unroll
+      for (int b = 0; b < GB; ++b) {
+        const int g = b * 32 + lane;
+        v[j][b] = (e < p.E && g < G) ? p.cta_counts[g * p.E + e] : 0;
       }
-      if (g < G) p.cta_counts[g * p.E + e] = carry + x - v;
-      carry += __shfl_sync(0xffffffffu, x, 31);
     }
-    if (lane == 0) tot[e] = carry;
+#pragma unroll
+    for (int j = 0; j < EB; ++j) {
+      const int e = warp + (k0 + j) * nwarps;
+      if (e >= p.E) break;   // warp-uniform
+      int carry = 0;
+#pragma unroll
+      for (int b = 0; b < GB; ++b) {
+        const int g = b * 32 + lane;
+        int x = v[j][b];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        if (g < G) p.cta_counts[g * p.E + e] = carry + x - v[j][b];
+        carry += __shfl_sync(0xffffffffu, x, 31);
+      }
+      if (lane == 0) tot[e] = carry;
+    }
   }
   __syncthreads();
   build_metadata(p, tot, start_s, tmp, scratch);
