@@ -973,9 +973,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                 wq[2 * i] = make_uint4(w[0], w[1], w[2], w[3]);
                 wq[2 * i + 1] = make_uint4(w[4], w[5], w[6], w[7]);
               }
-              // 64 one-byte outputs = one 64-byte row segment, written directly (staging it
-              // through shared memory was measured slower for this small store)
-              if (wr) {
+              // 64 one-byte outputs = one 64-byte row segment: the warp's 32 x 64 B block leaves
+              // by one bulk tensor store (a per-thread store touches 32 different lines per
+              // instruction); without a tensor map the segment is written directly
+              if (p.c_tma_ok) {
+                store_rows_tma(out_stage, wq, &tma_c, ocol, tile_row0, lane);
+              } else if (wr) {
                 uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.c) + row_off + ocol);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) dst[j] = wq[j];
@@ -1162,13 +1165,16 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   CUtensorMap mc;
   memset(&mc, 0, sizeof(mc));
   p.c_tma_ok = 0;
-  if (p.c_vec_ok && !a->scatter && (a->c_dtype == BOLT_BF16 || a->c_dtype == BOLT_F16)) {
+  const bool out8 = a->epilogue == BOLT_EPI_SILU_MUL_QUANT;   // e4m3 / int8 rows, never scattered
+  if (p.c_vec_ok && !a->scatter && (out8 || a->c_dtype == BOLT_BF16 || a->c_dtype == BOLT_F16)) {
     const int64_t out_cols = gated ? a->n / 2 : a->n;
+    const int esz = out8 ? 1 : 2;
     cuuint64_t dims[2] = {(cuuint64_t)out_cols, (cuuint64_t)a->capacity};
-    cuuint64_t strides[1] = {(cuuint64_t)a->c_ld * 2};
-    cuuint32_t box[2] = {32, 32};
+    cuuint64_t strides[1] = {(cuuint64_t)a->c_ld * esz};
+    cuuint32_t box[2] = {(cuuint32_t)(64 / esz), 32};   // 64 bytes x 32 rows either way
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(&mc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a->c, dims, strides, box, estr,
+    CUresult r = encode(&mc, out8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                        2, a->c, dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     p.c_tma_ok = (r == CUDA_SUCCESS) ? 1 : 0;   // on failure the per-thread store paths remain
