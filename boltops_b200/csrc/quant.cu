@@ -544,6 +544,93 @@ int dispatch_quant_scatter(const void* x, int64_t num_tokens, int cols, int grou
 #undef BOLT_QS
 }
 
+// ---- MX (OCP microscaling) e4m3: 1 x 32 groups, power-of-two E8M0 scales ---------------------
+// exponent byte = clamp(ceil(log2(amax / 448)) + 127, 0, 254), q = e4m3(v * 2^(127 - byte)),
+// optionally after a split gated activation  min(g, L) * sigmoid(alpha g) * (clamp(u, +-L) + beta)
+// computed in fp32 from [rows, 2 cols] = [gate | up].  Four lanes share a group (8 elements each).
+// Outputs (each optional): codes, exponent bytes, and the dequantised values q * 2^(byte - 127)
+// in a 16- or 32-bit float type (exact: an e4m3 value times a power of two).
+template <typename TIn, typename TDeq>
+__global__ void __launch_bounds__(256) k_mx_quant(const TIn* __restrict__ x, int64_t rows, int cols,
+                                                  int gated, float alpha, float beta,
+                                                  int has_limit, float limit,
+                                                  uint8_t* __restrict__ q,
+                                                  uint8_t* __restrict__ scales,
+                                                  TDeq* __restrict__ deq) {
+  const int units = cols / 8;                       // 8-element units per output row
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = tid / units;
+  const int unit = (int)(tid - row * units);
+  const bool live = row < rows;
+  const int in_cols = gated ? 2 * cols : cols;
+  float v[8];
+  float amax = 0.f;
+  if (live) {
+    const TIn* src = x + row * (int64_t)in_cols + unit * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = to_f32(src[i]);
+    if (gated) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float g = v[i], u = to_f32(src[cols + i]);
+        if (has_limit) {
+          g = fminf(g, limit);
+          u = fminf(fmaxf(u, -limit), limit);
+        }
+        v[i] = g * __frcp_rn(1.0f + expf(-alpha * g)) * (u + beta);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  if (!live) return;
+  amax = fmaxf(amax, 1.1754943508222875e-38f);
+  const float e = fminf(fmaxf(ceilf(log2f(__fdiv_rn(amax, 448.0f))) + 127.0f, 0.0f), 254.0f);
+  const int byte = (int)e;
+  const float down = exp2f(127.0f - e);             // exact powers of two
+  const float up2 = exp2f(e - 127.0f);
+  uint8_t code[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) code[i] = f32_to_e4m3(v[i] * down);
+  const int64_t o = row * (int64_t)cols + unit * 8;
+  if (q != nullptr) {
+    uint2 w;
+    w.x = code[0] | (code[1] << 8) | (code[2] << 16) | ((uint32_t)code[3] << 24);
+    w.y = code[4] | (code[5] << 8) | (code[6] << 16) | ((uint32_t)code[7] << 24);
+    *reinterpret_cast<uint2*>(q + o) = w;
+  }
+  if (scales != nullptr && (unit & 3) == 0) scales[row * (int64_t)(cols / 32) + unit / 4] = (uint8_t)byte;
+  if (deq != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __nv_fp8_e4m3 c = *reinterpret_cast<const __nv_fp8_e4m3*>(&code[i]);
+      deq[o + i] = from_f32<TDeq>(float(c) * up2);
+    }
+  }
+}
+
+// codes [rows, cols] e4m3 + exponent bytes [rows, cols/32] -> floats (checkpoint weights)
+template <typename TDeq>
+__global__ void __launch_bounds__(256) k_mx_dequant(const uint8_t* __restrict__ q,
+                                                    const uint8_t* __restrict__ scales,
+                                                    int64_t rows, int cols,
+                                                    TDeq* __restrict__ out) {
+  const int units = cols / 8;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = tid / units;
+  if (row >= rows) return;
+  const int unit = (int)(tid - row * units);
+  const int64_t o = row * (int64_t)cols + unit * 8;
+  const float s = exp2f((float)scales[row * (int64_t)(cols / 32) + unit / 4] - 127.0f);
+  const uint2 w = *reinterpret_cast<const uint2*>(q + o);
+  const uint8_t* c = reinterpret_cast<const uint8_t*>(&w);
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    out[o + i] = from_f32<TDeq>(float(*reinterpret_cast<const __nv_fp8_e4m3*>(&c[i])) * s);
+}
+
 }  // namespace
 }  // namespace bolt
 
@@ -632,4 +719,72 @@ extern "C" int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_t
       set_error("quant_scatter: unsupported input dtype %d", x_dtype);
       return BOLT_ERR_INVALID;
   }
+}
+
+extern "C" int bolt_mx_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int gated,
+                                  float alpha, float beta, int has_limit, float limit, void* q,
+                                  uint8_t* scales, void* deq, int deq_dtype, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, "mx_quant: cols %d must be a multiple of 32",
+               cols);
+  BOLT_REQUIRE(q != nullptr || deq != nullptr, "mx_quant: no output requested");
+  if (rows == 0) return BOLT_OK;
+  BOLT_REQUIRE(x != nullptr, "mx_quant: null input");
+  BOLT_REQUIRE(q == nullptr || reinterpret_cast<uintptr_t>(q) % 8 == 0, "mx_quant: q misaligned");
+  const int64_t threads = rows * (cols / 8);
+  const int64_t blocks = (threads + 255) / 256;
+  BOLT_REQUIRE(blocks < ((int64_t)1 << 31), "mx_quant: too many elements");
+#define BOLT_MXQ(TIn, TDeq)                                                                    \
+  k_mx_quant<TIn, TDeq><<<(unsigned)blocks, 256, 0, st>>>(                                     \
+      static_cast<const TIn*>(x), rows, cols, gated, alpha, beta, has_limit, limit,            \
+      static_cast<uint8_t*>(q), scales, static_cast<TDeq*>(deq))
+#define BOLT_MXQ_IN(TDeq)                                                                      \
+  switch (x_dtype) {                                                                           \
+    case BOLT_BF16: BOLT_MXQ(__nv_bfloat16, TDeq); break;                                      \
+    case BOLT_F16: BOLT_MXQ(__half, TDeq); break;                                              \
+    case BOLT_F32: BOLT_MXQ(float, TDeq); break;                                               \
+    default: set_error("mx_quant: unsupported input dtype %d", x_dtype); return BOLT_ERR_INVALID; \
+  }
+  switch (deq == nullptr ? BOLT_BF16 : deq_dtype) {
+    case BOLT_BF16: BOLT_MXQ_IN(__nv_bfloat16); break;
+    case BOLT_F16: BOLT_MXQ_IN(__half); break;
+    case BOLT_F32: BOLT_MXQ_IN(float); break;
+    default: set_error("mx_quant: unsupported output dtype %d", deq_dtype); return BOLT_ERR_INVALID;
+  }
+#undef BOLT_MXQ_IN
+#undef BOLT_MXQ
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+extern "C" int bolt_mx_dequant_rows(const void* q, const uint8_t* scales, int64_t rows, int cols,
+                                    void* out, int out_dtype, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0,
+               "mx_dequant: cols %d must be a multiple of 32", cols);
+  if (rows == 0) return BOLT_OK;
+  BOLT_REQUIRE(q && scales && out, "mx_dequant: null pointer");
+  BOLT_REQUIRE(reinterpret_cast<uintptr_t>(q) % 8 == 0, "mx_dequant: codes misaligned");
+  const int64_t threads = rows * (cols / 8);
+  const int64_t blocks = (threads + 255) / 256;
+  BOLT_REQUIRE(blocks < ((int64_t)1 << 31), "mx_dequant: too many elements");
+  switch (out_dtype) {
+    case BOLT_BF16:
+      k_mx_dequant<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+          static_cast<const uint8_t*>(q), scales, rows, cols, static_cast<__nv_bfloat16*>(out));
+      break;
+    case BOLT_F16:
+      k_mx_dequant<__half><<<(unsigned)blocks, 256, 0, st>>>(
+          static_cast<const uint8_t*>(q), scales, rows, cols, static_cast<__half*>(out));
+      break;
+    case BOLT_F32:
+      k_mx_dequant<float><<<(unsigned)blocks, 256, 0, st>>>(
+          static_cast<const uint8_t*>(q), scales, rows, cols, static_cast<float*>(out));
+      break;
+    default: set_error("mx_dequant: unsupported output dtype %d", out_dtype); return BOLT_ERR_INVALID;
+  }
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
 }

@@ -135,7 +135,22 @@ def fused_experts_impl(
         if any((use_fp8_w8a8, use_int8_w8a8, use_int8_w8a16, use_int4_w4a16, use_int4_w4a8,
                 per_channel_quant)):
             raise ValueError(f"{name} cannot be combined with other quantization flags")
-        raise NotImplementedError(f"{name} experts are not built in boltops_b200")
+        if use_mxfp8 and use_mxfp4_w4a8:
+            raise ValueError("MXFP8 and MXFP4 are mutually exclusive")
+        if use_mxfp4_w4a8:
+            raise NotImplementedError("MXFP4 experts are not built in boltops_b200")
+        from . import mxfp8
+        activation, is_gated = normalize_moe_activation(activation, is_gated)
+        mxfp8.validate(hidden_states, w1, w2, w1_scale, w2_scale, a1_scale, a2_scale, b1, b2,
+                       apply_router_weight_on_input, output_dtype, block_shape, activation,
+                       is_gated, inplace, no_combine)
+        return mxfp8.fused_experts_mxfp8(
+            hidden_states, w1, w2, topk_weights, topk_ids, w1_scale=w1_scale, w2_scale=w2_scale,
+            activation=activation, inplace=inplace, no_combine=no_combine,
+            global_num_experts=global_num_experts, expert_map=expert_map,
+            routed_scaling_factor=1.0 if routed_scaling_factor is None else routed_scaling_factor,
+            gemm1_alpha=gemm1_alpha, gemm1_beta=gemm1_beta, gemm1_limit=gemm1_limit,
+            chunk=_chunk_size())
     if use_int8_w8a16 or use_int4_w4a16 or use_int4_w4a8:
         raise NotImplementedError("weight-only / int4 experts are not built in boltops_b200")
     if w1_zp is not None or w2_zp is not None:

@@ -1,0 +1,149 @@
+"""Native-MXFP8 experts (`use_mxfp8=True`): e4m3 weights and activations with one E8M0
+exponent byte per 32 consecutive K elements.
+
+Reference semantics (boltops/fused_moe/triton/fused_moe.py:978-996,1079-1197 and the CPU
+statement in test/fused_moe/test_fused_moe.py:1904-1931 of the reference project): activations
+are quantised inside the layer per 1 x 32 group with scale 2^ceil(log2(amax/448)); GEMM1 is
+rounded to the input dtype; the split gated activation and the second quantisation run in fp32
+on that; GEMM2 and the router weights stay in fp32 until the sum over a token's routes; one cast
+at the end.
+
+How it runs here.  An e4m3 value times a power of two is exactly representable in bf16 / fp16,
+and products of two such values are exact in fp32, so the MX contraction equals a 16-bit GEMM
+over the DEQUANTISED operands with fp32 accumulation.  The layer therefore quantises and
+dequantises activations in one kernel (`bolt_mx_quant_rows`), decodes the checkpoint weights
+once to the activation dtype (`bolt_mx_dequant_rows`, cached per weight tensor) and runs the
+16-bit grouped GEMM.  Numerically this is the MX recipe; in memory traffic it is a 16-bit layer
+(the decoded weights take twice the bytes of the e4m3 codes).  A mainloop on the tensor cores'
+block-scaled e4m3 instruction, which keeps the weights in 8 bits, is not built.
+"""
+from __future__ import annotations
+
+import weakref
+from typing import Optional
+
+import torch
+
+from .. import _cabi
+from . import ops
+
+_decoded = {}     # (data_ptr, scale data_ptr, shape, dtype) -> (weakrefs of the sources, decoded tensor)
+
+
+def _decode_weights(w: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Checkpoint weights [E, N, K] e4m3 + E8M0 bytes [E, N, K/32] -> [E, N, K] in `dtype`.
+    Decoded once per (weight, scale) pair and kept while both source tensors are alive and
+    unmodified (their version counters are part of the key)."""
+    key = (w.data_ptr(), scale.data_ptr(), tuple(w.shape), dtype, w._version, scale._version)
+    hit = _decoded.get(key)
+    if hit is not None and hit[0]() is w and hit[1]() is scale:
+        return hit[2]
+    for k in [k for k, v in _decoded.items() if v[0]() is None or v[1]() is None]:
+        del _decoded[k]
+    out = ops.mx_dequant_rows(w.contiguous(), scale.contiguous(), dtype)
+    _decoded[key] = (weakref.ref(w), weakref.ref(scale), out)
+    return out
+
+
+def validate(hidden_states, w1, w2, w1_scale, w2_scale, a1_scale, a2_scale, b1, b2,
+             apply_router_weight_on_input, output_dtype, block_shape, activation, is_gated,
+             inplace, no_combine) -> None:
+    """The reference's argument checks for the native path, same order, types and messages."""
+    if hidden_states.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("native MXFP8 requires BF16/FP16 hidden_states")
+    if a1_scale is not None or a2_scale is not None:
+        raise ValueError("native MXFP8 quantizes activations internally; "
+                         "a1_scale/a2_scale must be None")
+    if b1 is not None or b2 is not None or apply_router_weight_on_input:
+        raise ValueError("native MXFP8 does not support bias or input routing weights")
+    if output_dtype is not None and output_dtype != hidden_states.dtype:
+        raise ValueError("native MXFP8 output_dtype must match hidden_states.dtype")
+    if w1.dtype != torch.float8_e4m3fn or w2.dtype != torch.float8_e4m3fn:
+        raise ValueError("MXFP8 weights must be E4M3; FNUZ is not supported")
+    if block_shape is not None and tuple(block_shape) != (1, 32):
+        raise ValueError("native MXFP8 requires weight block_shape=[1,32]")
+    for scale in (w1_scale, w2_scale):
+        if scale is None or scale.dtype != torch.uint8:
+            raise ValueError("native MXFP8 requires uint8 E8M0 weight scales")
+    if not is_gated or activation not in ("silu", "swigluoai"):
+        raise ValueError("MXFP8 requires gated ('silu', 'swigluoai')")
+    if no_combine:
+        assert not inplace, "no_combine + inplace is not supported"
+
+
+def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_scale, w2_scale,
+                        activation: str, inplace: bool, no_combine: bool,
+                        global_num_experts: int, expert_map: Optional[torch.Tensor],
+                        routed_scaling_factor: float, gemm1_alpha, gemm1_beta, gemm1_limit,
+                        chunk: int) -> torch.Tensor:
+    if not hidden_states.is_cuda:
+        raise ValueError("boltops_b200 kernels need CUDA tensors (there is no CPU path)")
+    assert hidden_states.shape[1] == w1.shape[2], "Hidden size mismatch"
+    assert topk_weights.shape == topk_ids.shape, "topk shape mismatch"
+    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    dtype = hidden_states.dtype
+    dev = hidden_states.device
+    num_tokens, hidden = hidden_states.shape
+    e_local, n1, _ = w1.shape
+    inter = n1 // 2
+    model_dim = w2.shape[1]
+    topk = topk_ids.shape[1]
+    assert hidden % 32 == 0 and inter % 32 == 0, "MXFP8 needs K dimensions divisible by 32"
+    assert tuple(w1_scale.shape) == (e_local, n1, hidden // 32), "w1_scale shape"
+    assert tuple(w2_scale.shape) == (e_local, model_dim, inter // 32), "w2_scale shape"
+    if expert_map is None:
+        global_num_experts = e_local          # appended shared experts included, as the reference
+    elif global_num_experts == -1:
+        global_num_experts = expert_map.numel()
+    oai = activation == "swigluoai"
+    alpha = (1.702 if oai else 1.0) if gemm1_alpha is None else gemm1_alpha
+    beta = (1.0 if oai else 0.0) if gemm1_beta is None else gemm1_beta
+    kind = _cabi.GEMM_BF16 if dtype == torch.bfloat16 else _cabi.GEMM_F16
+    w1_d = _decode_weights(w1, w1_scale, dtype)
+    w2_d = _decode_weights(w2, w2_scale, dtype)
+    expert_mask = (expert_map >= 0).to(torch.int32) if expert_map is not None else None
+    if topk_ids.dtype != torch.int32:
+        topk_ids = topk_ids.to(torch.int32)
+    topk_weights = topk_weights.to(torch.float32)
+
+    if no_combine:
+        out = torch.empty((num_tokens, topk, model_dim), device=dev, dtype=dtype)
+    elif inplace:
+        out = hidden_states
+    else:
+        out = torch.empty((num_tokens, model_dim), device=dev, dtype=dtype)
+    for begin in range(0, num_tokens, chunk):
+        end = min(begin + chunk, num_tokens)
+        m = end - begin
+        ids = topk_ids[begin:end].contiguous()
+        wts = topk_weights[begin:end].contiguous()
+        route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
+        sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
+            ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
+            alloc_moe_buf=False, route_pos=route_pos)
+        cap = sorted_ids.shape[0]
+        common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
+                      sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
+        # A1: quantise + dequantise once per token, gather into sorted rows
+        _, _, x_d = ops.mx_quant_rows(hidden_states[begin:end], want_codes=False, deq_dtype=dtype)
+        a_sorted, _ = ops.gather_rows(x_d, sorted_ids, num_valid, cap)
+        # GEMM1, rounded to the input dtype
+        g1 = torch.empty((cap, n1), device=dev, dtype=dtype)
+        ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1_d, c=g1, **common)
+        # split gated activation in fp32 + second quantisation, dequantised for GEMM2
+        _, _, act = ops.mx_quant_rows(g1, gated=True, alpha=alpha, beta=beta, limit=gemm1_limit,
+                                      want_codes=False, deq_dtype=dtype)
+        # GEMM2 in fp32 with the router weight, then the fp32 sum over the routes
+        if no_combine:
+            c3 = torch.zeros((m * topk, model_dim), device=dev, dtype=torch.float32) \
+                if expert_map is not None else \
+                torch.empty((m * topk, model_dim), device=dev, dtype=torch.float32)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2_d, c=c3, scatter=True,
+                             mul_routed_weight=False, **common)
+            out[begin:end].copy_(c3.view(m, topk, model_dim))
+        else:
+            c_sorted = torch.empty((cap, model_dim), device=dev, dtype=torch.float32)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2_d, c=c_sorted, scatter=False,
+                             mul_routed_weight=True, **common)
+            ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
+    return out

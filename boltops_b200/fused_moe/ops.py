@@ -219,6 +219,47 @@ def quant_scatter_rows(x: torch.Tensor, group: int, q_dtype: torch.dtype, route_
     return dst, dst_scale
 
 
+def mx_quant_rows(x: torch.Tensor, *, gated: bool = False, alpha: float = 1.0, beta: float = 0.0,
+                  limit: Optional[float] = None, want_codes: bool = True,
+                  deq_dtype: Optional[torch.dtype] = None):
+    """MX e4m3 quantisation of ``x`` [rows, cols] (or [rows, 2*cols] = [gate | up] with the split
+    gated activation fused in front).  Returns ``(q, scales, deq)``: e4m3 codes, E8M0 bytes
+    [rows, cols/32], and the dequantised values in ``deq_dtype`` (each ``None`` if not asked for)."""
+    _require_cuda(x)
+    lib = _cabi.load()
+    x = x.contiguous()
+    rows = x.shape[0]
+    cols = x.shape[1] // 2 if gated else x.shape[1]
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device) if want_codes else None
+    s = torch.empty((rows, cols // 32), dtype=torch.uint8, device=x.device) if want_codes else None
+    deq = torch.empty((rows, cols), dtype=deq_dtype, device=x.device) if deq_dtype is not None else None
+    with torch.cuda.device(x.device):
+        check(lib.bolt_mx_quant_rows(ptr(x), dtype_code(x.dtype), rows, cols, int(gated),
+                                     float(alpha), float(beta), int(limit is not None),
+                                     float(limit or 0.0), ptr(q), ptr(s), ptr(deq),
+                                     dtype_code(deq_dtype) if deq_dtype is not None else _cabi.BF16,
+                                     stream_of(x)))
+    _count()
+    return q, s, deq
+
+
+def mx_dequant_rows(q: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``q`` [..., cols] e4m3 with E8M0 bytes [..., cols/32] → floats ``q * 2^(byte-127)``."""
+    _require_cuda(q, scales)
+    lib = _cabi.load()
+    q = q.contiguous()
+    scales = scales.contiguous()
+    cols = q.shape[-1]
+    rows = q.numel() // cols
+    assert scales.dtype == torch.uint8 and scales.numel() == rows * (cols // 32)
+    out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
+    with torch.cuda.device(q.device):
+        check(lib.bolt_mx_dequant_rows(ptr(q), ptr(scales), rows, cols, ptr(out),
+                                       dtype_code(out_dtype), stream_of(q)))
+    _count()
+    return out
+
+
 def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
             routed_scaling_factor: float = 1.0,
             router_weights: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -225,6 +225,24 @@ int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_tokens, int 
                             int capacity, void* dst, float* dst_scale, int64_t dst_scale_ld,
                             void* stream);
 
+/* MX (microscaling) e4m3 quantisation with 1 x 32 groups and E8M0 exponent bytes.  Replaces
+ * mxfp8_e4m3_quantize (boltops/fused_moe/triton/mxfp8.py:122-175): byte =
+ * clamp(ceil(log2(amax/448)) + 127, 0, 254), q = e4m3(v * 2^(127-byte)); with gated != 0 the
+ * input is [rows, 2*cols] = [gate | up] and v = min(g,L) * sigmoid(alpha*g) * (clamp(u,+-L) + beta)
+ * in fp32 (L only when has_limit).  Outputs, each optional: q [rows, cols] e4m3, scales
+ * [rows, cols/32] bytes, deq [rows, cols] = q * 2^(byte-127) in deq_dtype (exact).
+ */
+int bolt_mx_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int gated, float alpha,
+                       float beta, int has_limit, float limit, void* q, uint8_t* scales, void* deq,
+                       int deq_dtype, void* stream);
+
+/* q [rows, cols] e4m3 with exponent bytes [rows, cols/32] -> out [rows, cols] in out_dtype
+ * (w * 2^(byte-127); the decoding of MX checkpoint weights,
+ * boltops/fused_moe/triton/moe_compat.py `_upcast_e8m0_to_fp32` applied per group).
+ */
+int bolt_mx_dequant_rows(const void* q, const uint8_t* scales, int64_t rows, int cols, void* out,
+                         int out_dtype, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Activations.  Replaces _apply_activation / moe_activation
  * (boltops/fused_moe/triton/moe_activation.py:1382-1525; kernels :70-128 etc.).

@@ -492,6 +492,70 @@ def quantize_weight_channel_int8(w: torch.Tensor):
     return q, s.squeeze(-1).contiguous()
 
 
+# ---------------------------------------------------------------------------
+# MXFP8: e4m3 codes with E8M0 exponent bytes per 1 x 32 group
+# ---------------------------------------------------------------------------
+def mx_quant(value: torch.Tensor):
+    """Codes, exponent bytes and dequantised values of the reference's MXFP8 quantiser
+    (test/fused_moe/test_fused_moe.py:1904-1909 `native_quant`;
+    boltops/fused_moe/triton/mxfp8.py:144-149): byte = clamp(ceil(log2(amax/448)) + 127, 0, 254)
+    per 32 elements, q = e4m3(v * 2^(127 - byte))."""
+    blocked = value.float().reshape(value.shape[0], -1, 32)
+    amax = blocked.abs().amax(-1).clamp_min(torch.finfo(torch.float32).tiny)
+    exponent = (torch.ceil(torch.log2(amax / 448.)) + 127).clamp(0, 254)
+    q = (blocked * torch.exp2(127 - exponent)[..., None]).to(torch.float8_e4m3fn)
+    deq = (q.float() * torch.exp2(exponent - 127)[..., None]).reshape(value.shape)
+    return q.reshape(value.shape), exponent.to(torch.uint8), deq
+
+
+def mx_dequant_weight(w: torch.Tensor, s: torch.Tensor, group: int = 32) -> torch.Tensor:
+    """e4m3 weights [E, N, K] with E8M0 bytes [E, N, K/group] -> fp32
+    (test/fused_moe/test_fused_moe.py:1893-1894)."""
+    return w.float() * torch.exp2(s.float() - 127).repeat_interleave(group, -1)
+
+
+def mx_gated_activation(g1: torch.Tensor, activation: str = "silu", alpha=None, beta=None,
+                        limit=None) -> torch.Tensor:
+    """Split [gate | up] activation of the MXFP8 path in fp32
+    (boltops/fused_moe/triton/mxfp8.py:137-143; defaults fused_moe.py:1166-1170)."""
+    oai = activation == "swigluoai"
+    alpha = (1.702 if oai else 1.0) if alpha is None else alpha
+    beta = (1.0 if oai else 0.0) if beta is None else beta
+    gate, up = g1.float().chunk(2, -1)
+    if limit is not None:
+        gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+    return gate * torch.sigmoid(alpha * gate) * (up + beta)
+
+
+def moe_mxfp8(x, w1, w2, s1, s2, topk_weights, topk_ids, *, expert_map=None, activation="silu",
+              alpha=None, beta=None, limit=None, no_combine=False):
+    """The reference's CPU statement of the native MXFP8 layer
+    (test/fused_moe/test_fused_moe.py:1910-1931): activations quantised per 1 x 32 group, GEMM1
+    rounded to the input dtype, activation and second quantisation in fp32, GEMM2 and the router
+    weights in fp32 until the sum over the routes, one cast at the end."""
+    m, k = x.shape
+    e = w1.shape[0]
+    topk = topk_ids.shape[1]
+    b1, b2 = mx_dequant_weight(w1, s1), mx_dequant_weight(w2, s2)
+    av = mx_quant(x)[2]
+    expected = torch.zeros(m, topk, w2.shape[1], dtype=torch.float32)
+    for token in range(m):
+        for rank, ge in enumerate(topk_ids[token].tolist()):
+            if ge < 0 or ge >= (e if expert_map is None else expert_map.numel()):
+                continue
+            expert = ge if expert_map is None else int(expert_map[ge])
+            if expert < 0:
+                continue
+            g1 = (av[token:token + 1] @ b1[expert].T).to(x.dtype).float()
+            act = mx_gated_activation(g1, activation, alpha, beta, limit)
+            a2 = mx_quant(act)[2]
+            g2 = (a2 @ b2[expert].T)[0]
+            if not no_combine:
+                g2 = g2 * topk_weights[token, rank].float()
+            expected[token, rank] = g2
+    return (expected if no_combine else expected.sum(1)).to(x.dtype)
+
+
 def rel_l2(actual: torch.Tensor, expected: torch.Tensor) -> float:
     a = actual.double().flatten()
     e = expected.double().flatten()

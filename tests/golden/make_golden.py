@@ -18,6 +18,7 @@ from __future__ import annotations
 import ast
 import os
 import sys
+import textwrap
 from pathlib import Path
 
 import numpy as np
@@ -50,6 +51,27 @@ def t2n(t: torch.Tensor) -> np.ndarray:
     if t.dtype == torch.float8_e4m3fn:
         return t.view(torch.uint8).numpy()
     return t.numpy()
+
+
+def make_mxfp8(ref: Path) -> None:
+    """Native MXFP8 layer: the CPU statement inside test_public_mxfp8_cpu_reference
+    (everything from the seed down to the line that forms `expected`; the device half of the
+    test follows that line and is not executed)."""
+    text = (ref / "test/fused_moe/test_fused_moe.py").read_text().splitlines()
+    start = next(i for i, l in enumerate(text) if l.strip() == "torch.manual_seed(673)")
+    stop = next(i for i in range(start, len(text))
+                if text[i].startswith("    expected = (expected if case"))
+    body = textwrap.dedent("\n".join(text[start:stop + 1]))
+    mx = {}
+    for case in ("default", "silu_alpha", "swigluoai", "no_combine", "dynamic_fp16"):
+        ns = {"torch": torch, "case": case, "monkeypatch": None}
+        exec(compile(body, "mxfp8_cpu_reference", "exec"), ns)
+        for name in ("x", "w1", "w2", "s1", "s2", "ids", "weights", "expected"):
+            v = ns[name]
+            if v.dtype == torch.float8_e4m3fn:
+                v = v.view(torch.uint8)
+            mx[f"{case}_{name}"] = t2n(v)
+    np.savez_compressed(HERE / "mxfp8.npz", **mx)
 
 
 def main(ref_root: str) -> None:
@@ -222,6 +244,8 @@ def main(ref_root: str) -> None:
         y = cm["apply_activation_ref"](x.float(), activation_name=name, is_gated=gated)
         acts[f"{name}_{int(gated)}"] = y.numpy()
     np.savez_compressed(HERE / "activations.npz", **acts)
+
+    make_mxfp8(ref)
     print("golden fixtures written to", HERE)
 
 
@@ -229,4 +253,8 @@ if __name__ == "__main__":
     if len(sys.argv) < 2 and "BOLTOPS_REFERENCE" not in os.environ:
         raise SystemExit("usage: make_golden.py <path of the reference project checkout> "
                          "(or set BOLTOPS_REFERENCE)")
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["BOLTOPS_REFERENCE"])
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ["BOLTOPS_REFERENCE"]
+    if len(sys.argv) > 2 and sys.argv[2] == "mxfp8":      # only the newest fixture
+        make_mxfp8(Path(root))
+    else:
+        main(root)

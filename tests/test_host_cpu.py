@@ -150,3 +150,29 @@ def test_custom_op_fake_impl_shapes():
         out = torch.ops.boltops_b200.fused_experts_impl(hid, w1, w2, wts, ids, no_combine=True,
                                                         output_dtype=torch.float16)
         assert out.shape == (5, 2, 128) and out.dtype == torch.float16
+
+
+@pytest.mark.parametrize("case", ["block128", "fp32_scale", "packed_scale", "bias", "input_router",
+                                  "prequantized", "output_dtype"])
+def test_mxfp8_rejections_match_reference(case):
+    """Same ValueErrors, raised before any device work, as the reference's
+    test_public_mxfp8_rejects_non_native_recipe / ..._unsupported_native_options."""
+    import torch
+    from boltops_b200.fused_moe import fused_experts
+    x = torch.zeros(1, 128, dtype=torch.bfloat16)
+    if case == "prequantized":
+        x = x.to(torch.float8_e4m3fn)
+    w1 = torch.zeros(1, 256, 128, dtype=torch.float8_e4m3fn)
+    w2 = torch.zeros(1, 128, 128, dtype=torch.float8_e4m3fn)
+    scale_dtype = {"fp32_scale": torch.float32, "packed_scale": torch.int32}.get(case, torch.uint8)
+    match = "native MXFP8 requires" if case in ("block128", "fp32_scale", "packed_scale") \
+        else "native MXFP8"
+    with pytest.raises(ValueError, match=match):
+        fused_experts(
+            x, w1, w2, torch.ones(1, 1), torch.zeros(1, 1, dtype=torch.int32), use_mxfp8=True,
+            block_shape=[128, 128] if case == "block128" else [1, 32],
+            b1=torch.zeros(1, 256) if case == "bias" else None,
+            apply_router_weight_on_input=case == "input_router",
+            output_dtype=torch.float32 if case == "output_dtype" else None,
+            w1_scale=torch.ones(1, 256, 4, dtype=scale_dtype),
+            w2_scale=torch.ones(1, 128, 4, dtype=scale_dtype))

@@ -178,3 +178,14 @@ def test_grouped_gate_fixture(shared):
         exp = sorted(zip(ref_i[row].tolist(), ref_w[row].tolist()))
         assert [a for a, _ in got] == [a for a, _ in exp]
         assert all(abs(a - b) <= 1e-6 for (_, a), (_, b) in zip(got, exp))
+
+
+@pytest.mark.parametrize("case", ["default", "silu_alpha", "swigluoai", "no_combine", "dynamic_fp16"])
+def test_mxfp8_layer_fixture(case):
+    """The oracle's MXFP8 layer reproduces the reference's own CPU statement bit for bit."""
+    from tests.helpers import MX_CASES, load_mx_case
+    c = load_mx_case(case)
+    out = O.moe_mxfp8(c["x"], c["w1"], c["w2"], c["s1"], c["s2"], c["weights"], c["ids"],
+                      **MX_CASES[case])
+    assert out.dtype == c["expected"].dtype
+    assert torch.equal(out.float(), c["expected"].float())
