@@ -21,7 +21,8 @@ BF16, F16, F32, FP8_E4M3, INT8 = 0, 1, 2, 3, 4
 (ACT_SILU, ACT_GELU, ACT_GELU_TANH, ACT_RELU2, ACT_SWIGLU_OAI, ACT_SWIGLU_STEP, ACT_SILU_CLAMP,
  ACT_SWIGLU_OAI_INTERLEAVED, ACT_SITU) = range(9)
 # enum bolt_gemm_kind
-GEMM_BF16, GEMM_F16, GEMM_FP8_BLOCK, GEMM_INT8_CHANNEL, GEMM_FP8_CHANNEL, GEMM_INT8_BLOCK = range(6)
+GEMM_BF16, GEMM_F16, GEMM_FP8_BLOCK, GEMM_INT8_CHANNEL, GEMM_FP8_CHANNEL, GEMM_INT8_BLOCK, \
+    GEMM_MXFP8 = range(7)
 # enum bolt_gemm_epilogue
 EPI_STORE, EPI_SILU_MUL, EPI_SILU_MUL_QUANT = range(3)
 
@@ -87,6 +88,8 @@ _SIGNATURES = {
                                      C.c_void_p, C.c_int, C.c_void_p]),
     "bolt_mx_dequant_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p,
                                        C.c_int, C.c_void_p]),
+    "bolt_mx_sf_layout": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
+                                    C.c_void_p, C.c_void_p]),
     "bolt_gather_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
                                    C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
                                    C.c_void_p]),

@@ -90,6 +90,10 @@ struct GemmParams {
   int kb_scale_cols;  // k/128 (block-scaled kinds)
   uint32_t idesc;
   int group_m;
+  // MX kind: E8M0 bytes in 512-byte tiles of (128 rows x 4 K groups), see k_mx_gemm
+  const uint8_t* sfa;   // [capacity/128][num_kb][512]
+  const uint8_t* sfb;   // [num_experts][n_blocks128][num_kb][512]
+  int n_blocks128;
 };
 
 // ---------------------------------------------------------------------------
@@ -226,6 +230,33 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         : "memory");
   }
 }
+// Block-scaled e4m3 MMA: D[tmem] (+)= (A . B^T) with one E8M0 scale per 32 K elements of every A
+// row and every B row, the scale bytes being read from TMEM (4 bytes per 32-bit column, the byte
+// used is part of the instruction descriptor).
+__device__ __forceinline__ void tc_mma_mx(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::
+          "r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, row r to lane r of every 32-lane quarter.
+__device__ __forceinline__ void tc_cp_sf(uint32_t dst_tmem, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(sdesc)
+               : "memory");
+}
+// Unswizzled K-major source of the copy above: rows 16 bytes apart, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;     // stride byte offset
+  d |= (uint64_t)1 << 46;              // descriptor version
+  return d;
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -1011,6 +1042,211 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------
+// MX (microscaled e4m3) grouped GEMM
+// ---------------------------------------------------------------------------
+// Same tiles, roles and operand pipeline as above, but the 1 x 32 E8M0 scales are applied by the
+// tensor core (kind::mxf8f6f4.block_scale): the accumulator stays in TMEM over the whole K loop
+// and nothing is promoted in registers.  Scale bytes travel in 512-byte tiles of 128 rows x 4 K
+// groups, byte (r % 32) * 16 + (r / 32) * 4 + g for row r and group g: one bulk copy per tile and
+// K block into a shared-memory ring, one tcgen05.cp into four TMEM columns.  TMEM: columns
+// [0,256) accumulator, [256,260) A scales, [260,268) B scales of the current K block (copies and
+// MMAs of one thread execute in order, so the scale columns are reused every K block).  One
+// accumulator stage: the epilogue of a tile is not overlapped with the next tile's MMAs.
+constexpr int kMxStages = 4;
+constexpr int kMxSfSlots = 6;             // >= operand stages + 1
+constexpr int kMxSfSlotBytes = 512 * 3;   // A scales + two 128-row blocks of B scales
+constexpr int kMxSmemBytes = kMxStages * kStageBytes + 4096 + kMxSfSlots * kMxSfSlotBytes +
+                             8 * 2560 + 1024;
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+          const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* ctrl = smem + kMxStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 260);
+  uint8_t* sf_ring = ctrl + 4096;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kMxStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kMxStages;
+  const uint32_t bar_tempty = bar_tfull + 8;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMxStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tempty, 8);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_valid = min(*p.num_valid, p.capacity);
+  const int num_m = num_valid / kBM;
+  const int total_tiles = num_m * p.tiles_n;
+  const int stride = gridDim.x;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0, kbi = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
+        const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+        const int expert = p.expert_ids[tc.m_blk];
+        if (expert < 0 || expert >= p.num_experts) continue;
+        const int nb0 = min(2 * tc.n_blk, p.n_blocks128 - 1);
+        const int nb1 = min(2 * tc.n_blk + 1, p.n_blocks128 - 1);
+        const uint8_t* sfa_t = p.sfa + (int64_t)tc.m_blk * p.num_kb * 512;
+        const uint8_t* sfb0 = p.sfb + ((int64_t)expert * p.n_blocks128 + nb0) * p.num_kb * 512;
+        const uint8_t* sfb1 = p.sfb + ((int64_t)expert * p.n_blocks128 + nb1) * p.num_kb * 512;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * s;
+          const uint32_t sa = smem_base + s * kStageBytes;
+          const uint32_t sf = smem_u32(sf_ring) + (kbi % kMxSfSlots) * kMxSfSlotBytes;
+          ++kbi;
+          mbar_expect_tx(full, kStageBytes + kMxSfSlotBytes);
+          bulk_load(sf, sfa_t + (int64_t)kb * 512, 512, full);
+          bulk_load(sf + 512, sfb0 + (int64_t)kb * 512, 512, full);
+          bulk_load(sf + 1024, sfb1 + (int64_t)kb * 512, 512, full);
+          tma_load_2d(sa, &tma_a, full, kb * 128, tc.m_blk * kBM);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tma_load_3d(sa + kABytes + j * (kBBytes / 4), &tma_b, full, kb * 128,
+                        tc.n_blk * 256 + j * 64, expert);
+          if (++s == kMxStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0, tph = 0, kbi = 0;
+      bool ok = true;
+      const uint32_t sfa_t = tmem_base + 256, sfb_t = tmem_base + 260;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
+        const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+        const int expert = p.expert_ids[tc.m_blk];
+        if (expert < 0 || expert >= p.num_experts) continue;
+        ok = mbar_wait(bar_tempty, tph ^ 1, abort_flag, p.status, 2);
+        if (!ok) break;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * kStageBytes;
+          const uint32_t sf = smem_u32(sf_ring) + (kbi % kMxSfSlots) * kMxSfSlotBytes;
+          ++kbi;
+          tc_cp_sf(sfa_t, make_sf_desc(sf));
+          tc_cp_sf(sfb_t, make_sf_desc(sf + 512));
+          tc_cp_sf(sfb_t + 4, make_sf_desc(sf + 1024));
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + kABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_mx(tmem_base, adesc + 2 * k, bdesc + 2 * k,
+                      p.idesc | ((uint32_t)k << 4) | ((uint32_t)k << 29), sfa_t, sfb_t,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(bar_empty + 8 * s);
+          if (++s == kMxStages) { s = 0; ph ^= 1; }
+        }
+        if (ok) tc_commit(bar_tfull);
+        tph ^= 1;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue -----------------------------------
+    const int q = warp & 3;
+    const int h = (warp - 4) >> 2;
+    const int row_in_tile = 32 * q + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * q) << 16) + h * kHalfCols;
+    const bool has_ids = p.sorted_ids != nullptr;
+    const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
+    uint8_t* out_stage = ctrl + 4096 + kMxSfSlots * kMxSfSlotBytes + (warp - 4) * 2560;
+    uint32_t tph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
+      const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+      const int expert = p.expert_ids[tc.m_blk];
+      if (expert < 0 || expert >= p.num_experts) continue;
+      const int row = tc.m_blk * kBM + row_in_tile;
+      const int tile_row0 = tc.m_blk * kBM + 32 * q;
+      const int sid = has_ids ? p.sorted_ids[row] : 0;
+      const float rw = has_rw ? p.sorted_weights[row] : 1.0f;
+      const int token = sid & 0xFFFFFF;
+      const bool live = token < p.num_tokens;
+      int64_t out_row = row;
+      if (p.scatter) out_row = (int64_t)token * p.topk + ((uint32_t)sid >> 24);
+      const int64_t row_off = out_row * p.c_ld;
+      const int ocol = tc.n_blk * 256 + 128 * h;
+      ok = mbar_wait(bar_tfull, tph, abort_flag, p.status, 4);
+      if (!ok) break;
+      tph ^= 1;
+      tc_fence_after();
+      if (lane == 0) bulk_wait_read();
+      __syncwarp();
+#pragma unroll 1
+      for (int i = 0; i < 4; ++i) {
+        uint32_t raw[32];
+        tmem_ld32(lane_addr + 32 * i, raw);
+        tmem_ld_wait();
+        if (i == 3) {   // this warp has read its part of the accumulator
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty);
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        if (has_rw) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= rw;
+        }
+        store_chunk<1>(out_stage, 0, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n, live, lane, v);
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  if (warp >= 4 && lane == 0) bulk_wait_all();
+  __syncwarp();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1076,8 +1312,14 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   const bool is16 = a->kind == BOLT_GEMM_BF16 || a->kind == BOLT_GEMM_F16;
   const bool block = a->kind == BOLT_GEMM_FP8_BLOCK || a->kind == BOLT_GEMM_INT8_BLOCK;
   const bool is_int = a->kind == BOLT_GEMM_INT8_CHANNEL || a->kind == BOLT_GEMM_INT8_BLOCK;
-  BOLT_REQUIRE(a->kind >= BOLT_GEMM_BF16 && a->kind <= BOLT_GEMM_INT8_BLOCK,
+  const bool mx = a->kind == BOLT_GEMM_MXFP8;
+  BOLT_REQUIRE(a->kind >= BOLT_GEMM_BF16 && a->kind <= BOLT_GEMM_MXFP8,
                "grouped_gemm: unknown kind %d", a->kind);
+  if (mx) {
+    BOLT_REQUIRE(a->epilogue == BOLT_EPI_STORE, "grouped_gemm: the MX kind has the plain epilogue only");
+    BOLT_REQUIRE(a->k % 128 == 0, "grouped_gemm: the MX kind needs k a multiple of 128");
+    BOLT_REQUIRE(a->bias == nullptr, "grouped_gemm: the MX kind takes no bias");
+  }
   const int elem = is16 ? 2 : 1;
   BOLT_REQUIRE(((int64_t)a->k * elem) % 16 == 0, "grouped_gemm: k*elem_size must be a multiple of 16");
   BOLT_REQUIRE((reinterpret_cast<uintptr_t>(a->a) | reinterpret_cast<uintptr_t>(a->b)) % 16 == 0,
@@ -1200,12 +1442,31 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   const uint32_t cfmt = is_int ? 2u : 1u;
   p.idesc = (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kAccCols >> 3) << 17) |
             ((uint32_t)(kBM >> 4) << 24);
+  if (mx) {
+    // block-scaled descriptor: e4m3 x e4m3 (formats 0), K-major, N >> 3 at bit 17, E8M0 scales
+    // (bit 23), M >> 4 at bit 24; the scale-byte selectors (bits 4-5, 29-30) are set per K step
+    p.idesc = ((uint32_t)(kAccCols >> 3) << 17) | (1u << 23) | ((uint32_t)(kBM >> 4) << 24);
+    p.sfa = reinterpret_cast<const uint8_t*>(a->a_scale);
+    p.sfb = reinterpret_cast<const uint8_t*>(a->b_scale);
+    p.n_blocks128 = (a->n + 127) / 128;
+  }
 
   int sms = a->sm_count > 0 ? a->sm_count : sm_count_of_current_device();
   const int max_tiles = (a->capacity / kBM) * p.tiles_n;
   const int grid = max_tiles < sms ? max_tiles : sms;
   if (grid <= 0) return BOLT_OK;
 
+  if (mx) {
+    static bool configured = false;
+    if (!configured) {
+      BOLT_CUDA(cudaFuncSetAttribute(k_mx_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMxSmemBytes));
+      configured = true;
+    }
+    k_mx_gemm<<<grid, kThreads, kMxSmemBytes, st>>>(ma, mb, mc, p);
+    BOLT_LAUNCH_CHECK();
+    return BOLT_OK;
+  }
   switch (a->kind) {
     case BOLT_GEMM_BF16:
     case BOLT_GEMM_F16: return launch_epi<OP_F16, false>(a->epilogue, ma, mb, mc, p, grid, st);

@@ -631,6 +631,35 @@ __global__ void __launch_bounds__(256) k_mx_dequant(const uint8_t* __restrict__ 
     out[o + i] = from_f32<TDeq>(float(*reinterpret_cast<const __nv_fp8_e4m3*>(&c[i])) * s);
 }
 
+// E8M0 bytes [rows, sf_cols] (one per 32 K elements) -> the tiled layout the block-scaled MMA
+// reads through TMEM: tiles of 128 rows x 4 K groups = 512 bytes, [row tile][K block][512], byte
+// (r % 32) * 16 + (r / 32) * 4 + g.  With row_ids the rows are gathered (sorted layout, token in
+// the low 24 bits); rows without a source get byte 0, a valid tiny scale.
+__global__ void __launch_bounds__(256) k_mx_sf_layout(const uint8_t* __restrict__ src,
+                                                      int64_t src_rows, int sf_cols,
+                                                      const int32_t* __restrict__ row_ids,
+                                                      const int32_t* __restrict__ num_valid,
+                                                      int64_t dst_rows,
+                                                      uint8_t* __restrict__ dst) {
+  const int num_kb = sf_cols / 4;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = tid / num_kb;
+  if (r >= dst_rows) return;
+  const int kb = (int)(tid - r * num_kb);
+  int64_t s = r;
+  bool ok = r < src_rows;
+  if (row_ids != nullptr) {
+    const int64_t valid = num_valid != nullptr ? *num_valid : dst_rows;
+    s = row_ids[r] & 0xFFFFFF;
+    ok = r < valid && s < src_rows;
+  }
+  uint32_t w = 0;
+  if (ok) w = *reinterpret_cast<const uint32_t*>(src + s * (int64_t)sf_cols + kb * 4);
+  const int rr = (int)(r & 127);
+  const int64_t off = ((r >> 7) * num_kb + kb) * 512 + (rr & 31) * 16 + (rr >> 5) * 4;
+  *reinterpret_cast<uint32_t*>(dst + off) = w;
+}
+
 }  // namespace
 }  // namespace bolt
 
@@ -785,6 +814,28 @@ extern "C" int bolt_mx_dequant_rows(const void* q, const uint8_t* scales, int64_
       break;
     default: set_error("mx_dequant: unsupported output dtype %d", out_dtype); return BOLT_ERR_INVALID;
   }
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+extern "C" int bolt_mx_sf_layout(const uint8_t* src, int64_t src_rows, int sf_cols,
+                                 const int32_t* row_ids, const int32_t* num_valid_ids,
+                                 int64_t dst_rows, uint8_t* dst, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(src_rows >= 0 && dst_rows >= 0 && dst_rows % 128 == 0,
+               "mx_sf_layout: dst_rows must be a multiple of 128");
+  BOLT_REQUIRE(sf_cols > 0 && sf_cols % 4 == 0, "mx_sf_layout: sf_cols %d must be a multiple of 4",
+               sf_cols);
+  if (dst_rows == 0) return BOLT_OK;
+  BOLT_REQUIRE(dst != nullptr && (src != nullptr || src_rows == 0), "mx_sf_layout: null pointer");
+  BOLT_REQUIRE((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 4 == 0,
+               "mx_sf_layout: buffers must be 4-byte aligned");
+  const int64_t threads = dst_rows * (sf_cols / 4);
+  const int64_t blocks = (threads + 255) / 256;
+  BOLT_REQUIRE(blocks < ((int64_t)1 << 31), "mx_sf_layout: too many elements");
+  k_mx_sf_layout<<<(unsigned)blocks, 256, 0, st>>>(src, src_rows, sf_cols, row_ids, num_valid_ids,
+                                                   dst_rows, dst);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }

@@ -45,6 +45,26 @@ def _decode_weights(w: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) ->
     return out
 
 
+def _tile_weight_scales(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """E8M0 bytes [E, N, K/32] -> the 512-byte tiles the block-scaled GEMM kind reads
+    ([E * ceil(N/128), K/128, 512]); done once per scale tensor, like the decoding above."""
+    key = ("sf", scale.data_ptr(), tuple(scale.shape), scale._version)
+    hit = _decoded.get(key)
+    if hit is not None and hit[0]() is scale:
+        return hit[2]
+    for k in [k for k, v in _decoded.items() if v[0]() is None or v[1]() is None]:
+        del _decoded[k]
+    e, n, sf_cols = scale.shape
+    n_pad = (n + 127) // 128 * 128
+    src = scale
+    if n_pad != n:
+        src = torch.zeros((e, n_pad, sf_cols), dtype=torch.uint8, device=scale.device)
+        src[:, :n] = scale
+    out = ops.mx_sf_layout(src.reshape(e * n_pad, sf_cols), e * n_pad)
+    _decoded[key] = (weakref.ref(scale), weakref.ref(scale), out)
+    return out
+
+
 def validate(hidden_states, w1, w2, w1_scale, w2_scale, a1_scale, a2_scale, b1, b2,
              apply_router_weight_on_input, output_dtype, block_shape, activation, is_gated,
              inplace, no_combine) -> None:
@@ -98,9 +118,20 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
     oai = activation == "swigluoai"
     alpha = (1.702 if oai else 1.0) if gemm1_alpha is None else gemm1_alpha
     beta = (1.0 if oai else 0.0) if gemm1_beta is None else gemm1_beta
-    kind = _cabi.GEMM_BF16 if dtype == torch.bfloat16 else _cabi.GEMM_F16
-    w1_d = _decode_weights(w1, w1_scale, dtype)
-    w2_d = _decode_weights(w2, w2_scale, dtype)
+    # Both reduction lengths in whole 128-wide K blocks: the tensor core applies the E8M0 scales
+    # itself (BOLT_GEMM_MXFP8) and the weights stay in 8 bits.  Otherwise the operands are
+    # dequantised (exactly) and the 16-bit kind computes the same contraction.
+    native = hidden % 128 == 0 and inter % 128 == 0
+    if native:
+        kind = _cabi.GEMM_MXFP8
+        w1 = w1 if w1.is_contiguous() else w1.contiguous()
+        w2 = w2 if w2.is_contiguous() else w2.contiguous()
+        sfb1 = _tile_weight_scales(w1, w1_scale)
+        sfb2 = _tile_weight_scales(w2, w2_scale)
+    else:
+        kind = _cabi.GEMM_BF16 if dtype == torch.bfloat16 else _cabi.GEMM_F16
+        w1_d = _decode_weights(w1, w1_scale, dtype)
+        w2_d = _decode_weights(w2, w2_scale, dtype)
     expert_mask = (expert_map >= 0).to(torch.int32) if expert_map is not None else None
     if topk_ids.dtype != torch.int32:
         topk_ids = topk_ids.to(torch.int32)
@@ -124,26 +155,39 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
         cap = sorted_ids.shape[0]
         common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
                       sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
-        # A1: quantise + dequantise once per token, gather into sorted rows
-        _, _, x_d = ops.mx_quant_rows(hidden_states[begin:end], want_codes=False, deq_dtype=dtype)
-        a_sorted, _ = ops.gather_rows(x_d, sorted_ids, num_valid, cap)
-        # GEMM1, rounded to the input dtype
         g1 = torch.empty((cap, n1), device=dev, dtype=dtype)
-        ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1_d, c=g1, **common)
-        # split gated activation in fp32 + second quantisation, dequantised for GEMM2
-        _, _, act = ops.mx_quant_rows(g1, gated=True, alpha=alpha, beta=beta, limit=gemm1_limit,
-                                      want_codes=False, deq_dtype=dtype)
+        if native:
+            # A1: codes + exponent bytes once per token; codes gathered into sorted rows, bytes
+            # gathered straight into the tiled layout
+            x_q, x_s, _ = ops.mx_quant_rows(hidden_states[begin:end])
+            a_sorted, _ = ops.gather_rows(x_q, sorted_ids, num_valid, cap)
+            sfa = ops.mx_sf_layout(x_s, cap, sorted_ids, num_valid)
+            # GEMM1, rounded to the input dtype
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1, c=g1, a_scale=sfa,
+                             b_scale=sfb1, **common)
+            # split gated activation in fp32 + second quantisation (rows are already sorted)
+            act, act_s, _ = ops.mx_quant_rows(g1, gated=True, alpha=alpha, beta=beta,
+                                              limit=gemm1_limit)
+            gemm2 = dict(a=act, b=w2, a_scale=ops.mx_sf_layout(act_s, cap), b_scale=sfb2)
+        else:
+            _, _, x_d = ops.mx_quant_rows(hidden_states[begin:end], want_codes=False,
+                                          deq_dtype=dtype)
+            a_sorted, _ = ops.gather_rows(x_d, sorted_ids, num_valid, cap)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1_d, c=g1, **common)
+            _, _, act = ops.mx_quant_rows(g1, gated=True, alpha=alpha, beta=beta,
+                                          limit=gemm1_limit, want_codes=False, deq_dtype=dtype)
+            gemm2 = dict(a=act, b=w2_d)
         # GEMM2 in fp32 with the router weight, then the fp32 sum over the routes
         if no_combine:
             c3 = torch.zeros((m * topk, model_dim), device=dev, dtype=torch.float32) \
                 if expert_map is not None else \
                 torch.empty((m * topk, model_dim), device=dev, dtype=torch.float32)
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2_d, c=c3, scatter=True,
-                             mul_routed_weight=False, **common)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, c=c3, scatter=True,
+                             mul_routed_weight=False, **gemm2, **common)
             out[begin:end].copy_(c3.view(m, topk, model_dim))
         else:
             c_sorted = torch.empty((cap, model_dim), device=dev, dtype=torch.float32)
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2_d, c=c_sorted, scatter=False,
-                             mul_routed_weight=True, **common)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, c=c_sorted, scatter=False,
+                             mul_routed_weight=True, **gemm2, **common)
             ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
     return out

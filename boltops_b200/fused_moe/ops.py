@@ -260,6 +260,23 @@ def mx_dequant_rows(q: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtyp
     return out
 
 
+def mx_sf_layout(scales: torch.Tensor, dst_rows: int, row_ids: Optional[torch.Tensor] = None,
+                 num_valid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """E8M0 bytes [rows, K/32] → 512-byte tiles [dst_rows/128, K/128, 512] for the MX GEMM kind
+    (optionally gathering rows through the sorted ids)."""
+    _require_cuda(scales)
+    lib = _cabi.load()
+    scales = scales.contiguous()
+    rows, sf_cols = scales.shape
+    assert scales.dtype == torch.uint8 and sf_cols % 4 == 0 and dst_rows % 128 == 0
+    dst = torch.empty((dst_rows // 128, sf_cols // 4, 512), dtype=torch.uint8, device=scales.device)
+    with torch.cuda.device(scales.device):
+        check(lib.bolt_mx_sf_layout(ptr(scales), rows, sf_cols, ptr(row_ids), ptr(num_valid),
+                                    dst_rows, ptr(dst), stream_of(scales)))
+    _count()
+    return dst
+
+
 def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
             routed_scaling_factor: float = 1.0,
             router_weights: Optional[torch.Tensor] = None) -> torch.Tensor:

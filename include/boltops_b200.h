@@ -63,7 +63,11 @@ enum bolt_gemm_kind {
   BOLT_GEMM_FP8_BLOCK = 2,    /* e4m3, [128,128] weight blocks, 1x128 activation groups */
   BOLT_GEMM_INT8_CHANNEL = 3, /* int8, per-row activation / per-output-channel weight   */
   BOLT_GEMM_FP8_CHANNEL = 4,  /* e4m3, per-row activation / per-output-channel weight   */
-  BOLT_GEMM_INT8_BLOCK = 5    /* int8, [128,128] weight blocks, 1x128 activation groups */
+  BOLT_GEMM_INT8_BLOCK = 5,   /* int8, [128,128] weight blocks, 1x128 activation groups */
+  BOLT_GEMM_MXFP8 = 6         /* e4m3 with one E8M0 byte per 32 K elements on both operands,
+                                 applied by the tensor core; a_scale / b_scale carry BYTE
+                                 arrays in the tiled layout of bolt_mx_sf_layout; plain
+                                 epilogue only, k a multiple of 128                        */
 };
 
 enum bolt_gemm_epilogue {
@@ -242,6 +246,16 @@ int bolt_mx_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int g
  */
 int bolt_mx_dequant_rows(const void* q, const uint8_t* scales, int64_t rows, int cols, void* out,
                          int out_dtype, void* stream);
+
+/* E8M0 bytes [src_rows, sf_cols] (sf_cols = K/32, a multiple of 4) -> the tiled layout that
+ * BOLT_GEMM_MXFP8 reads: [dst_rows/128][sf_cols/4][512] bytes, byte (r%32)*16 + (r/32)*4 + g for
+ * row r of a 128-row tile and K group g of a 128-wide K block.  row_ids (optional) gathers rows
+ * as the expert-sorted layout does (token in the low 24 bits, rows at or beyond
+ * num_valid_ids[0] and padding ids get byte 0).  No reference counterpart: the reference's
+ * Triton kernel reads the plain [rows, K/32] array (boltops/fused_moe/triton/mxfp8.py).
+ */
+int bolt_mx_sf_layout(const uint8_t* src, int64_t src_rows, int sf_cols, const int32_t* row_ids,
+                      const int32_t* num_valid_ids, int64_t dst_rows, uint8_t* dst, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Activations.  Replaces _apply_activation / moe_activation

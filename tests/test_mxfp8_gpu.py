@@ -60,9 +60,10 @@ def _random_mx_weights(e, n, k, seed):
 
 
 @pytest.mark.parametrize("masked", [False, True])
-def test_mxfp8_layer_random_vs_oracle(masked):
+@pytest.mark.parametrize("inter", [128, 96])   # 128: tensor-core MX kind; 96: dequantised 16-bit kind
+def test_mxfp8_layer_random_vs_oracle(masked, inter):
     from boltops_b200.fused_moe import fused_experts
-    m, e, k, h, inter = 150, 8, 2, 256, 128
+    m, e, k, h = 150, 8, 2, 256
     w1, s1 = _random_mx_weights(e, 2 * inter, h, 1)
     w2, s2 = _random_mx_weights(e, h, inter, 2)
     x = (torch.randn(m, h, generator=torch.Generator().manual_seed(4)) * 0.5).bfloat16()
@@ -80,3 +81,47 @@ def test_mxfp8_layer_random_vs_oracle(masked):
                         expert_map=None if emap is None else emap.cuda(),
                         global_num_experts=e)
     assert O.rel_l2(out.cpu(), ref) <= 2e-2
+
+
+@pytest.mark.parametrize("m,e,topk,n,k", [(150, 4, 2, 512, 256), (40, 3, 1, 384, 128), (600, 8, 2, 256, 1024)])
+@pytest.mark.parametrize("c_dtype", [torch.float32, torch.bfloat16])
+def test_mx_grouped_gemm_kind(m, e, topk, n, k, c_dtype):
+    """The tensor-core block-scaled kind against an fp32 matmul over the dequantised operands."""
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(m + n)
+    x = (torch.randn(m, k) * 0.7).bfloat16().cuda()
+    w, ws = _random_mx_weights(e, n, k, 5)
+    wts, ids = O.make_routing(m, e, topk, 21)
+    pos = torch.empty((m, topk), dtype=torch.int32, device="cuda")
+    s_ids, s_w, s_e, nv, _, _ = ops.moe_sorting_ck(ids.cuda(), wts.cuda(), e, None, None, 128, None,
+                                                   alloc_moe_buf=False, route_pos=pos)
+    cap = s_ids.shape[0]
+    q, sc, deq = ops.mx_quant_rows(x, deq_dtype=torch.float32)
+    a_sorted, _ = ops.gather_rows(q, s_ids, nv, cap)
+    sfa = ops.mx_sf_layout(sc, cap, s_ids, nv)
+    n_pad = (n + 127) // 128 * 128
+    ws_pad = torch.zeros(e, n_pad, k // 32, dtype=torch.uint8)
+    ws_pad[:, :n] = ws
+    sfb = ops.mx_sf_layout(ws_pad.view(e * n_pad, k // 32).cuda(), e * n_pad)
+    c = torch.full((cap, n), -7.0, dtype=c_dtype, device="cuda")
+    ops.grouped_gemm(kind=_cabi.GEMM_MXFP8, epilogue=_cabi.EPI_STORE, a=a_sorted, b=w.cuda(), c=c,
+                     a_scale=sfa, b_scale=sfb, sorted_expert_ids=s_e, num_valid=nv,
+                     sorted_ids=s_ids, sorted_weights=s_w, num_tokens=m, topk=topk,
+                     mul_routed_weight=True)
+    torch.cuda.synchronize()
+    ops.check_device_status(torch.device("cuda"))
+    wd = O.mx_dequant_weight(w, ws)
+    deq = deq.cpu()
+    pos = pos.cpu()
+    got = c.cpu().float()
+    worst = 0.0
+    for t in range(m):
+        for j in range(topk):
+            r = int(pos[t, j])
+            ref = (deq[t] @ wd[int(ids[t, j])].T) * wts[t, j]
+            if c_dtype != torch.float32:
+                ref = ref.to(c_dtype).float()
+            err = (got[r] - ref).abs().max() / ref.abs().max().clamp_min(1e-6)
+            worst = max(worst, float(err))
+    assert worst <= (1e-5 if c_dtype == torch.float32 else 1e-2), worst
