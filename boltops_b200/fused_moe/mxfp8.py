@@ -8,14 +8,15 @@ rounded to the input dtype; the split gated activation and the second quantisati
 on that; GEMM2 and the router weights stay in fp32 until the sum over a token's routes; one cast
 at the end.
 
-How it runs here.  An e4m3 value times a power of two is exactly representable in bf16 / fp16,
-and products of two such values are exact in fp32, so the MX contraction equals a 16-bit GEMM
-over the DEQUANTISED operands with fp32 accumulation.  The layer therefore quantises and
-dequantises activations in one kernel (`bolt_mx_quant_rows`), decodes the checkpoint weights
-once to the activation dtype (`bolt_mx_dequant_rows`, cached per weight tensor) and runs the
-16-bit grouped GEMM.  Numerically this is the MX recipe; in memory traffic it is a 16-bit layer
-(the decoded weights take twice the bytes of the e4m3 codes).  A mainloop on the tensor cores'
-block-scaled e4m3 instruction, which keeps the weights in 8 bits, is not built.
+How it runs here.  When both reduction lengths (hidden and intermediate size) are whole
+128-wide K blocks, the two GEMMs use the tensor cores' block-scaled e4m3 instruction
+(`BOLT_GEMM_MXFP8`): codes stay 8-bit, the exponent bytes are re-tiled once per call for the
+activations (`bolt_mx_sf_layout`) and once per weight tensor (cached).  Other shapes rely on an
+identity: an e4m3 value times a power of two is exactly representable in bf16 / fp16 and
+products of two such values are exact in fp32, so the MX contraction equals a 16-bit GEMM over
+the DEQUANTISED operands with fp32 accumulation; activations are then dequantised in the
+quantiser kernel itself and the checkpoint weights decoded once (`bolt_mx_dequant_rows`,
+cached), at 16-bit memory traffic.
 """
 from __future__ import annotations
 
