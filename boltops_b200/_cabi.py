@@ -53,6 +53,8 @@ class GemmArgs(C.Structure):
         ("sorted_ids", C.c_void_p), ("sorted_weights", C.c_void_p),
         ("sorted_expert_ids", C.c_void_p), ("num_valid_ids", C.c_void_p),
         ("status", C.c_void_p), ("sm_count", C.c_int),
+        ("act_alpha", C.c_float), ("act_beta", C.c_float), ("act_limit", C.c_float),
+        ("act_has_limit", C.c_int),
     ]
 
 
@@ -127,7 +129,7 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.bolt_abi_version() != 1:
+    if lib.bolt_abi_version() != 2:
         raise RuntimeError("libboltops_b200.so ABI version mismatch")
     _lib = lib
     return lib

@@ -94,6 +94,8 @@ struct GemmParams {
   const uint8_t* sfa;   // [capacity/128][num_kb][512]
   const uint8_t* sfb;   // [num_experts][n_blocks128][num_kb][512]
   int n_blocks128;
+  float act_alpha, act_beta, act_limit;   // MX gated epilogue
+  int act_has_limit;
 };
 
 // ---------------------------------------------------------------------------
@@ -1058,6 +1060,12 @@ constexpr int kMxSfSlotBytes = 512 * 3;   // A scales + two 128-row blocks of B 
 constexpr int kMxSmemBytes = kMxStages * kStageBytes + 4096 + kMxSfSlots * kMxSfSlotBytes +
                              8 * 2560 + 1024;
 
+//
+// GATED: B rows are loaded as [gate n0.., up n0.., gate n0+64.., up n0+64..] (64 each) so that a
+// thread holds 32 gate columns and their 32 up columns; the epilogue rounds both through
+// mid_dtype, applies min(g,L) * sigmoid(alpha g) * (clamp(u,+-L) + beta) in fp32 and quantises
+// the 32 results - exactly one MX group - to e4m3 codes and one exponent byte, all in registers.
+template <bool GATED>
 __global__ void __launch_bounds__(kThreads, 1)
 k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
           const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
@@ -1135,7 +1143,9 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             tma_load_3d(sa + kABytes + j * (kBBytes / 4), &tma_b, full, kb * 128,
-                        tc.n_blk * 256 + j * 64, expert);
+                        GATED ? ((j & 1) ? p.n_half : 0) + tc.n_blk * 128 + (j >> 1) * 64
+                              : tc.n_blk * 256 + j * 64,
+                        expert);
           if (++s == kMxStages) { s = 0; ph ^= 1; }
         }
       }
@@ -1208,24 +1218,86 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
       tc_fence_after();
       if (lane == 0) bulk_wait_read();
       __syncwarp();
+      if (!GATED) {
 #pragma unroll 1
-      for (int i = 0; i < 4; ++i) {
-        uint32_t raw[32];
-        tmem_ld32(lane_addr + 32 * i, raw);
-        tmem_ld_wait();
-        if (i == 3) {   // this warp has read its part of the accumulator
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tempty);
-        }
-        float v[32];
+        for (int i = 0; i < 4; ++i) {
+          uint32_t raw[32];
+          tmem_ld32(lane_addr + 32 * i, raw);
+          tmem_ld_wait();
+          if (i == 3) {   // this warp has read its part of the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty);
+          }
+          float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-        if (has_rw) {
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          if (has_rw) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= rw;
+            for (int j = 0; j < 32; ++j) v[j] *= rw;
+          }
+          store_chunk<1>(out_stage, 0, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n, live,
+                         lane, v);
         }
-        store_chunk<1>(out_stage, 0, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n, live, lane, v);
+      } else {
+        // half h: columns [0,64) gate and [64,128) up of output columns 128 n_blk + 64 h + [0,64)
+        const int ocol_g = tc.n_blk * 128 + 64 * h;
+        uint8_t* c8 = static_cast<uint8_t*>(p.c) + row * (int64_t)p.c_ld + ocol_g;
+        uint8_t* s8 = reinterpret_cast<uint8_t*>(p.c_scale) + row * p.c_scale_ld + ocol_g / 32;
+#pragma unroll 1
+        for (int i = 0; i < 2; ++i) {
+          uint32_t rg[32], ru[32];
+          tmem_ld32(lane_addr + 32 * i, rg);
+          tmem_ld32(lane_addr + 64 + 32 * i, ru);
+          tmem_ld_wait();
+          if (i == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty);
+          }
+          float v[32];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float g0 = __uint_as_float(rg[j]), g1 = __uint_as_float(rg[j + 1]);
+            float u0 = __uint_as_float(ru[j]), u1 = __uint_as_float(ru[j + 1]);
+            if (p.mid_dtype == BOLT_BF16) {
+              round2<BOLT_BF16>(g0, g1);
+              round2<BOLT_BF16>(u0, u1);
+            } else if (p.mid_dtype == BOLT_F16) {
+              round2<BOLT_F16>(g0, g1);
+              round2<BOLT_F16>(u0, u1);
+            }
+            if (p.act_has_limit) {
+              g0 = fminf(g0, p.act_limit);
+              g1 = fminf(g1, p.act_limit);
+              u0 = fminf(fmaxf(u0, -p.act_limit), p.act_limit);
+              u1 = fminf(fmaxf(u1, -p.act_limit), p.act_limit);
+            }
+            v[j] = g0 * __frcp_rn(1.0f + expf(-p.act_alpha * g0)) * (u0 + p.act_beta);
+            v[j + 1] = g1 * __frcp_rn(1.0f + expf(-p.act_alpha * g1)) * (u1 + p.act_beta);
+            if (!live) v[j] = v[j + 1] = 0.f;
+            amax = fmaxf(amax, fmaxf(fabsf(v[j]), fabsf(v[j + 1])));
+          }
+          amax = fmaxf(amax, 1.1754943508222875e-38f);
+          const float e =
+              fminf(fmaxf(ceilf(log2f(__fdiv_rn(amax, 448.0f))) + 127.0f, 0.0f), 254.0f);
+          const float down = exp2f(127.0f - e);
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                make_float2(v[4 * j] * down, v[4 * j + 1] * down), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                make_float2(v[4 * j + 2] * down, v[4 * j + 3] * down), __NV_SATFINITE, __NV_E4M3);
+            w[j] = lo | (hi << 16);
+          }
+          // padding rows are written too (zeros, exponent byte 0): the next GEMM streams them
+          uint4* dst = reinterpret_cast<uint4*>(c8 + 32 * i);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          s8[i] = live ? (uint8_t)(int)e : (uint8_t)0;
+        }
       }
     }
   }
@@ -1316,7 +1388,10 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   BOLT_REQUIRE(a->kind >= BOLT_GEMM_BF16 && a->kind <= BOLT_GEMM_MXFP8,
                "grouped_gemm: unknown kind %d", a->kind);
   if (mx) {
-    BOLT_REQUIRE(a->epilogue == BOLT_EPI_STORE, "grouped_gemm: the MX kind has the plain epilogue only");
+    BOLT_REQUIRE(a->epilogue == BOLT_EPI_STORE || a->epilogue == BOLT_EPI_SILU_MUL_QUANT,
+                 "grouped_gemm: the MX kind has the plain and the activation + MX-quantising epilogue");
+    BOLT_REQUIRE(a->epilogue == BOLT_EPI_STORE || (a->n / 2) % 128 == 0,
+                 "grouped_gemm: the MX gated epilogue needs n/2 a multiple of 128");
     BOLT_REQUIRE(a->k % 128 == 0, "grouped_gemm: the MX kind needs k a multiple of 128");
     BOLT_REQUIRE(a->bias == nullptr, "grouped_gemm: the MX kind takes no bias");
   }
@@ -1337,8 +1412,10 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   if (a->epilogue == BOLT_EPI_SILU_MUL_QUANT) {
     BOLT_REQUIRE(a->c_dtype == BOLT_FP8_E4M3 || a->c_dtype == BOLT_INT8,
                  "grouped_gemm: quantising epilogue needs an 8-bit c_dtype");
-    BOLT_REQUIRE(a->c_scale != nullptr && a->c_scale_ld >= a->capacity,
+    BOLT_REQUIRE(a->c_scale != nullptr &&
+                     a->c_scale_ld >= (mx ? (int64_t)(a->n / 2 / 32) : (int64_t)a->capacity),
                  "grouped_gemm: c_scale / c_scale_ld invalid");
+    BOLT_REQUIRE(!mx || a->c_dtype == BOLT_FP8_E4M3, "grouped_gemm: MX codes are e4m3");
     BOLT_REQUIRE(a->c_ld % 16 == 0 && reinterpret_cast<uintptr_t>(a->c) % 16 == 0,
                  "grouped_gemm: quantised output must be 16-byte aligned");
     BOLT_REQUIRE(!a->scatter, "grouped_gemm: quantising epilogue writes sorted rows only");
@@ -1448,7 +1525,11 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     p.idesc = ((uint32_t)(kAccCols >> 3) << 17) | (1u << 23) | ((uint32_t)(kBM >> 4) << 24);
     p.sfa = reinterpret_cast<const uint8_t*>(a->a_scale);
     p.sfb = reinterpret_cast<const uint8_t*>(a->b_scale);
-    p.n_blocks128 = (a->n + 127) / 128;
+    p.n_blocks128 = gated ? 2 * p.tiles_n : (a->n + 127) / 128;
+    p.act_alpha = a->act_alpha;
+    p.act_beta = a->act_beta;
+    p.act_limit = a->act_limit;
+    p.act_has_limit = a->act_has_limit;
   }
 
   int sms = a->sm_count > 0 ? a->sm_count : sm_count_of_current_device();
@@ -1459,11 +1540,16 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   if (mx) {
     static bool configured = false;
     if (!configured) {
-      BOLT_CUDA(cudaFuncSetAttribute(k_mx_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      BOLT_CUDA(cudaFuncSetAttribute(k_mx_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMxSmemBytes));
+      BOLT_CUDA(cudaFuncSetAttribute(k_mx_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kMxSmemBytes));
       configured = true;
     }
-    k_mx_gemm<<<grid, kThreads, kMxSmemBytes, st>>>(ma, mb, mc, p);
+    if (gated)
+      k_mx_gemm<true><<<grid, kThreads, kMxSmemBytes, st>>>(ma, mb, mc, p);
+    else
+      k_mx_gemm<false><<<grid, kThreads, kMxSmemBytes, st>>>(ma, mb, mc, p);
     BOLT_LAUNCH_CHECK();
     return BOLT_OK;
   }

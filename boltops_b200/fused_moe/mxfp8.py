@@ -46,16 +46,30 @@ def _decode_weights(w: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) ->
     return out
 
 
-def _tile_weight_scales(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+def _tile_weight_scales(w: torch.Tensor, scale: torch.Tensor, gated: bool = False) -> torch.Tensor:
     """E8M0 bytes [E, N, K/32] -> the 512-byte tiles the block-scaled GEMM kind reads
-    ([E * ceil(N/128), K/128, 512]); done once per scale tensor, like the decoding above."""
-    key = ("sf", scale.data_ptr(), tuple(scale.shape), scale._version)
+    ([E * ceil(N/128), K/128, 512]); done once per scale tensor, like the decoding above.
+    gated: rows in the order the gated kernel loads the weight rows of a tile
+    ([gate n0.., up n0.., gate n0+64.., up n0+64..], 64 rows each, n0 = 128 * column tile)."""
+    key = ("sf", scale.data_ptr(), tuple(scale.shape), scale._version, gated)
     hit = _decoded.get(key)
     if hit is not None and hit[0]() is scale:
         return hit[2]
     for k in [k for k, v in _decoded.items() if v[0]() is None or v[1]() is None]:
         del _decoded[k]
     e, n, sf_cols = scale.shape
+    if gated:
+        half = n // 2
+        assert half % 128 == 0 and e * n < (1 << 24)
+        j = torch.arange(256, device=scale.device)
+        # tile row j -> weight row: 64-row pieces gate, up, gate + 64, up + 64
+        piece = j // 64
+        within = (piece % 2) * half + (piece // 2) * 64 + j % 64
+        rows = (torch.arange(half // 128, device=scale.device)[:, None] * 128 + within[None, :])
+        idx = (torch.arange(e, device=scale.device)[:, None, None] * n + rows[None]).to(torch.int32)
+        out = ops.mx_sf_layout(scale.reshape(e * n, sf_cols), idx.numel(), idx.reshape(-1).contiguous())
+        _decoded[key] = (weakref.ref(scale), weakref.ref(scale), out)
+        return out
     n_pad = (n + 127) // 128 * 128
     src = scale
     if n_pad != n:
@@ -127,7 +141,7 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
         kind = _cabi.GEMM_MXFP8
         w1 = w1 if w1.is_contiguous() else w1.contiguous()
         w2 = w2 if w2.is_contiguous() else w2.contiguous()
-        sfb1 = _tile_weight_scales(w1, w1_scale)
+        sfb1 = _tile_weight_scales(w1, w1_scale, gated=True)
         sfb2 = _tile_weight_scales(w2, w2_scale)
     else:
         kind = _cabi.GEMM_BF16 if dtype == torch.bfloat16 else _cabi.GEMM_F16
@@ -156,24 +170,26 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
         cap = sorted_ids.shape[0]
         common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
                       sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
-        g1 = torch.empty((cap, n1), device=dev, dtype=dtype)
         if native:
             # A1: codes + exponent bytes once per token; codes gathered into sorted rows, bytes
             # gathered straight into the tiled layout
             x_q, x_s, _ = ops.mx_quant_rows(hidden_states[begin:end])
             a_sorted, _ = ops.gather_rows(x_q, sorted_ids, num_valid, cap)
             sfa = ops.mx_sf_layout(x_s, cap, sorted_ids, num_valid)
-            # GEMM1, rounded to the input dtype
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1, c=g1, a_scale=sfa,
-                             b_scale=sfb1, **common)
-            # split gated activation in fp32 + second quantisation (rows are already sorted)
-            act, act_s, _ = ops.mx_quant_rows(g1, gated=True, alpha=alpha, beta=beta,
-                                              limit=gemm1_limit)
+            # GEMM1 with the rounding to the input dtype, the split gated activation (fp32) and
+            # the second quantisation in its epilogue: 32 outputs of a thread are one MX group
+            act = torch.empty((cap, inter), device=dev, dtype=torch.float8_e4m3fn)
+            act_s = torch.empty((cap, inter // 32), device=dev, dtype=torch.uint8)
+            ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
+                             a_scale=sfa, b_scale=sfb1, c_scale=act_s, c_scale_ld=inter // 32,
+                             mid_dtype=dtype, act_alpha=alpha, act_beta=beta,
+                             act_limit=gemm1_limit, **common)
             gemm2 = dict(a=act, b=w2, a_scale=ops.mx_sf_layout(act_s, cap), b_scale=sfb2)
         else:
             _, _, x_d = ops.mx_quant_rows(hidden_states[begin:end], want_codes=False,
                                           deq_dtype=dtype)
             a_sorted, _ = ops.gather_rows(x_d, sorted_ids, num_valid, cap)
+            g1 = torch.empty((cap, n1), device=dev, dtype=dtype)
             ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1_d, c=g1, **common)
             _, _, act = ops.mx_quant_rows(g1, gated=True, alpha=alpha, beta=beta,
                                           limit=gemm1_limit, want_codes=False, deq_dtype=dtype)

@@ -362,7 +362,9 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
                  mid_dtype: Optional[torch.dtype] = None, scatter: bool = False,
                  num_tokens: int = 0, topk: int = 1, mul_routed_weight: bool = False,
                  sorted_ids: Optional[torch.Tensor] = None,
-                 sorted_weights: Optional[torch.Tensor] = None, sm_count: int = 0) -> None:
+                 sorted_weights: Optional[torch.Tensor] = None, sm_count: int = 0,
+                 act_alpha: float = 1.0, act_beta: float = 0.0,
+                 act_limit: Optional[float] = None) -> None:
     """One grouped expert GEMM launch (see ``bolt_grouped_gemm``)."""
     lib = _cabi.load()
     args = _cabi.GemmArgs()
@@ -395,6 +397,10 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
     args.num_valid_ids = ptr(num_valid)
     args.status = ptr(device_status(a.device))
     args.sm_count = sm_count
+    args.act_alpha = float(act_alpha)
+    args.act_beta = float(act_beta)
+    args.act_limit = float(act_limit or 0.0)
+    args.act_has_limit = int(act_limit is not None)
     with torch.cuda.device(a.device):
         check(lib.bolt_grouped_gemm(C.byref(args), stream_of(a)))
     _count()

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define BOLT_ABI_VERSION 1
+#define BOLT_ABI_VERSION 2
 
 enum bolt_status {
   BOLT_OK = 0,
@@ -341,6 +341,14 @@ typedef struct bolt_gemm_args {
   int32_t* status;          /* optional device int32: set non-zero if a bounded
                                device-side wait expired                          */
   int sm_count;             /* 0 = all SMs of the current device                 */
+  /* BOLT_GEMM_MXFP8 with BOLT_EPI_SILU_MUL_QUANT only: split gated activation
+     min(g,L) * sigmoid(alpha g) * (clamp(u,+-L) + beta) on the mid_dtype-rounded
+     GEMM result, then 1 x 32 MX quantisation: c = e4m3 codes [capacity, n/2],
+     c_scale = BYTES [capacity, c_scale_ld] (c_scale_ld >= n/2/32).               */
+  float act_alpha;
+  float act_beta;
+  float act_limit;
+  int act_has_limit;
 } bolt_gemm_args;
 
 int bolt_grouped_gemm(const bolt_gemm_args* args, void* stream);
