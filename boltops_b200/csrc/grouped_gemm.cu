@@ -1218,20 +1218,22 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
       tc_fence_after();
       if (lane == 0) bulk_wait_read();
       __syncwarp();
+      // With one accumulator stage the next tile's MMAs wait for this epilogue, so each warp
+      // first copies its 128 columns to registers, hands the accumulator back, and only then
+      // converts and stores.
+      uint32_t raw[4][32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tmem_ld32(lane_addr + 32 * i, raw[i]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty);
       if (!GATED) {
-#pragma unroll 1
+#pragma unroll
         for (int i = 0; i < 4; ++i) {
-          uint32_t raw[32];
-          tmem_ld32(lane_addr + 32 * i, raw);
-          tmem_ld_wait();
-          if (i == 3) {   // this warp has read its part of the accumulator
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty);
-          }
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[i][j]);
           if (has_rw) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= rw;
@@ -1244,17 +1246,10 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
         const int ocol_g = tc.n_blk * 128 + 64 * h;
         uint8_t* c8 = static_cast<uint8_t*>(p.c) + row * (int64_t)p.c_ld + ocol_g;
         uint8_t* s8 = reinterpret_cast<uint8_t*>(p.c_scale) + row * p.c_scale_ld + ocol_g / 32;
-#pragma unroll 1
+#pragma unroll
         for (int i = 0; i < 2; ++i) {
-          uint32_t rg[32], ru[32];
-          tmem_ld32(lane_addr + 32 * i, rg);
-          tmem_ld32(lane_addr + 64 + 32 * i, ru);
-          tmem_ld_wait();
-          if (i == 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty);
-          }
+          const uint32_t(&rg)[32] = raw[i];
+          const uint32_t(&ru)[32] = raw[2 + i];
           float v[32];
           float amax = 0.f;
 #pragma unroll
