@@ -40,6 +40,8 @@ WORKLOADS = {
     "qwen3_30b_int8_channel": dict(kind="int8_channel", E=128, K=8, H=2048, I=768, M=16384),
     "qwen3_235b_fp8_block_zipf": dict(kind="fp8_block", E=128, K=8, H=4096, I=1536, M=256,
                                       zipf=1.2),
+    # the DeepSeek-V3 shape in the native-MXFP8 recipe (E8M0 scale bytes per 32 K elements)
+    "deepseek_v3_mxfp8": dict(kind="mxfp8", E=256, K=8, H=7168, I=2048, M=4096),
 }
 DEFAULT_WORKLOAD = "deepseek_v3_fp8_block"
 
@@ -76,6 +78,16 @@ def _quant_block_fp8(w):
     return q, s.reshape(n // 128, k // 128)
 
 
+def _quant_mx(w):
+    """1 x 32 groups, exponent byte = ceil(log2(amax/448)) + 127, e4m3 codes."""
+    n, k = w.shape
+    v = w.float().reshape(n, k // 32, 32)
+    amax = v.abs().amax(-1).clamp_min(torch.finfo(torch.float32).tiny)
+    e = (torch.ceil(torch.log2(amax / 448.0)) + 127).clamp(0, 254)
+    q = (v * torch.exp2(127 - e)[..., None]).to(FP8).reshape(n, k)
+    return q, e.to(torch.uint8)
+
+
 def _quant_channel_int8(w):
     amax = w.float().abs().amax(dim=-1, keepdim=True).clamp(min=1e-10)
     s = amax / 127.0
@@ -96,6 +108,11 @@ def make_weights(cfg, device, experts, seed):
         w2 = torch.empty(n, H, I, dtype=FP8, device=device)
         w1s = torch.empty(n, 2 * I // 128, H // 128, dtype=torch.float32, device=device)
         w2s = torch.empty(n, H // 128, I // 128, dtype=torch.float32, device=device)
+    elif kind == "mxfp8":
+        w1 = torch.empty(n, 2 * I, H, dtype=FP8, device=device)
+        w2 = torch.empty(n, H, I, dtype=FP8, device=device)
+        w1s = torch.empty(n, 2 * I, H // 32, dtype=torch.uint8, device=device)
+        w2s = torch.empty(n, H, I // 32, dtype=torch.uint8, device=device)
     else:
         w1 = torch.empty(n, 2 * I, H, dtype=torch.int8, device=device)
         w2 = torch.empty(n, H, I, dtype=torch.int8, device=device)
@@ -111,6 +128,9 @@ def make_weights(cfg, device, experts, seed):
         elif kind == "fp8_block":
             w1[j], w1s[j] = _quant_block_fp8(m1)
             w2[j], w2s[j] = _quant_block_fp8(m2)
+        elif kind == "mxfp8":
+            w1[j], w1s[j] = _quant_mx(m1)
+            w2[j], w2s[j] = _quant_mx(m2)
         else:
             w1[j], w1s[j] = _quant_channel_int8(m1)
             w2[j], w2s[j] = _quant_channel_int8(m2)
@@ -150,6 +170,8 @@ def layer_kwargs(cfg, w1s, w2s):
         return dict(use_fp8_w8a8=True, w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
     if cfg["kind"] == "int8_channel":
         return dict(use_int8_w8a8=True, per_channel_quant=True, w1_scale=w1s, w2_scale=w2s)
+    if cfg["kind"] == "mxfp8":
+        return dict(use_mxfp8=True, w1_scale=w1s, w2_scale=w2s, block_shape=[1, 32])
     return {}
 
 
@@ -259,11 +281,13 @@ def gemm1_algorithmic(cfg, m, active_experts):
     routes = m * K
     wb = 2 if cfg["kind"] == "bf16" else 1
     ab = 2 if cfg["kind"] == "bf16" else 1
-    ob = 1 if cfg["kind"] == "fp8_block" else 2
+    ob = 1 if cfg["kind"] in ("fp8_block", "mxfp8") else 2
     byts = active_experts * 2 * I * H * wb + routes * H * ab + routes * I * ob
     if cfg["kind"] == "fp8_block":
         byts += active_experts * (2 * I // 128) * (H // 128) * 4 + routes * (H // 128) * 4 \
             + routes * (I // 128) * 4
+    if cfg["kind"] == "mxfp8":    # one scale byte per 32 elements of weights, inputs and outputs
+        byts += active_experts * 2 * I * (H // 32) + routes * (H // 32) + routes * (I // 32)
     return byts, 4.0 * routes * H * I
 
 
@@ -288,6 +312,8 @@ def cpu_reference(cfg, m, seed, budget_experts=None):
     if budget_experts is None:
         budget_experts = int(max(1, min(E, 15.0 * cores * 25e9 / max(per_expert_flops, 1.0))))
         budget_experts = max(1, min(budget_experts, 32 if cfg["kind"] != "bf16" else E))
+        if cfg["kind"] == "mxfp8":      # the oracle holds fp32 copies of the sampled experts
+            budget_experts = min(budget_experts, 8)
     es = budget_experts
     hidden, wts, ids = make_tokens(cfg, m, seed)
     w1, w2, w1s, w2s = make_weights(cfg, "cpu", list(range(es)), seed)
@@ -298,6 +324,8 @@ def cpu_reference(cfg, m, seed, budget_experts=None):
         O.moe_block_fp8(hidden, w1, w2, w1s, w2s, wts, ids, (128, 128), expert_map=emap)
     elif cfg["kind"] == "int8_channel":
         O.moe_per_channel(hidden, w1, w2, w1s, w2s, wts, ids, torch.int8, expert_map=emap)
+    elif cfg["kind"] == "mxfp8":
+        O.moe_mxfp8(hidden, w1, w2, w1s, w2s, wts, ids, expert_map=emap)
     else:
         sel_ids = torch.where(ids < es, ids, torch.full_like(ids, -1))
         O.moe_bf16(hidden, w1, w2, wts, sel_ids)
@@ -338,7 +366,8 @@ def main():
                   hidden=cfg["H"], intermediate=cfg["I"], tokens_per_gpu=m,
                   parallelism=f"ep{world}" if world > 1 else "single",
                   l2="inputs larger than L2 (weights stream from HBM every step)")
-    dtype = {"bf16": "bf16", "fp8_block": "fp8_e4m3", "int8_channel": "int8"}[cfg["kind"]]
+    dtype = {"bf16": "bf16", "fp8_block": "fp8_e4m3", "int8_channel": "int8",
+             "mxfp8": "mxfp8_e4m3"}[cfg["kind"]]
 
     if args.impl == "reference":
         if rank != 0:
@@ -575,7 +604,9 @@ def main():
                 ach = flops / (g_ms * 1e-3) / 1e12
                 roof = dict(bound="tensor", achieved=ach, peak=tc_peak, unit="TFLOP/s",
                             frac=ach / tc_peak, traffic=traffic)
-            roof.update(kernel="k_grouped_gemm (gate/up GEMM + SiLU-mul epilogue)",
+            roof.update(kernel=("k_mx_gemm (gate/up GEMM, tensor-core block scaling, activation + MX "
+                                "quantisation epilogue)" if cfg["kind"] == "mxfp8" else
+                                "k_grouped_gemm (gate/up GEMM + SiLU-mul epilogue)"),
                         ms_per_launch=g_ms, algorithmic_bytes=byts, algorithmic_flops=flops,
                         peak_source=peaks["source"] + (
                             "" if cfg["kind"] == "bf16" or t_hbm >= t_tc

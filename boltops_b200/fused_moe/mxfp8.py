@@ -28,6 +28,23 @@ import torch
 from .. import _cabi
 from . import ops
 
+
+class _Stage:
+    """Same per-stage CUDA-event bookkeeping as the main layer (off unless a timer is set)."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        from . import layer
+        self.t = layer.STAGE_TIMER
+        self.start = self.t.begin() if self.t is not None else None
+
+    def __exit__(self, *exc):
+        if self.t is not None:
+            self.t.end(self.name, self.start)
+        return False
+
 _decoded = {}     # (data_ptr, scale data_ptr, shape, dtype) -> (weakrefs of the sources, decoded tensor)
 
 
@@ -164,27 +181,32 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
         ids = topk_ids[begin:end].contiguous()
         wts = topk_weights[begin:end].contiguous()
         route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
-        sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
-            ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
-            alloc_moe_buf=False, route_pos=route_pos)
+        with _Stage("sort"):
+            sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
+                ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
+                alloc_moe_buf=False, route_pos=route_pos)
         cap = sorted_ids.shape[0]
         common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
                       sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
         if native:
             # A1: codes + exponent bytes once per token; codes gathered into sorted rows, bytes
             # gathered straight into the tiled layout
-            x_q, x_s, _ = ops.mx_quant_rows(hidden_states[begin:end])
-            a_sorted, _ = ops.gather_rows(x_q, sorted_ids, num_valid, cap)
-            sfa = ops.mx_sf_layout(x_s, cap, sorted_ids, num_valid)
+            with _Stage("quant_a1"):
+                x_q, x_s, _ = ops.mx_quant_rows(hidden_states[begin:end])
+            with _Stage("gather"):
+                a_sorted, _ = ops.gather_rows(x_q, sorted_ids, num_valid, cap)
+                sfa = ops.mx_sf_layout(x_s, cap, sorted_ids, num_valid)
             # GEMM1 with the rounding to the input dtype, the split gated activation (fp32) and
             # the second quantisation in its epilogue: 32 outputs of a thread are one MX group
             act = torch.empty((cap, inter), device=dev, dtype=torch.float8_e4m3fn)
             act_s = torch.empty((cap, inter // 32), device=dev, dtype=torch.uint8)
-            ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
-                             a_scale=sfa, b_scale=sfb1, c_scale=act_s, c_scale_ld=inter // 32,
-                             mid_dtype=dtype, act_alpha=alpha, act_beta=beta,
-                             act_limit=gemm1_limit, **common)
-            gemm2 = dict(a=act, b=w2, a_scale=ops.mx_sf_layout(act_s, cap), b_scale=sfb2)
+            with _Stage("gemm1"):
+                ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
+                                 a_scale=sfa, b_scale=sfb1, c_scale=act_s,
+                                 c_scale_ld=inter // 32, mid_dtype=dtype, act_alpha=alpha,
+                                 act_beta=beta, act_limit=gemm1_limit, **common)
+            with _Stage("scales_a2"):
+                gemm2 = dict(a=act, b=w2, a_scale=ops.mx_sf_layout(act_s, cap), b_scale=sfb2)
         else:
             _, _, x_d = ops.mx_quant_rows(hidden_states[begin:end], want_codes=False,
                                           deq_dtype=dtype)
@@ -204,7 +226,9 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             out[begin:end].copy_(c3.view(m, topk, model_dim))
         else:
             c_sorted = torch.empty((cap, model_dim), device=dev, dtype=torch.float32)
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, c=c_sorted, scatter=False,
-                             mul_routed_weight=True, **gemm2, **common)
-            ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
+            with _Stage("gemm2"):
+                ops.grouped_gemm(epilogue=_cabi.EPI_STORE, c=c_sorted, scatter=False,
+                                 mul_routed_weight=True, **gemm2, **common)
+            with _Stage("combine"):
+                ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
     return out
