@@ -48,7 +48,18 @@ def _worker(rank, world, port, ret):
                          w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
         torch.cuda.synchronize()
         assert ep.last_stats.get("mode") == "replicated"
-        ret[rank] = max(O.rel_l2(out.cpu(), full.cpu()), O.rel_l2(rep.cpu(), full.cpu()))
+        err = max(O.rel_l2(out.cpu(), full.cpu()), O.rel_l2(rep.cpu(), full.cpu()))
+        # the MXFP8 recipe through the same dispatch (rows travel in 16 bits, experts quantise)
+        ep.replicate_below = 0
+        mcfg = dict(cfg, kind="mxfp8")
+        mw1, mw2, ms1, ms2 = B.make_weights(mcfg, dev, mine, 0)
+        mx = ep.forward(hidden.to(dev), mw1, mw2, wts.to(dev), ids.to(dev), use_mxfp8=True,
+                        w1_scale=ms1, w2_scale=ms2, block_shape=[1, 32])
+        fw1, fw2, fs1, fs2 = B.make_weights(mcfg, dev, list(range(cfg["E"])), 0)
+        mfull = fused_experts(hidden.to(dev), fw1, fw2, wts.to(dev), ids.to(dev), use_mxfp8=True,
+                              w1_scale=fs1, w2_scale=fs2, block_shape=[1, 32])
+        torch.cuda.synchronize()
+        ret[rank] = max(err, O.rel_l2(mx.cpu(), mfull.cpu()))
     finally:
         dist.destroy_process_group()
 
