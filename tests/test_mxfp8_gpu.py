@@ -125,3 +125,24 @@ def test_mx_grouped_gemm_kind(m, e, topk, n, k, c_dtype):
             err = (got[r] - ref).abs().max() / ref.abs().max().clamp_min(1e-6)
             worst = max(worst, float(err))
     assert worst <= (1e-5 if c_dtype == torch.float32 else 1e-2), worst
+
+
+def test_mxfp8_layer_chunked_scaled_inplace(monkeypatch):
+    """Token chunking, routed_scaling_factor and inplace go through the MX path unchanged."""
+    from boltops_b200.fused_moe import fused_experts
+    m, e, k, h, inter = 200, 4, 2, 128, 128
+    w1, s1 = _random_mx_weights(e, 2 * inter, h, 7)
+    w2, s2 = _random_mx_weights(e, h, inter, 8)
+    x = (torch.randn(m, h, generator=torch.Generator().manual_seed(1)) * 0.5).bfloat16()
+    wts, ids = O.make_routing(m, e, k, 2)
+    ref = (O.moe_mxfp8(x, w1, w2, s1, s2, wts, ids).float() * 2.0)
+    args = (w1.cuda(), w2.cuda(), wts.cuda(), ids.cuda())
+    kw = dict(use_mxfp8=True, w1_scale=s1.cuda(), w2_scale=s2.cuda(), block_shape=[1, 32],
+              routed_scaling_factor=2.0)
+    whole = fused_experts(x.cuda(), *args, **kw)
+    monkeypatch.setenv("BOLTOPS_FUSED_MOE_CHUNK_SIZE", "64")
+    xin = x.cuda().clone()
+    out = fused_experts(xin, *args, inplace=True, **kw)
+    assert out.data_ptr() == xin.data_ptr()
+    assert torch.equal(out.cpu(), whole.cpu())          # rows are independent of the chunking
+    assert O.rel_l2(out.cpu().float(), ref) <= 2e-2
