@@ -1439,7 +1439,7 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(&ma, dt, 2, const_cast<void*>(a->a), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
       set_error("grouped_gemm: tensor map for A failed (CUresult %d)", (int)r);
       return BOLT_ERR_CUDA;
