@@ -45,13 +45,76 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "deepseek_v3_fp8_block"
 
-# DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), keyed by
-# (workload, tokens); None when no capture exists for that case.
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of
+# one ncu capture), keyed by (workload, tokens); None when no capture exists for that case.
+# The capture ran on 64 of the 256 experts with the same rows per expert; DRAM traffic of this
+# kernel is proportional to the expert count, so the figure is that capture's times 256/64.
 NCU_TRAFFIC_BYTES = {
-    # profiles/grouped_gemm_fp8_block_dsv3_E64_M1024.md: 2.196 GB per launch at E=64 (same rows per
-    # expert), scaled by 256/64 -- DRAM traffic of this kernel is proportional to the expert count
     ("deepseek_v3_fp8_block", 4096): 8.78e9,
 }
+
+# Dense 8-bit tensor-core peaks of this pool's B200s, measured with the recipe of the bf16
+# figure in MEASURED_PEAKS.json (8192^3, best of 10 = burst, back to back for 4 s = sustained;
+# `python bench.py --measure-peaks` repeats the measurement and prints it).
+TENSOR_PEAKS_8BIT = {
+    "fp8": dict(burst=None, sustained=None),
+    "int8": dict(burst=None, sustained=None),
+    "source": None,
+}
+
+
+def measure_tensor_peaks(device):
+    """Library GEMM peaks (cuBLASLt through torch): bf16, e4m3 and int8 at 8192^3."""
+    n = 8192
+    out = {}
+
+    def run(name, fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        reps = 0
+        while time.perf_counter() - t0 < 4.0:
+            for _ in range(20):
+                fn()
+            reps += 20
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = dict(burst=2.0 * n ** 3 / (best * 1e-3) / 1e12,
+                         sustained=2.0 * n ** 3 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+
+    a16 = torch.randn(n, n, device=device, dtype=torch.bfloat16)
+    b16 = torch.randn(n, n, device=device, dtype=torch.bfloat16)
+    run("bf16", lambda: torch.matmul(a16, b16))
+    a8, b8 = a16.to(FP8), b16.to(FP8).t().contiguous().t()
+    one = torch.ones((), device=device, dtype=torch.float32)
+    try:
+        run("fp8", lambda: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one,
+                                            out_dtype=torch.bfloat16))
+    except Exception as exc:  # noqa: BLE001 - report and carry on
+        out["fp8"] = dict(error=str(exc)[:200])
+    ai = torch.randint(-8, 8, (n, n), device=device, dtype=torch.int8)
+    bi = torch.randint(-8, 8, (n, n), device=device, dtype=torch.int8).t().contiguous().t()
+    try:
+        run("int8", lambda: torch._int_mm(ai, bi))
+    except Exception as exc:  # noqa: BLE001
+        out["int8"] = dict(error=str(exc)[:200])
+    out["how"] = ("torch.matmul bf16 / torch._scaled_mm e4m3 (bf16 out) / torch._int_mm, 8192^3, "
+                  "2*N^3 ops: best of 10 (burst) and back to back for 4 s (sustained)")
+    out["torch"] = torch.__version__
+    out["gpu"] = torch.cuda.get_device_name(device)
+    return out
 
 
 def load_peaks():
@@ -64,6 +127,18 @@ def load_peaks():
                     source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0,
                 source="fallback")
+
+
+def tensor_peak(kind, peaks):
+    """(TFLOP/s, source) of the dense tensor-core peak a workload kind is held against: the
+    measured burst figure of the matching library GEMM, else twice the measured bf16 figure."""
+    if kind == "bf16":
+        return peaks["bf16_tflops"], peaks["source"] + " bf16 burst (MEASURED_PEAKS.json)"
+    key = "int8" if kind.startswith("int8") else "fp8"
+    got = TENSOR_PEAKS_8BIT[key]["burst"]
+    if got:
+        return got, f"measured {key} burst ({TENSOR_PEAKS_8BIT['source']})"
+    return 2.0 * peaks["bf16_tflops"], peaks["source"] + " bf16 burst x2 (no measured 8-bit peak)"
 
 
 # ---------------------------------------------------------------------------
@@ -336,6 +411,33 @@ def cpu_reference(cfg, m, seed, budget_experts=None):
     return m / full, cores, sample, full
 
 
+def spot_check(cfg, out, hidden_h, wts_h, ids_h, device, seed, tokens=4):
+    """rel-L2 of ``out`` against the CPU oracle on a few tokens; only the experts those tokens
+    use are built (on the device, from the per-expert seed) and copied to the host."""
+    from oracle import moe_oracle as O
+
+    m = hidden_h.shape[0]
+    toks = sorted({0, m // 3, (2 * m) // 3, m - 1})[:tokens]
+    used = sorted(set(ids_h[toks].reshape(-1).tolist()))
+    remap = {e: j for j, e in enumerate(used)}
+    w1, w2, w1s, w2s = (None if t is None else t.cpu()
+                        for t in make_weights(cfg, device, used, seed))
+    loc = torch.tensor([[remap[int(e)] for e in row] for row in ids_h[toks]], dtype=torch.int32)
+    h, w = hidden_h[toks], wts_h[toks]
+    if cfg["kind"] == "fp8_block":
+        expect, tol = O.moe_block_fp8(h, w1, w2, w1s, w2s, w, loc, (128, 128)), 2e-2
+    elif cfg["kind"] == "int8_channel":
+        expect, tol = O.moe_per_channel(h, w1, w2, w1s, w2s, w, loc, torch.int8), 2e-2
+    elif cfg["kind"] == "mxfp8":
+        expect, tol = O.moe_mxfp8(h, w1, w2, w1s, w2s, w, loc), 2e-2
+    else:
+        expect, tol = O.moe_bf16(h, w1, w2, w, loc), 1e-2
+    torch.cuda.synchronize()
+    err = O.rel_l2(out[toks].cpu(), expect)
+    return dict(rel_l2=err, tolerance=tol, tokens=len(toks), experts_rebuilt=len(used),
+                ok=bool(err <= tol))
+
+
 # ---------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -349,10 +451,16 @@ def main():
                     help="shrink the expert count (profiling captures of a reduced case)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--measure-peaks", action="store_true",
+                    help="measure the library GEMM peaks (bf16, e4m3, int8) on cuda:0 and exit")
     ap.add_argument("--graph", action="store_true",
                     help="1 GPU only: replay the layer from a CUDA graph in the device-resident timing")
     args = ap.parse_args()
 
+    if args.measure_peaks:
+        print(json.dumps(dict(tensor_peaks=measure_tensor_peaks(torch.device("cuda", 0)))),
+              flush=True)
+        return
     cfg = dict(WORKLOADS[args.workload])
     if args.experts:
         cfg["E"] = args.experts
@@ -432,19 +540,32 @@ def main():
             torch.cuda.synchronize()
 
     def timed(fn, steps):
+        """K steps in one region bracketed by barrier + synchronize; an event after every step
+        gives K per-step samples (max over ranks per step).  Returns (median ms per step,
+        statistics): the reference reports the median of its samples and re-measures when the
+        trimmed spread exceeds 3 % (test/fused_moe/test_fused_moe.py:1317-1331 of the reference);
+        here the spread is reported with the number."""
         sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record()
+        for k in range(steps):
             fn()
-        e1.record()
+            evs[k + 1].record()
         sync_all()
-        ms = e0.elapsed_time(e1) / steps
+        per = torch.tensor([evs[k].elapsed_time(evs[k + 1]) for k in range(steps)],
+                           dtype=torch.float64, device=device)
+        total = torch.tensor([evs[0].elapsed_time(evs[steps]) / steps], dtype=torch.float64,
+                             device=device)
         if dist is not None:
-            t = torch.tensor([ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+            dist.all_reduce(per, op=dist.ReduceOp.MAX)
+            dist.all_reduce(total, op=dist.ReduceOp.MAX)
+        vals = sorted(per.tolist())
+        trim = vals[1:-1] if len(vals) >= 5 else vals
+        med = statistics.median(vals)
+        stats = dict(samples=len(vals), median_ms=med, mean_ms=float(total.item()),
+                     min_ms=vals[0], max_ms=vals[-1],
+                     trimmed_spread=(trim[-1] - trim[0]) / med if med > 0 else None)
+        return med, stats
 
     # ---- device-resident timing ------------------------------------------------------------
     for _ in range(warmup):
@@ -463,10 +584,10 @@ def main():
             graph_out = step(hidden, wts, ids)
         for _ in range(3):
             graph.replay()
-        ms = timed(graph.replay, args.steps)
+        ms, timing = timed(graph.replay, args.steps)
         config["cuda_graph"] = True
     else:
-        ms = timed(lambda: step(hidden, wts, ids), args.steps)
+        ms, timing = timed(lambda: step(hidden, wts, ids), args.steps)
         launches = (ops.launch_count() - launches0) // max(args.steps, 1)
 
     # ---- end to end through the public API with host buffers ----------------------------
@@ -480,7 +601,7 @@ def main():
 
     for _ in range(2):
         e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
+    ms_e2e, timing_e2e = timed(e2e_step, args.steps)
 
     # the same traffic double-buffered: step i+1's inputs cross PCIe while step i computes and
     # step i-1's result returns (what a serving loop does); reported next to the strict number
@@ -562,6 +683,12 @@ def main():
         dist.all_reduce(per_rank)
         ep_stats["routes_per_rank"] = dict(max=float(per_rank.max()), mean=float(per_rank.mean()),
                                            max_over_mean=float(per_rank.max() / per_rank.mean()))
+    # ---- correctness of the multi-GPU path: rank 0 rebuilds the experts of four of its tokens
+    # (any rank can build any expert from the seed) and holds its output against the CPU oracle
+    ep_check = None
+    check_out = step(hidden, wts, ids)          # every rank takes part in the exchange
+    if rank == 0:
+        ep_check = spot_check(cfg, check_out, hidden_h, wts_h, ids_h, device, args.seed)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -574,9 +701,9 @@ def main():
     line = dict(metric="moe_layer_tokens_per_s", value=value, unit="tokens/s", n_gpus=world,
                 steps=args.steps, warmup=warmup, ms_per_step=ms, higher_is_better=True,
                 scaling="weak", vs_baseline=None, dtype=dtype, data="synthetic", config=config,
-                tflops=tflops, gpu_launches=launches, clocks=clocks,
+                tflops=tflops, gpu_launches=launches, clocks=clocks, timing=timing,
                 e2e=dict(value=total_tokens / (ms_e2e * 1e-3), unit="tokens/s",
-                         ms_per_step=ms_e2e,
+                         ms_per_step=ms_e2e, timing=timing_e2e,
                          note="value: copies and layer strictly in sequence each step; "
                               "double_buffered: same bytes per step, copies overlapped with compute",
                          double_buffered_value=total_tokens / (ms_e2e_pipe * 1e-3),
@@ -586,6 +713,8 @@ def main():
                          d2h_bytes_per_step=out_host.numel() * 2 * world))
     if ep_stats is not None:
         line["ep_rank0"] = ep_stats
+    if ep_check is not None:
+        line["ep_check" if world > 1 else "output_check"] = ep_check
     if stage_ms is not None:
         line["stage_ms"] = stage_ms
         active = int(torch.unique(ids_h).numel())
@@ -593,7 +722,7 @@ def main():
         g_ms = stage_ms.get("gemm1")
         if g_ms:
             t_hbm = byts / (peaks["hbm_gbs"] * 1e9)
-            tc_peak = peaks["bf16_tflops"] * (1.0 if cfg["kind"] == "bf16" else 2.0)
+            tc_peak, tc_source = tensor_peak(cfg["kind"], peaks)
             t_tc = flops / (tc_peak * 1e12)
             traffic = NCU_TRAFFIC_BYTES.get((args.workload, m))
             if t_hbm >= t_tc:
@@ -608,9 +737,9 @@ def main():
                                 "quantisation epilogue)" if cfg["kind"] == "mxfp8" else
                                 "k_grouped_gemm (gate/up GEMM + SiLU-mul epilogue)"),
                         ms_per_launch=g_ms, algorithmic_bytes=byts, algorithmic_flops=flops,
-                        peak_source=peaks["source"] + (
-                            "" if cfg["kind"] == "bf16" or t_hbm >= t_tc
-                            else " bf16 x2 (no measured 8-bit peak)"))
+                        tensor_time_ms=t_tc * 1e3, hbm_time_ms=t_hbm * 1e3,
+                        peak_source=(peaks["source"] + " (MEASURED_PEAKS.json copy bandwidth)"
+                                     if t_hbm >= t_tc else tc_source))
             line["roofline"] = roof
     if not args.no_cpu_baseline and world == 1:
         v, cores, sample, _ = cpu_reference(cfg, m, args.seed)
@@ -619,6 +748,8 @@ def main():
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+    if ep_check is not None and not ep_check["ok"]:
+        raise SystemExit(f"layer output differs from the oracle: {ep_check}")
 
 
 if __name__ == "__main__":

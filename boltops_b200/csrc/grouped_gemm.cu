@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded; on expiry the kernel records a status
 // word, stops issuing work, drains and frees its TMEM before returning.
 #include <cuda.h>
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -35,6 +36,7 @@ namespace bolt {
 namespace {
 
 constexpr int kThreads = 384;
+constexpr int kMaxDevices = 64;
 // shared-memory operand stages: the block-scaled kinds spend ~950 cycles per K block (three
 // stages cover the load latency, and the space goes to bulk-store slots); the others stream a
 // K block every ~500 cycles and need four
@@ -1334,16 +1336,41 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// One-time set-up of a kernel on the CURRENT device (`done` has one slot per device ordinal):
+// the dynamic shared-memory opt-in is a per-device attribute, and a kernel that re-splits its
+// registers with setmaxnreg must have been compiled to a register count from which the split
+// balances -- `setmaxnreg.inc` only gets registers that `setmaxnreg.dec` released in the same
+// CTA and waits forever otherwise, so an unbalanced split is refused here instead of launched.
+// dec_threads drop to dec_regs, inc_threads rise to inc_regs (0 threads: no split).
+template <typename KernelT>
+int configure_kernel(KernelT kfn, int smem_bytes, std::atomic<bool>* done, int dec_threads,
+                     int dec_regs, int inc_threads, int inc_regs) {
+  int dev = 0;
+  BOLT_CUDA(cudaGetDevice(&dev));
+  BOLT_REQUIRE(dev >= 0 && dev < kMaxDevices, "grouped_gemm: device index %d out of range", dev);
+  if (done[dev].load(std::memory_order_acquire)) return BOLT_OK;
+  cudaFuncAttributes attr;
+  BOLT_CUDA(cudaFuncGetAttributes(&attr, kfn));
+  if (dec_threads > 0 &&
+      (int64_t)dec_threads * (attr.numRegs - dec_regs) < (int64_t)inc_threads * (inc_regs - attr.numRegs)) {
+    set_error("grouped_gemm: kernel was built with %d registers per thread; the register split "
+              "%d x %d -> %d / %d x %d -> %d cannot balance, refusing to launch",
+              attr.numRegs, dec_threads, attr.numRegs, dec_regs, inc_threads, attr.numRegs, inc_regs);
+    return BOLT_ERR_UNSUPPORTED;
+  }
+  BOLT_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  done[dev].store(true, std::memory_order_release);
+  return BOLT_OK;
+}
+
 template <int OPK, bool BS, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
            const GemmParams& p, int grid, cudaStream_t st) {
   auto kfn = k_grouped_gemm<OPK, BS, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    BOLT_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   smem_bytes_of(BS)));
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  // warps 0-3 drop to 56 registers, the eight epilogue warps rise to 224
+  const int rc = configure_kernel(kfn, smem_bytes_of(BS), configured, 128, 56, 256, 224);
+  if (rc != BOLT_OK) return rc;
   kfn<<<grid, kThreads, smem_bytes_of(BS), st>>>(ma, mb, mc, p);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
@@ -1542,14 +1569,10 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   if (grid <= 0) return BOLT_OK;
 
   if (mx) {
-    static bool configured = false;
-    if (!configured) {
-      BOLT_CUDA(cudaFuncSetAttribute(k_mx_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kMxSmemBytes));
-      BOLT_CUDA(cudaFuncSetAttribute(k_mx_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kMxSmemBytes));
-      configured = true;
-    }
+    static std::atomic<bool> configured[2][kMaxDevices];
+    int rc = configure_kernel(k_mx_gemm<false>, kMxSmemBytes, configured[0], 0, 0, 0, 0);
+    if (rc == BOLT_OK) rc = configure_kernel(k_mx_gemm<true>, kMxSmemBytes, configured[1], 0, 0, 0, 0);
+    if (rc != BOLT_OK) return rc;
     if (gated)
       k_mx_gemm<true><<<grid, kThreads, kMxSmemBytes, st>>>(ma, mb, mc, p);
     else

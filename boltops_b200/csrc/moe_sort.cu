@@ -13,6 +13,7 @@
 //                            per-block expert ids, counts/starts, num_valid)
 //                  k_scatter(per-warp histograms in shared memory, warp-ordered
 //                            match_any ranking, stable scatter, pad fill).
+#include <atomic>
 #include "common.cuh"
 
 namespace bolt {
@@ -444,7 +445,9 @@ namespace bolt {
 namespace {
 constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB, held by every GPU that loads the library
 static __device__ __align__(256) unsigned char g_sort_scratch[kStaticScratchBytes];
-void* g_sort_scratch_ptr[64] = {nullptr};  // per-device address of g_sort_scratch
+// per-device address of g_sort_scratch; atomic because two host threads may make their first
+// call on a device at the same time (both would store the same value)
+std::atomic<void*> g_sort_scratch_ptr[64];
 }  // namespace
 }  // namespace bolt
 
@@ -466,18 +469,18 @@ extern "C" int bolt_moe_sort_ck_static(const int32_t* topk_ids, const float* top
   int dev = 0;
   BOLT_CUDA(cudaGetDevice(&dev));
   BOLT_REQUIRE(dev >= 0 && dev < 64, "moe sort (static): device index %d out of range", dev);
-  if (g_sort_scratch_ptr[dev] == nullptr) {
+  void* scratch = g_sort_scratch_ptr[dev].load(std::memory_order_relaxed);
+  if (scratch == nullptr) {
     // one-time set-up for this device: resolve the array's device address
-    void* ptr = nullptr;
-    BOLT_CUDA(cudaGetSymbolAddress(&ptr, g_sort_scratch));
-    g_sort_scratch_ptr[dev] = ptr;
+    BOLT_CUDA(cudaGetSymbolAddress(&scratch, g_sort_scratch));
+    g_sort_scratch_ptr[dev].store(scratch, std::memory_order_relaxed);
   }
   // No entry of the scratch has to start at zero: the count kernel writes every
   // per-CTA histogram entry and the scan kernel every offset before it is read.
   return bolt_moe_sort_ck(topk_ids, topk_weights, local_expert_mask, num_tokens, topk,
                           num_experts, unit_size, sorted_ids, sorted_weights, sorted_expert_ids,
                           tokens_positions_per_expert, num_valid_ids, nullptr, nullptr, 0,
-                          g_sort_scratch_ptr[dev], kStaticScratchBytes, stream);
+                          scratch, kStaticScratchBytes, stream);
 }
 
 extern "C" int bolt_moe_align_block_size(const int32_t* topk_ids, int numel, int num_experts,

@@ -485,7 +485,7 @@ int launch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group,
                          int64_t dst_scale_ld, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(TIn);
   const int tpg = group / VEC;
-  const int pad_blocks = 148 * 4;
+  const int pad_blocks = sm_count_of_current_device() * 4;
   if (tpg > 32 || (tpg & (tpg - 1)) != 0) {
     // a warp per group, groups strided over a capped grid
     const int64_t num_groups = num_tokens * (cols / group);

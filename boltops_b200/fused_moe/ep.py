@@ -109,6 +109,11 @@ class ExpertParallelMoE:
         both[0].copy_(send_counts)
         dist.all_to_all_single(both[1], both[0], group=self.group)
         send_split, recv_split = both.tolist()          # one host synchronisation for both
+        if both.is_cuda:
+            # the host has just synchronised with the device anyway: a good moment to notice a
+            # bounded device-side wait that expired in an earlier layer
+            from . import ops
+            ops.check_device_status(both.device)
         return send_split, recv_split
 
     # -- small batches: replicated tokens, no dispatch ---------------------------------------

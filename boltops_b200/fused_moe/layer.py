@@ -6,10 +6,11 @@ relative to the reference project root): same arguments, defaults, error
 behaviour and numerics contract; the schedule is B200-native:
 
     sort (CK format, 128-row units) -> [quantise hidden once per token]
-    -> gather rows into the expert-sorted layout
+    -> gather (or quantise-and-scatter) rows into the expert-sorted layout
     -> grouped GEMM 1 with SiLU(gate)*up (+ 1x128 re-quantisation) in its epilogue
-    -> grouped GEMM 2 with the router weight in its epilogue, scattered to [M, topk, H]
-    -> top-k combine.
+    -> grouped GEMM 2 with the router weight in its epilogue, rows kept in sorted order
+    -> top-k combine that gathers each token's rows through the sort's inverse permutation
+       ([M, topk, H] exists only for ``no_combine=True``).
 
 No step synchronises the host; the padded row count stays on the device.
 """
@@ -22,7 +23,7 @@ import torch
 
 from .. import _cabi
 from . import ops
-from .activation import activation_quant, apply_activation, normalize_moe_activation
+from .activation import apply_activation, normalize_moe_activation
 
 _FLOAT_OUT = (torch.float16, torch.bfloat16, torch.float32)
 
@@ -188,6 +189,20 @@ def fused_experts_impl(
         raise ValueError("boltops_b200 kernels need CUDA tensors (there is no CPU path)")
 
     quantised = use_fp8_w8a8 or use_int8_w8a8
+    if quantised and hidden_states.dtype == torch.float32:
+        # the reference quantises fp16 / bf16 rows only and hands any other dtype to its 8-bit
+        # kernel as it is (fused_moe.py:1486-1492,1524-1529 of the reference); that combination
+        # has no defined result, so it is refused here instead of quantised silently
+        raise NotImplementedError("w8a8 experts take fp16 / bf16 rows (quantised here) or "
+                                  "pre-quantised int8 / e4m3 rows with a1_scale")
+    # TMA tiles and 128-bit row accesses need 16-byte rows in every operand and result
+    for what, cols, esz in (("hidden size", w1.shape[2], w1.element_size()),
+                            ("intermediate size", w2.shape[2], w2.element_size()),
+                            ("hidden size", w1.shape[2], hidden_states.element_size()),
+                            ("output size", w2.shape[1], torch.empty((), dtype=output_dtype).element_size())):
+        if (cols * esz) % 16:
+            raise NotImplementedError(
+                f"{what} {cols} x {esz} B is not a multiple of 16 bytes: not built in boltops_b200")
     if quantised and not per_channel_quant and block_shape is None:
         raise NotImplementedError("per-tensor quantised experts are not built in boltops_b200")
     if quantised and block_shape is not None and not per_channel_quant:
@@ -256,8 +271,7 @@ def fused_experts_impl(
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
         a_scale = None
-        if (quantised and block_mode
-                and x.dtype in (torch.float16, torch.bfloat16, torch.float32)):
+        if quantised and block_mode and x.dtype in (torch.float16, torch.bfloat16):
             # quantise each token once and write it straight to its sorted rows
             with _Stage("quant_a1"):
                 a_sorted, a_scale = ops.quant_scatter_rows(
@@ -268,7 +282,7 @@ def fused_experts_impl(
             # faster than a token-centric scatter of whole rows; measured 0.131 vs 0.157 ms at
             # 16384 x 2048)
             with _Stage("quant_a1"):
-                if x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+                if x.dtype in (torch.float16, torch.bfloat16):
                     if block_mode:
                         x_q, x_s = ops.per_block_quant(x, 128, q_dtype, scale_ue8m0=use_ue8m0)
                     else:

@@ -67,7 +67,8 @@ enum bolt_gemm_kind {
   BOLT_GEMM_MXFP8 = 6         /* e4m3 with one E8M0 byte per 32 K elements on both operands,
                                  applied by the tensor core; a_scale / b_scale carry BYTE
                                  arrays in the tiled layout of bolt_mx_sf_layout; plain
-                                 epilogue only, k a multiple of 128                        */
+                                 epilogue or the gated activation + MX re-quantisation
+                                 (BOLT_EPI_SILU_MUL_QUANT); k a multiple of 128            */
 };
 
 enum bolt_gemm_epilogue {

@@ -74,6 +74,29 @@ def make_mxfp8(ref: Path) -> None:
     np.savez_compressed(HERE / "mxfp8.npz", **mx)
 
 
+def make_signatures(ref: Path) -> None:
+    """Parameter lists of the public functions (name, kind, default as source text), read from
+    the reference's package file with ``ast`` -- the drop-in signature contract."""
+    import json
+    tree = ast.parse((ref / "boltops/fused_moe/__init__.py").read_text(encoding="utf-8"))
+    out = {}
+    for node in tree.body:
+        if not isinstance(node, ast.FunctionDef) or node.name.startswith("_"):
+            continue
+        a = node.args
+        params = []
+        pos = a.posonlyargs + a.args
+        defaults = [None] * (len(pos) - len(a.defaults)) + list(a.defaults)
+        for arg, d in zip(pos, defaults):
+            params.append([arg.arg, "positional", None if d is None else ast.unparse(d)])
+        for arg, d in zip(a.kwonlyargs, a.kw_defaults):
+            params.append([arg.arg, "keyword_only", None if d is None else ast.unparse(d)])
+        out[node.name] = params
+    lines = [f' "{name}": [\n' + ",\n".join("  " + json.dumps(q) for q in params) + "\n ]"
+             for name, params in out.items()]
+    (HERE / "signatures.json").write_text("{\n" + ",\n".join(lines) + "\n}\n")
+
+
 def main(ref_root: str) -> None:
     ref = Path(ref_root)
     tdir = ref / "test" / "fused_moe"
@@ -246,6 +269,7 @@ def main(ref_root: str) -> None:
     np.savez_compressed(HERE / "activations.npz", **acts)
 
     make_mxfp8(ref)
+    make_signatures(ref)
     print("golden fixtures written to", HERE)
 
 
@@ -254,7 +278,9 @@ if __name__ == "__main__":
         raise SystemExit("usage: make_golden.py <path of the reference project checkout> "
                          "(or set BOLTOPS_REFERENCE)")
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ["BOLTOPS_REFERENCE"]
-    if len(sys.argv) > 2 and sys.argv[2] == "mxfp8":      # only the newest fixture
+    if len(sys.argv) > 2 and sys.argv[2] == "mxfp8":      # only one fixture
         make_mxfp8(Path(root))
+    elif len(sys.argv) > 2 and sys.argv[2] == "signatures":
+        make_signatures(Path(root))
     else:
         main(root)

@@ -1,4 +1,6 @@
-"""Benchmark-sized cases (DeepSeek-V3 fp8 block, Qwen3-30B int8 per-channel shapes).
+"""Benchmark-sized cases: every configuration of the benchmark at its own shape
+(Mixtral-8x7B bf16, DeepSeek-V3 fp8 block, Qwen3-30B int8 per-channel, Qwen3-235B fp8 block
+with Zipf routing), including the end points of the token sweeps.
 
 Full CPU oracles of these layers take minutes, so parity is checked through
 size-independent properties plus an oracle spot check on a few tokens:
@@ -105,3 +107,79 @@ def test_qwen3_int8_channel_full_shape_spot_oracle():
     expect = O.moe_per_channel(hidden[toks], w1.cpu(), w2.cpu(), w1s.cpu(), w2s.cpu(), wts[toks],
                                ids[toks], torch.int8)
     assert O.rel_l2(out[toks].cpu(), expect) <= 2e-2
+
+
+def _spot_block_fp8(out, toks, hidden, wts, ids, w1, w2, w1s, w2s):
+    """Oracle on the listed tokens: only the experts they use are copied to the host."""
+    used = sorted(set(ids[toks].reshape(-1).tolist()))
+    remap = {e: j for j, e in enumerate(used)}
+    sel = torch.tensor(used, device=w1.device)
+    loc_ids = torch.tensor([[remap[int(e)] for e in row] for row in ids[toks]], dtype=torch.int32)
+    expect = O.moe_block_fp8(hidden[toks], w1[sel].cpu(), w2[sel].cpu(), w1s[sel].cpu(),
+                             w2s[sel].cpu(), wts[toks], loc_ids, (128, 128))
+    return O.rel_l2(out[toks].cpu(), expect)
+
+
+@pytest.mark.parametrize("m,toks", [(1, [0]), (8192, [0, 4097, 8191])])
+def test_dsv3_sweep_end_points_spot_oracle(dsv3, m, toks):
+    """The DeepSeek-V3 layer at both ends of its token sweep (one token: eight experts, one
+    live row each; 8192 tokens: two and three row tiles per expert)."""
+    from boltops_b200.fused_moe import fused_experts
+    cfg, (w1, w2, w1s, w2s), _ = dsv3
+    hidden, wts, ids = B.make_tokens(cfg, m, 5 + m)
+    out = fused_experts(hidden.cuda(), w1, w2, wts.cuda(), ids.cuda(), use_fp8_w8a8=True,
+                        w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+    _finish(w1.device)
+    assert torch.isfinite(out.float()).all()
+    assert _spot_block_fp8(out, toks, hidden, wts, ids, w1, w2, w1s, w2s) <= 2e-2
+
+
+@pytest.fixture(scope="module")
+def mixtral():
+    cfg = dict(B.WORKLOADS["mixtral_8x7b_bf16"])
+    w1, w2, _, _ = B.make_weights(cfg, torch.device("cuda"), list(range(cfg["E"])), 2)
+    return cfg, w1, w2
+
+
+@pytest.mark.parametrize("m,toks", [(1, [0]), (8192, [3, 8191])])
+def test_mixtral_bf16_full_shape_spot_oracle(mixtral, m, toks):
+    """Mixtral-8x7B shape (16 row tiles per expert at 8192 tokens, 224 K blocks in the down
+    GEMM) against the bf16 oracle on a few tokens."""
+    from boltops_b200.fused_moe import fused_experts
+    cfg, w1, w2 = mixtral
+    hidden, wts, ids = B.make_tokens(cfg, m, 11 + m)
+    out = fused_experts(hidden.cuda(), w1, w2, wts.cuda(), ids.cuda())
+    _finish(w1.device)
+    assert torch.isfinite(out.float()).all()
+    used = sorted(set(ids[toks].reshape(-1).tolist()))
+    remap = {e: j for j, e in enumerate(used)}
+    sel = torch.tensor(used, device=w1.device)
+    loc_ids = torch.tensor([[remap[int(e)] for e in row] for row in ids[toks]], dtype=torch.int32)
+    expect = O.moe_bf16(hidden[toks], w1[sel].cpu(), w2[sel].cpu(), wts[toks], loc_ids)
+    assert O.rel_l2(out[toks].cpu(), expect) <= 1e-2
+
+
+@pytest.fixture(scope="module")
+def qwen235():
+    cfg = dict(B.WORKLOADS["qwen3_235b_fp8_block_zipf"])
+    w = B.make_weights(cfg, torch.device("cuda"), list(range(cfg["E"])), 3)
+    return cfg, w
+
+
+@pytest.mark.parametrize("m", [1, 16, 256])
+def test_qwen3_235b_zipf_full_shape_spot_oracle(qwen235, m):
+    """Decode-skew case: Zipf(1.2) routing puts many rows on a few experts and none on others."""
+    from boltops_b200.fused_moe import fused_experts
+    cfg, (w1, w2, w1s, w2s) = qwen235
+    hidden, wts, ids = B.make_tokens(cfg, m, 23 + m)
+    counts = torch.bincount(ids.flatten().long(), minlength=cfg["E"])
+    if m == 256:
+        assert counts.max() >= 4 * counts.float().mean() and (counts == 0).any()   # skewed
+    out = fused_experts(hidden.cuda(), w1, w2, wts.cuda(), ids.cuda(), use_fp8_w8a8=True,
+                        w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+    out2 = fused_experts(hidden.cuda(), w1, w2, wts.cuda(), ids.cuda(), use_fp8_w8a8=True,
+                         w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+    _finish(w1.device)
+    assert torch.equal(out, out2) and torch.isfinite(out.float()).all()
+    toks = list(range(m)) if m <= 16 else [0, 100, 255, int(ids[:, 0].argmax())]
+    assert _spot_block_fp8(out, toks, hidden, wts, ids, w1, w2, w1s, w2s) <= 2e-2

@@ -78,15 +78,24 @@ def test_activation_registry():
 
 
 def test_public_signatures_match_reference_order():
+    """Every public function has the reference's parameters: same names, order, kind and
+    defaults (tests/golden/signatures.json is written by make_golden.py from the reference's
+    boltops/fused_moe/__init__.py)."""
     import inspect
-    from boltops_b200.fused_moe import fused_experts, moe_activation
-    names = list(inspect.signature(fused_experts).parameters)
-    assert names[:10] == ["hidden_states", "w1", "w2", "topk_weights", "topk_ids", "inplace",
-                          "activation", "b1", "b2", "is_gated"]
-    assert names[-1] == "gemm1_beta" and len(names) == 37
-    sig = inspect.signature(moe_activation)
-    assert list(sig.parameters)[:4] == ["activated_out", "ffn1_out_2d", "activation", "is_gated"]
-    assert sig.parameters["gemm1_alpha"].kind is inspect.Parameter.KEYWORD_ONLY
+    import json
+    import boltops_b200.fused_moe as pkg
+    ref = json.loads((ROOT / "tests" / "golden" / "signatures.json").read_text())
+    assert set(ref) == {"fused_experts", "moe_activation", "normalize_moe_activation",
+                        "moe_activation_output_size"}
+    assert len(ref["fused_experts"]) == 37
+    for fn_name, params in ref.items():
+        sig = inspect.signature(getattr(pkg, fn_name))
+        got = []
+        for name, prm in sig.parameters.items():
+            kind = "keyword_only" if prm.kind is inspect.Parameter.KEYWORD_ONLY else "positional"
+            default = None if prm.default is inspect.Parameter.empty else repr(prm.default)
+            got.append([name, kind, default])
+        assert got == params, f"{fn_name}: {got} != {params}"
 
 
 def test_no_cpu_fallback():
