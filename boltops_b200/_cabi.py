@@ -25,6 +25,9 @@ GEMM_BF16, GEMM_F16, GEMM_FP8_BLOCK, GEMM_INT8_CHANNEL, GEMM_FP8_CHANNEL, GEMM_I
     GEMM_MXFP8 = range(7)
 # enum bolt_gemm_epilogue
 EPI_STORE, EPI_SILU_MUL, EPI_SILU_MUL_QUANT = range(3)
+# enum bolt_gemm_schedule, BOLT_PAIR_SEGMENT_ROWS
+SCHEDULE_ROW_TILES, SCHEDULE_TILE_PAIRS = range(2)
+PAIR_SEGMENT_ROWS = 256
 
 _DTYPES = {
     torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32,
@@ -55,6 +58,8 @@ class GemmArgs(C.Structure):
         ("status", C.c_void_p), ("sm_count", C.c_int),
         ("act_alpha", C.c_float), ("act_beta", C.c_float), ("act_limit", C.c_float),
         ("act_has_limit", C.c_int),
+        ("schedule", C.c_int), ("max_segments", C.c_int),
+        ("segments", C.c_void_p), ("num_segments", C.c_void_p),
     ]
 
 
@@ -64,8 +69,8 @@ _SIGNATURES = {
     "bolt_moe_sort_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "bolt_moe_sort_ck": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                    C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
-                                   C.c_size_t, C.c_void_p]),
+                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                   C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
     "bolt_moe_sort_static_scratch_bytes": (C.c_size_t, []),
     "bolt_moe_sort_ck_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                           C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -81,7 +86,7 @@ _SIGNATURES = {
     "bolt_ep_dest_ranks": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
                                      C.c_void_p, C.c_void_p]),
     "bolt_quant_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
-                                  C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+                                  C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "bolt_quant_scatter_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                           C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
@@ -129,7 +134,7 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.bolt_abi_version() != 2:
+    if lib.bolt_abi_version() != 3:
         raise RuntimeError("libboltops_b200.so ABI version mismatch")
     _lib = lib
     return lib

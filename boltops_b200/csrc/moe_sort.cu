@@ -35,6 +35,10 @@ struct SortParams {
   int32_t* positions;        // [2E] (CK) or nullptr
   int32_t* num_valid;        // [1]
   int32_t* route_pos;        // [R] sorted position of every route (optional, pre-filled with -1)
+  int32_t* segments;         // optional [*][4]: {expert label, first row, rows, 0} per run of at
+                             // most segment_rows live rows of one expert, in sorted order
+  int32_t* num_segments;     // [1]
+  int segment_rows;
   int32_t* cta_counts;       // scratch [G][E]: counts, then exclusive offsets
   int32_t* expert_start;     // scratch [E+1]: padded start per expert, -1 if none
   int R, E, topk, tokens, unit;
@@ -102,7 +106,7 @@ __device__ void block_exclusive_scan(int* data, int n, int* scratch, int* total_
 // On return start_s[e] = padded start (or -1 if expert e has no segment),
 // start_s[E] = padded total.  tmp: E ints, scratch: 33 ints.
 __device__ void build_metadata(const SortParams& p, const int* tot, int* start_s, int* tmp,
-                               int* scratch) {
+                               int* scratch, int* seg_s) {
   const int E = p.E;
   // padded sizes
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -135,6 +139,32 @@ __device__ void build_metadata(const SortParams& p, const int* tot, int* start_s
       p.positions[e] = tot[e];
       p.positions[E + e] = on ? s : -1;
     }
+  }
+  if (p.segments != nullptr) {
+    // runs of at most segment_rows live rows per expert, numbered in expert order
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      bool on = p.mask == nullptr || p.mask[e] != 0;
+      seg_s[e] = on ? (tot[e] + p.segment_rows - 1) / p.segment_rows : 0;
+    }
+    __syncthreads();
+    __shared__ int seg_total_s;
+    block_exclusive_scan(seg_s, E, scratch, &seg_total_s);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      bool on = p.mask == nullptr || p.mask[e] != 0;
+      if (!on) continue;
+      const int c = tot[e];
+      const int label = (p.mask != nullptr) ? tmp[e] : e;
+      int* dst = p.segments + 4 * seg_s[e];
+      for (int r = 0; r < c; r += p.segment_rows, dst += 4) {
+        dst[0] = label;
+        dst[1] = start_s[e] + r;
+        dst[2] = min(p.segment_rows, c - r);
+        dst[3] = 0;
+      }
+    }
+    if (threadIdx.x == 0) p.num_segments[0] = seg_total_s;
   }
   if (p.vllm) {
     // blocks beyond the padded total hold expert 0 (mapped) as in the zero-filled buffer
@@ -228,9 +258,10 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_small(SortParams p) {
   int* start_s = tot + p.E;        // [E+1]
   int* tmp = start_s + p.E + 1;    // [E]
   int* scratch = tmp + p.E;        // [33]
-  int* warp_cnt = scratch + 33;    // [kSortWarps][E]
+  int* seg_s = scratch + 33;       // [E]
+  int* warp_cnt = seg_s + p.E;     // [kSortWarps][E]
   cta_histogram(p, 0, tot);
-  build_metadata(p, tot, start_s, tmp, scratch);
+  build_metadata(p, tot, start_s, tmp, scratch, seg_s);
   cta_scatter(p, 0, warp_cnt, start_s);
   pad_fill(p, start_s, tot, 0, 1);
   if (p.vllm) {
@@ -290,7 +321,7 @@ __global__ void __launch_bounds__(1024) k_sort_scan(SortParams p, int G) {
     }
   }
   __syncthreads();
-  build_metadata(p, tot, start_s, tmp, scratch);
+  build_metadata(p, tot, start_s, tmp, scratch, scratch + 33);
   for (int e = threadIdx.x; e <= p.E; e += blockDim.x) p.expert_start[e] = start_s[e];
   // expert totals are needed again by the scatter kernel for the pad fill
   for (int e = threadIdx.x; e < p.E; e += blockDim.x) p.expert_start[p.E + 1 + e] = tot[e];
@@ -352,7 +383,7 @@ int run_sort(SortParams p, void* workspace, size_t workspace_bytes, cudaStream_t
   p.chunk = pl.chunk;
   const size_t need = workspace_bytes_for(p.R, p.E);
   if (pl.G == 1) {
-    size_t smem = (size_t)(3 * p.E + 1 + 33 + kSortWarps * p.E) * sizeof(int);
+    size_t smem = (size_t)(4 * p.E + 1 + 33 + kSortWarps * p.E) * sizeof(int);
     BOLT_REQUIRE(smem <= 200 * 1024, "moe sort: num_experts %d too large", p.E);
     if (smem > 48 * 1024)
       BOLT_CUDA(cudaFuncSetAttribute(k_sort_small, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -368,7 +399,7 @@ int run_sort(SortParams p, void* workspace, size_t workspace_bytes, cudaStream_t
   p.cta_counts = static_cast<int32_t*>(workspace);
   p.expert_start = p.cta_counts + (size_t)pl.G * p.E;
   size_t smem1 = (size_t)p.E * sizeof(int);
-  size_t smem2 = (size_t)(3 * p.E + 1 + 33) * sizeof(int);
+  size_t smem2 = (size_t)(4 * p.E + 1 + 33) * sizeof(int);
   size_t smem3 = (size_t)(3 * p.E + 1 + kSortWarps * p.E) * sizeof(int);
   BOLT_REQUIRE(smem3 <= 200 * 1024, "moe sort: num_experts %d too large", p.E);
   if (smem3 > 48 * 1024)
@@ -396,7 +427,8 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
                                 int num_experts, int unit_size, int32_t* sorted_ids,
                                 float* sorted_weights, int32_t* sorted_expert_ids,
                                 int32_t* tokens_positions_per_expert, int32_t* num_valid_ids,
-                                int32_t* route_pos, void* moe_buf, size_t moe_buf_bytes,
+                                int32_t* route_pos, int32_t* segments, int32_t* num_segments,
+                                int segment_rows, void* moe_buf, size_t moe_buf_bytes,
                                 void* workspace, size_t workspace_bytes, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -418,6 +450,11 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
   p.positions = tokens_positions_per_expert;
   p.num_valid = num_valid_ids;
   p.route_pos = route_pos;
+  BOLT_REQUIRE(segments == nullptr || (num_segments != nullptr && segment_rows > 0),
+               "moe sort: segments need num_segments and a positive segment_rows");
+  p.segments = segments;
+  p.num_segments = num_segments;
+  p.segment_rows = segment_rows;
   p.R = num_tokens * topk;
   p.E = num_experts;
   p.topk = topk;
@@ -479,8 +516,8 @@ extern "C" int bolt_moe_sort_ck_static(const int32_t* topk_ids, const float* top
   // per-CTA histogram entry and the scan kernel every offset before it is read.
   return bolt_moe_sort_ck(topk_ids, topk_weights, local_expert_mask, num_tokens, topk,
                           num_experts, unit_size, sorted_ids, sorted_weights, sorted_expert_ids,
-                          tokens_positions_per_expert, num_valid_ids, nullptr, nullptr, 0,
-                          scratch, kStaticScratchBytes, stream);
+                          tokens_positions_per_expert, num_valid_ids, nullptr, nullptr, nullptr, 0,
+                          nullptr, 0, scratch, kStaticScratchBytes, stream);
 }
 
 extern "C" int bolt_moe_align_block_size(const int32_t* topk_ids, int numel, int num_experts,

@@ -44,10 +44,22 @@ __device__ __forceinline__ typename QTraits<QT>::type quant_one(float x, float i
 
 // ---- small groups: TPG threads (a power of two <= 32) share one group ----------
 // A thread owns W input vectors = EPT consecutive elements (EPT = 16: 16-byte stores).
+// Where the scale of group `grp` (= row * groups_per_row + g) goes: row-major [rows, groups]
+// (ld == 0) or group-major [groups, ld] (the layout the grouped GEMM reads per K block).
+struct ScaleOut {
+  float* p;
+  int groups_per_row;
+  int64_t ld;
+  __device__ __forceinline__ void put(int64_t grp, float v) const {
+    if (ld == 0) p[grp] = v;
+    else p[(grp % groups_per_row) * ld + grp / groups_per_row] = v;
+  }
+};
+
 template <typename TIn, int QT, bool POW2, int W>
 __global__ void __launch_bounds__(256) k_quant_group(const TIn* __restrict__ x,
                                                      typename QTraits<QT>::type* __restrict__ q,
-                                                     float* __restrict__ scales,
+                                                     const ScaleOut scales,
                                                      int64_t num_groups, int tpg) {
   constexpr int VEC = 16 / sizeof(TIn);
   constexpr int EPT = VEC * W;
@@ -76,14 +88,14 @@ __global__ void __launch_bounds__(256) k_quant_group(const TIn* __restrict__ x,
 #pragma unroll
     for (int i = 0; i < VEC; ++i) o.v[w * VEC + i] = quant_one<QT, POW2>(to_f32(v[w].v[i]), inv);
   reinterpret_cast<VOut*>(q)[tid] = o;
-  if ((tid % tpg) == 0) scales[grp] = scale;
+  if ((tid % tpg) == 0) scales.put(grp, scale);
 }
 
 // ---- one CTA per group (large or oddly sized groups) ---------------------------
 template <typename TIn, int QT, bool POW2>
 __global__ void __launch_bounds__(256) k_quant_row(const TIn* __restrict__ x,
                                                    typename QTraits<QT>::type* __restrict__ q,
-                                                   float* __restrict__ scales, int group) {
+                                                   const ScaleOut scales, int group) {
   const int64_t g = blockIdx.x;
   const TIn* xr = x + g * (int64_t)group;
   typename QTraits<QT>::type* qr = q + g * (int64_t)group;
@@ -100,14 +112,14 @@ __global__ void __launch_bounds__(256) k_quant_row(const TIn* __restrict__ x,
   scale_from_amax<QT, POW2>(amax, scale, inv);
   for (int i = threadIdx.x; i < group; i += blockDim.x)
     qr[i] = quant_one<QT, POW2>(to_f32(xr[i]), inv);
-  if (threadIdx.x == 0) scales[g] = scale;
+  if (threadIdx.x == 0) scales.put(g, scale);
 }
 
 // vectorised variant of the above: group % VEC == 0 and 16-byte aligned rows.
 template <typename TIn, int QT, bool POW2, int NV>
 __global__ void __launch_bounds__(256) k_quant_row_vec(const TIn* __restrict__ x,
                                                        typename QTraits<QT>::type* __restrict__ q,
-                                                       float* __restrict__ scales, int group) {
+                                                       const ScaleOut scales, int group) {
   constexpr int VEC = 16 / sizeof(TIn);
   using VIn = Vec<TIn, VEC>;
   using VOut = Vec<typename QTraits<QT>::type, VEC>;
@@ -157,7 +169,7 @@ __global__ void __launch_bounds__(256) k_quant_row_vec(const TIn* __restrict__ x
     for (int e = 0; e < VEC; ++e) o.v[e] = quant_one<QT, POW2>(to_f32(v.v[e]), inv);
     qr[i] = o;
   }
-  if (threadIdx.x == 0) scales[g] = scale;
+  if (threadIdx.x == 0) scales.put(g, scale);
 }
 
 // ---- one warp per group (mid-sized rows: the row lives in the warp's registers) -----
@@ -166,7 +178,7 @@ __global__ void __launch_bounds__(256) k_quant_row_vec(const TIn* __restrict__ x
 template <typename TIn, int QT, bool POW2, int NV, int W>
 __global__ void __launch_bounds__(256) k_quant_row_warp(const TIn* __restrict__ x,
                                                         typename QTraits<QT>::type* __restrict__ q,
-                                                        float* __restrict__ scales,
+                                                        const ScaleOut scales,
                                                         int64_t num_groups, int group) {
   constexpr int VEC = 16 / sizeof(TIn);
   constexpr int EPT = VEC * W;
@@ -209,12 +221,12 @@ __global__ void __launch_bounds__(256) k_quant_row_warp(const TIn* __restrict__ 
         qr[i] = o;
       }
     }
-    if (lane == 0) scales[g] = scale;
+    if (lane == 0) scales.put(g, scale);
   }
 }
 
 template <typename TIn, int QT, bool POW2>
-int launch_quant(const void* x, int64_t rows, int cols, int group, void* q, float* scales,
+int launch_quant(const void* x, int64_t rows, int cols, int group, void* q, ScaleOut scales,
                  cudaStream_t st) {
   using QTy = typename QTraits<QT>::type;
   constexpr int VEC = 16 / sizeof(TIn);
@@ -259,7 +271,7 @@ int launch_quant(const void* x, int64_t rows, int cols, int group, void* q, floa
 
 template <typename TIn>
 int dispatch_quant(const void* x, int64_t rows, int cols, int group, int q_dtype, int power2,
-                   void* q, float* scales, cudaStream_t st) {
+                   void* q, ScaleOut scales, cudaStream_t st) {
   if (q_dtype == BOLT_FP8_E4M3) {
     return power2 ? launch_quant<TIn, BOLT_FP8_E4M3, true>(x, rows, cols, group, q, scales, st)
                   : launch_quant<TIn, BOLT_FP8_E4M3, false>(x, rows, cols, group, q, scales, st);
@@ -664,15 +676,19 @@ __global__ void __launch_bounds__(256) k_mx_sf_layout(const uint8_t* __restrict_
 }  // namespace bolt
 
 extern "C" int bolt_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int group,
-                               int q_dtype, int power2, void* q, float* scales, void* stream) {
+                               int q_dtype, int power2, void* q, float* scales_ptr,
+                               int64_t scales_ld, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(scales_ld == 0 || scales_ld >= rows, "quant: scales_ld %lld below the row count",
+               (long long)scales_ld);
+  const ScaleOut scales{scales_ptr, group > 0 ? cols / group : 1, scales_ld};
   BOLT_REQUIRE(rows >= 0 && cols > 0, "quant: bad shape");
   BOLT_REQUIRE(group > 0 && cols % group == 0, "quant: group %d does not divide cols %d", group,
                cols);
   BOLT_REQUIRE(q_dtype == BOLT_FP8_E4M3 || q_dtype == BOLT_INT8, "quant: bad q_dtype %d", q_dtype);
   BOLT_REQUIRE(!power2 || q_dtype == BOLT_FP8_E4M3, "quant: power-of-two scales need e4m3");
-  BOLT_REQUIRE(rows == 0 || (x && q && scales), "quant: null pointer");
+  BOLT_REQUIRE(rows == 0 || (x && q && scales_ptr), "quant: null pointer");
   switch (x_dtype) {
     case BOLT_BF16:
       return dispatch_quant<__nv_bfloat16>(x, rows, cols, group, q_dtype, power2, q, scales, st);

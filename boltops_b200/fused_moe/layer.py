@@ -79,6 +79,30 @@ def _chunk_size() -> int:
     return size
 
 
+def _use_tile_pairs(kind: int, routes: int, experts: int) -> bool:
+    """Schedule of the two grouped GEMMs.  From about three 128-row tiles per expert on, two
+    CTAs of a cluster take two row tiles of one expert and share its weight tile (tcgen05
+    ``cta_group::2``): each CTA then stages half of the weight tile, which lifts the
+    shared-memory bandwidth limit a single CTA meets at full tensor-core rate.  With fewer rows
+    per expert many pairs would hold one live tile, so single tiles stay.  The host knows only
+    the average (tokens * topk / experts).  ``BOLTOPS_B200_GEMM_SCHEDULE`` = ``tiles`` /
+    ``pairs`` overrides the choice."""
+    forced = os.environ.get("BOLTOPS_B200_GEMM_SCHEDULE", "auto")
+    if forced == "tiles":
+        return False
+    if forced == "pairs":
+        return True
+    return routes >= _PAIR_MIN_AVG_ROWS * max(experts, 1)
+
+
+_PAIR_MIN_AVG_ROWS = 384
+
+
+def gemm_schedule(kind: int, routes: int, experts: int) -> str:
+    """Name of the schedule ``fused_experts`` picks for this problem ("pairs" / "tiles")."""
+    return "pairs" if _use_tile_pairs(kind, routes, experts) else "tiles"
+
+
 def _gemm_kind(w_dtype, use_fp8, use_int8, per_channel, block_shape) -> int:
     if use_fp8:
         return _cabi.GEMM_FP8_CHANNEL if per_channel else _cabi.GEMM_FP8_BLOCK
@@ -263,10 +287,16 @@ def fused_experts_impl(
         # inverse permutation of the sort: the combine gathers through it, and the block
         # quantiser scatters through it
         route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
+        pairs = _use_tile_pairs(kind, m * topk, global_num_experts)
+        segments = num_segments = None
         with _Stage("sort"):
-            sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
+            res = ops.moe_sorting_ck(
                 ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
-                alloc_moe_buf=False, route_pos=route_pos)
+                alloc_moe_buf=False, route_pos=route_pos,
+                segment_rows=_cabi.PAIR_SEGMENT_ROWS if pairs else 0)
+            sorted_ids, sorted_w, expert_ids, num_valid = res[:4]
+            if pairs:
+                segments, num_segments = res[6:8]
         cap = sorted_ids.shape[0]
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
@@ -299,7 +329,8 @@ def fused_experts_impl(
                 a_sorted, _ = ops.gather_rows(x, sorted_ids, num_valid, cap)
 
         common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
-                      sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
+                      sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk,
+                      segments=segments, num_segments=num_segments)
 
         # ---- GEMM1 (+ activation, + re-quantisation) ---------------------------------------
         act_scale = None
@@ -333,8 +364,8 @@ def fused_experts_impl(
             if quantised:
                 with _Stage("quant_a2"):
                     if block_mode:
-                        act, s = ops.per_block_quant(act_f, 128, q_dtype, scale_ue8m0=use_ue8m0)
-                        act_scale = s.t().contiguous()          # [act_dim/128, cap]
+                        act, act_scale = ops.per_block_quant(       # scales [act_dim/128, cap]
+                            act_f, 128, q_dtype, scale_ue8m0=use_ue8m0, group_major=True)
                     else:
                         act, s = ops.per_token_quant(act_f, quant_dtype=q_dtype)
                         act_scale = s.reshape(-1)

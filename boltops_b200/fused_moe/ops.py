@@ -49,14 +49,18 @@ def ceil_to(x: int, m: int) -> int:
 def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
                    model_dim: Optional[int] = None, moebuf_dtype: Optional[torch.dtype] = None,
                    block_size: int = 32, expert_mask: Optional[torch.Tensor] = None,
-                   alloc_moe_buf: bool = True, route_pos: Optional[torch.Tensor] = None):
+                   alloc_moe_buf: bool = True, route_pos: Optional[torch.Tensor] = None,
+                   segment_rows: int = 0):
     """CK-format sort.  Returns ``(sorted_ids, sorted_weights, sorted_expert_ids,
     num_valid_ids, tokens_positions_per_expert, moe_buf)`` like the reference.
 
     ``sorted_ids``/``sorted_weights`` are allocated with the capacity rounded up to
     a multiple of ``block_size`` so that the last row tile is always addressable.
     ``route_pos`` (optional int32 ``[tokens, topk]``) receives every route's position in
-    the sorted order (-1 for routes to masked experts).
+    the sorted order (-1 for routes to masked experts).  With ``segment_rows > 0`` the tuple
+    gains ``(segments [S, 4] int32, num_segments [1] int32)``: every expert's live rows cut
+    into runs of at most ``segment_rows`` rows (``{expert, first row, rows, 0}``), the work
+    list of the tile-pair GEMM schedule (``segment_rows`` = two row tiles).
     """
     _require_cuda(topk_ids, topk_weights, expert_mask)
     if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape:
@@ -85,14 +89,22 @@ def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_exper
         moe_buf = torch.empty((m, model_dim), dtype=moebuf_dtype, device=dev)
     ws_bytes = lib.bolt_moe_sort_workspace_bytes(m, topk, num_experts)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    segments = num_segments = None
+    if segment_rows > 0:
+        max_segments = min(num_experts, m * topk) + (m * topk) // segment_rows
+        segments = torch.empty((max(max_segments, 1), 4), dtype=torch.int32, device=dev)
+        num_segments = torch.empty(1, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         check(lib.bolt_moe_sort_ck(
             ptr(topk_ids), ptr(topk_weights), ptr(expert_mask), m, topk, num_experts, block_size,
             ptr(sorted_ids), ptr(sorted_weights), ptr(sorted_expert_ids), ptr(positions),
-            ptr(num_valid), ptr(route_pos), ptr(moe_buf),
-            0 if moe_buf is None else moe_buf.numel() * moe_buf.element_size(),
+            ptr(num_valid), ptr(route_pos), ptr(segments), ptr(num_segments), segment_rows,
+            ptr(moe_buf), 0 if moe_buf is None else moe_buf.numel() * moe_buf.element_size(),
             ptr(ws), ws_bytes, stream_of(topk_ids)))
     _count((1 if ws_bytes <= 16 else 3) + (1 if route_pos is not None else 0))
+    if segment_rows > 0:
+        return (sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf,
+                segments, num_segments)
     return sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf
 
 
@@ -126,9 +138,11 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
 # quantisation
 # ---------------------------------------------------------------------------
 def quant_rows(x: torch.Tensor, quant_dtype: torch.dtype, group: Optional[int] = None,
-               scale_ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+               scale_ue8m0: bool = False, group_major: bool = False
+               ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dynamic quantisation of a 2-D tensor per row (``group=None``) or per
-    ``1 x group`` block.  Returns ``(q, scales[rows, cols/group])``."""
+    ``1 x group`` block.  Returns ``(q, scales[rows, cols/group])``, or with ``group_major``
+    ``(q, scales[cols/group, rows])`` -- the layout the grouped GEMM reads per K block."""
     _require_cuda(x)
     if x.dim() != 2:
         raise ValueError("quant_rows expects a 2-D tensor")
@@ -137,11 +151,12 @@ def quant_rows(x: torch.Tensor, quant_dtype: torch.dtype, group: Optional[int] =
     rows, cols = x.shape
     g = cols if group is None else group
     q = torch.empty((rows, cols), dtype=quant_dtype, device=x.device)
-    scales = torch.empty((rows, cols // g), dtype=torch.float32, device=x.device)
+    shape = (cols // g, rows) if group_major else (rows, cols // g)
+    scales = torch.empty(shape, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         check(lib.bolt_quant_rows(ptr(x), dtype_code(x.dtype), rows, cols, g,
                                   dtype_code(quant_dtype), int(scale_ue8m0), ptr(q), ptr(scales),
-                                  stream_of(x)))
+                                  rows if group_major else 0, stream_of(x)))
     _count()
     return q, scales
 
@@ -157,10 +172,11 @@ def per_token_quant(x: torch.Tensor, scale: Optional[torch.Tensor] = None,
 
 
 def per_block_quant(x: torch.Tensor, block_n: int = 128, quant_dtype: torch.dtype = torch.int8,
-                    scale_ue8m0: bool = False):
-    """1 x ``block_n`` group quantisation of a 2-D tensor: ``(q[m,n], s[m,n/block_n])``."""
+                    scale_ue8m0: bool = False, group_major: bool = False):
+    """1 x ``block_n`` group quantisation of a 2-D tensor: ``(q[m,n], s[m,n/block_n])``
+    (``s[n/block_n, m]`` with ``group_major``)."""
     assert x.shape[-1] % block_n == 0, f"block size {block_n} not match {x.shape[-1]}"
-    return quant_rows(x, quant_dtype, block_n, scale_ue8m0)
+    return quant_rows(x, quant_dtype, block_n, scale_ue8m0, group_major)
 
 
 # ---------------------------------------------------------------------------
@@ -364,8 +380,10 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
                  sorted_ids: Optional[torch.Tensor] = None,
                  sorted_weights: Optional[torch.Tensor] = None, sm_count: int = 0,
                  act_alpha: float = 1.0, act_beta: float = 0.0,
-                 act_limit: Optional[float] = None) -> None:
-    """One grouped expert GEMM launch (see ``bolt_grouped_gemm``)."""
+                 act_limit: Optional[float] = None, segments: Optional[torch.Tensor] = None,
+                 num_segments: Optional[torch.Tensor] = None) -> None:
+    """One grouped expert GEMM launch (see ``bolt_grouped_gemm``).  With ``segments`` (from
+    ``moe_sorting_ck(..., segment_rows=PAIR_SEGMENT_ROWS)``) the tile-pair schedule runs."""
     lib = _cabi.load()
     args = _cabi.GemmArgs()
     args.kind = kind
@@ -401,6 +419,11 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
     args.act_beta = float(act_beta)
     args.act_limit = float(act_limit or 0.0)
     args.act_has_limit = int(act_limit is not None)
+    if segments is not None:
+        args.schedule = _cabi.SCHEDULE_TILE_PAIRS
+        args.max_segments = segments.shape[0]
+        args.segments = ptr(segments)
+        args.num_segments = ptr(num_segments)
     with torch.cuda.device(a.device):
         check(lib.bolt_grouped_gemm(C.byref(args), stream_of(a)))
     _count()

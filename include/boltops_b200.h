@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define BOLT_ABI_VERSION 2
+#define BOLT_ABI_VERSION 3
 
 enum bolt_status {
   BOLT_OK = 0,
@@ -71,6 +71,17 @@ enum bolt_gemm_kind {
                                  (BOLT_EPI_SILU_MUL_QUANT); k a multiple of 128            */
 };
 
+/* grouped-GEMM schedules */
+enum bolt_gemm_schedule {
+  BOLT_GEMM_SCHEDULE_ROW_TILES = 0,  /* one CTA per 128-row x 256-column tile                      */
+  BOLT_GEMM_SCHEDULE_TILE_PAIRS = 1  /* two CTAs of a cluster share the weight tile of two row
+                                        tiles of one expert (tcgen05 cta_group::2, 256 x 256 per
+                                        pair): for experts with several row tiles.  Needs the
+                                        segment list of bolt_moe_sort_ck with segment_rows =
+                                        BOLT_PAIR_SEGMENT_ROWS; not for the MX kind.               */
+};
+#define BOLT_PAIR_SEGMENT_ROWS 256
+
 enum bolt_gemm_epilogue {
   BOLT_EPI_STORE = 0,        /* C = dequant(A.B^T)                                      */
   BOLT_EPI_SILU_MUL = 1,     /* C = silu(gate)*up, B rows [0,N/2) gate, [N/2,N) up       */
@@ -99,6 +110,12 @@ int bolt_abi_version(void);
  *   route_pos (optional, may be NULL): [num_tokens*topk] position of every route in the
  *                     sorted order, -1 for routes to masked or out-of-range experts (an
  *                     addition of this library: the inverse permutation the combine uses)
+ *   segments / num_segments (optional, may be NULL; another addition): every enabled expert's
+ *                     live rows cut into runs of at most segment_rows rows, in sorted order:
+ *                     segments[4*s..] = {expert id as in sorted_expert_ids, first sorted row,
+ *                     rows, 0}; at most min(E, routes) + routes/segment_rows entries;
+ *                     num_segments[0] = their number.  Consumed by the tile-pair schedule
+ *                     of bolt_grouped_gemm (segment_rows = 2 * unit_size = 256).
  *   moe_buf (optional, may be NULL): zero-filled, moe_buf_bytes long.
  *   workspace: bolt_moe_sort_workspace_bytes() bytes, 16-byte aligned; contents
  *   are scratch and need no initialisation.
@@ -109,7 +126,8 @@ int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weights,
                      int num_experts, int unit_size, int32_t* sorted_ids,
                      float* sorted_weights, int32_t* sorted_expert_ids,
                      int32_t* tokens_positions_per_expert, int32_t* num_valid_ids,
-                     int32_t* route_pos, void* moe_buf, size_t moe_buf_bytes, void* workspace,
+                     int32_t* route_pos, int32_t* segments, int32_t* num_segments,
+                     int segment_rows, void* moe_buf, size_t moe_buf_bytes, void* workspace,
                      size_t workspace_bytes, void* stream);
 
 /* Allocation-free CK-format sort.  Same outputs as bolt_moe_sort_ck, but the scratch
@@ -196,10 +214,12 @@ int bolt_ep_dest_ranks(const int32_t* topk_ids, int64_t num_tokens, int topk, in
  * power2 != 0, dynamic_per_group_quant_fp8_power2 (quant.py:636-661).
  *   x [rows, cols] (bf16/f16/f32, contiguous); group = cols (per token) or a
  *   divisor of cols (1 x group); q [rows, cols] e4m3 or int8; scales fp32
- *   [rows, cols/group].
+ *   [rows, cols/group] (scales_ld == 0) or group-major [cols/group, scales_ld] with
+ *   scales_ld >= rows (the layout bolt_grouped_gemm reads its a_scale in).
  */
 int bolt_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int group,
-                    int q_dtype, int power2, void* q, float* scales, void* stream);
+                    int q_dtype, int power2, void* q, float* scales, int64_t scales_ld,
+                    void* stream);
 
 /* Row gather into the expert-sorted padded layout used by the grouped GEMMs.
  *   dst[i, :] = src[sorted_ids[i] & 0xFFFFFF, :] for i < num_valid_ids[0]
@@ -350,6 +370,15 @@ typedef struct bolt_gemm_args {
   float act_beta;
   float act_limit;
   int act_has_limit;
+  /* schedule (enum bolt_gemm_schedule).  The tile-pair schedule takes its work from the expert
+     segments instead of sorted_expert_ids: segments [max_segments][4] int32 = {expert, first
+     row, live rows, 0}, num_segments [1], both written by bolt_moe_sort_ck.  The reference's
+     nearest notion is its choice between kernel variants by token count
+     (boltops/fused_moe/triton/fused_moe.py:801-821).                                          */
+  int schedule;
+  int max_segments;
+  const int32_t* segments;
+  const int32_t* num_segments;
 } bolt_gemm_args;
 
 int bolt_grouped_gemm(const bolt_gemm_args* args, void* stream);

@@ -210,3 +210,120 @@ def test_dense_block_scaled_gemm(m, n, k, qdtype):
     y2 = w8a8_block_scaled_mm(x_q, w.cuda(), x_s, w_s.cuda(), [128, 128], torch.float16)
     assert y2.dtype == torch.float16
     torch.testing.assert_close(y2.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+# ---------------------------------------------------------------------------
+# tile-pair schedule (two CTAs of a cluster share the weight tile of two row tiles)
+# ---------------------------------------------------------------------------
+def _pair_problem(m, e, topk, seed, mask=None):
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    w, ids = _routing(m, e, topk, seed)
+    pos = torch.empty(ids.shape, dtype=torch.int32, device="cuda")
+    res = ops.moe_sorting_ck(ids.cuda(), w.cuda(), e, None, None, 128,
+                             None if mask is None else mask.cuda(), route_pos=pos,
+                             segment_rows=_cabi.PAIR_SEGMENT_ROWS)
+    torch.cuda.synchronize()
+    return dict(w=w, ids=ids, s_ids=res[0], s_w=res[1], s_e=res[2], nv=res[3], segs=res[6],
+                nseg=res[7], cap=res[0].shape[0], pos=pos, nvi=int(res[3].item()),
+                h_ids=res[0].cpu(), h_e=res[2].cpu())
+
+
+def test_sort_segments_are_pairs_of_row_tiles():
+    """Segment list of the sort: per enabled expert, runs of at most 256 live rows."""
+    import numpy as np
+    m, e, topk = 900, 8, 2
+    mask = torch.ones(e, dtype=torch.int32)
+    mask[2] = 0
+    pr = _pair_problem(m, e, topk, 13, mask)
+    counts = np.bincount(pr["ids"].numpy().ravel(), minlength=e)
+    expect, start, label = [], 0, 0
+    for ex in range(e):
+        if mask[ex] == 0:
+            continue
+        c = int(counts[ex])
+        for r in range(0, c, 256):
+            expect.append([label, start + r, min(256, c - r), 0])
+        start += (c + 127) // 128 * 128
+        label += 1
+    n = int(pr["nseg"].item())
+    assert n == len(expect)
+    assert np.array_equal(pr["segs"].cpu().numpy()[:n], np.array(expect, dtype=np.int32))
+
+
+@pytest.mark.parametrize("kind_name", ["bf16", "fp8_block", "int8_block", "int8_channel"])
+@pytest.mark.parametrize("m,e,topk", [(1500, 8, 2), (700, 4, 1), (300, 16, 4)])
+def test_gemm_tile_pairs_equal_single_tiles(kind_name, m, e, topk):
+    """Same tiles, same arithmetic, other CTA-to-tile mapping: every epilogue of the tile-pair
+    schedule reproduces the single-tile schedule bit for bit (experts with one, two, three and
+    more row tiles, i.e. full pairs and pairs whose second CTA idles), and untouched rows stay
+    untouched."""
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(m + e)
+    inter, k = 256, 512
+    pr = _pair_problem(m, e, topk, 3 + m)
+    x = (torch.randn(m, k) / 2).bfloat16()
+    extra = {}
+    if kind_name == "bf16":
+        kind = _cabi.GEMM_BF16
+        w1 = (torch.randn(e, 2 * inter, k) / 8).bfloat16()
+        a_sorted, _ = ops.gather_rows(x.cuda(), pr["s_ids"], pr["nv"], pr["cap"])
+    elif kind_name in ("fp8_block", "int8_block"):
+        qd = FP8 if kind_name == "fp8_block" else torch.int8
+        kind = _cabi.GEMM_FP8_BLOCK if qd == FP8 else _cabi.GEMM_INT8_BLOCK
+        w1 = ((torch.randn(e, 2 * inter, k) * 40).clamp(-448, 448).to(FP8) if qd == FP8
+              else torch.randint(-127, 128, (e, 2 * inter, k), dtype=torch.int8))
+        a_sorted, a_scale = ops.quant_scatter_rows(x.cuda(), 128, qd, pr["pos"], pr["s_ids"],
+                                                   pr["nv"], pr["cap"])
+        extra = dict(a_scale=a_scale, a_scale_ld=pr["cap"],
+                     b_scale=(torch.rand(e, 2 * inter // 128, k // 128) * 1e-2 + 1e-3).cuda())
+    else:
+        kind = _cabi.GEMM_INT8_CHANNEL
+        w1 = torch.randint(-127, 128, (e, 2 * inter, k), dtype=torch.int8)
+        xq, xs = ops.per_token_quant(x.cuda(), quant_dtype=torch.int8)
+        a_sorted, a_scale = ops.gather_rows(xq, pr["s_ids"], pr["nv"], pr["cap"], xs)
+        extra = dict(a_scale=a_scale, b_scale=(torch.rand(e, 2 * inter) * 1e-2 + 1e-3).cuda())
+    bias = (torch.randn(e, 2 * inter) / 4).bfloat16().cuda()
+    common = dict(kind=kind, sorted_expert_ids=pr["s_e"], num_valid=pr["nv"], a=a_sorted,
+                  b=w1.cuda(), sorted_ids=pr["s_ids"], sorted_weights=pr["s_w"], num_tokens=m,
+                  topk=topk, **extra)
+    pairs = dict(segments=pr["segs"], num_segments=pr["nseg"])
+    sentinel = -12345.0   # exactly representable in bf16 / fp32
+
+    def run(sched, shape, dtype=torch.bfloat16, **kw):
+        c = torch.full(shape, sentinel, dtype=dtype, device="cuda") if dtype.is_floating_point \
+            and dtype not in (FP8,) else torch.zeros(shape, dtype=dtype, device="cuda")
+        cs = kw.pop("c_scale_shape", None)
+        if cs is not None:
+            kw["c_scale"] = torch.full(cs, sentinel, dtype=torch.float32, device="cuda")
+            kw["c_scale_ld"] = cs[1]
+        ops.grouped_gemm(c=c, **kw, **common, **sched)
+        torch.cuda.synchronize()
+        ops.check_device_status(c.device)
+        return c, kw.get("c_scale")
+
+    cap = pr["cap"]
+    cases = [
+        dict(epilogue=_cabi.EPI_STORE, bias=bias, shape=(cap, 2 * inter)),
+        dict(epilogue=_cabi.EPI_STORE, scatter=True, mul_routed_weight=True,
+             shape=(m * topk, 2 * inter)),
+        dict(epilogue=_cabi.EPI_STORE, shape=(cap, 2 * inter), dtype=torch.float32),
+        dict(epilogue=_cabi.EPI_SILU_MUL, bias=bias, mid_dtype=torch.bfloat16, shape=(cap, inter)),
+    ]
+    if kind_name in ("fp8_block", "int8_block"):
+        cases.append(dict(epilogue=_cabi.EPI_SILU_MUL_QUANT, mid_dtype=torch.bfloat16,
+                          shape=(cap, inter), dtype=FP8 if kind_name == "fp8_block" else torch.int8,
+                          c_scale_shape=(inter // 128, cap)))
+    for case in cases:
+        shape = case.pop("shape")
+        dtype = case.pop("dtype", torch.bfloat16)
+        c1, s1 = run({}, shape, dtype, **dict(case))
+        c2, s2 = run(pairs, shape, dtype, **dict(case))
+        v1 = c1.view(torch.uint8) if dtype in (FP8, torch.int8) else c1
+        v2 = c2.view(torch.uint8) if dtype in (FP8, torch.int8) else c2
+        assert torch.equal(v1, v2), f"{kind_name} {case.get('epilogue')} differs"
+        if s1 is not None:
+            assert torch.equal(s1, s2)
+        if dtype == torch.bfloat16 and not case.get("scatter"):
+            assert (c2 != sentinel).any()

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(lib):
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert declared == set(_cabi.EXPORTS)
-    assert lib.bolt_abi_version() == 2
+    assert lib.bolt_abi_version() == 3
 
 
 def test_gemm_args_struct_matches_header(tmp_path):

@@ -335,3 +335,53 @@ def test_layer_special_values_stay_in_their_rows():
     assert torch.equal(out[ok_rows], clean[ok_rows])
     assert torch.isfinite(out[10].float()).all() and (out[10] == 0).all()
     assert torch.isfinite(out[11].float()).all()
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8_block", "int8_channel"])
+def test_layer_tile_pair_schedule(monkeypatch, kind):
+    """The layer with the tile-pair GEMM schedule forced (experts with one to five row tiles,
+    expert parallel mask included): equal to the single-tile schedule bit for bit, and within
+    the tolerance of the oracle."""
+    from boltops_b200.fused_moe import fused_experts
+    m, e, topk, h, i = 1200, 8, 2, 512, 256
+    g = torch.Generator().manual_seed(21)
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    m1 = torch.randn(e, 2 * i, h, generator=g) * 0.05
+    m2 = torch.randn(e, h, i, generator=g) * 0.05
+    wts, ids = O.make_routing(m, e, topk, 8)
+    if kind == "bf16":
+        w1, w2, kw, tol = m1.bfloat16(), m2.bfloat16(), {}, 1e-2
+        expect = O.moe_bf16(hidden, w1, w2, wts, ids)
+    elif kind == "fp8_block":
+        w1, w1s = O.quantize_weight_block_fp8(m1)
+        w2, w2s = O.quantize_weight_block_fp8(m2)
+        kw, tol = dict(use_fp8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(),
+                       block_shape=[128, 128]), 2e-2
+        expect = O.moe_block_fp8(hidden, w1, w2, w1s, w2s, wts, ids, (128, 128))
+    else:
+        w1, w1s = O.quantize_weight_channel_int8(m1)
+        w2, w2s = O.quantize_weight_channel_int8(m2)
+        kw, tol = dict(use_int8_w8a8=True, per_channel_quant=True, w1_scale=w1s.cuda(),
+                       w2_scale=w2s.cuda()), 2e-2
+        expect = O.moe_per_channel(hidden, w1, w2, w1s, w2s, wts, ids, torch.int8)
+    args = _dev(hidden, w1, w2, wts, ids)
+    outs = {}
+    for sched in ("tiles", "pairs"):
+        monkeypatch.setenv("BOLTOPS_B200_GEMM_SCHEDULE", sched)
+        outs[sched] = _finish(fused_experts(*args, **kw))
+    assert torch.equal(outs["pairs"], outs["tiles"])
+    assert O.rel_l2(outs["pairs"], expect) <= tol
+    # expert-parallel mask: two ranks' partial outputs add up to the full layer
+    monkeypatch.setenv("BOLTOPS_B200_GEMM_SCHEDULE", "pairs")
+    total = torch.zeros(m, h)
+    for lo in (0, 4):
+        emap = torch.full((e,), -1, dtype=torch.int32)
+        emap[lo:lo + 4] = torch.arange(4, dtype=torch.int32)
+        loc = dict(kw)
+        for name in ("w1_scale", "w2_scale"):
+            if name in loc:
+                loc[name] = loc[name][lo:lo + 4]
+        part = fused_experts(args[0], args[1][lo:lo + 4], args[2][lo:lo + 4], args[3], args[4],
+                             expert_map=emap.cuda(), global_num_experts=e, **loc)
+        total += _finish(part).float()
+    assert O.rel_l2(total, outs["pairs"].float()) <= 1e-2

@@ -42,7 +42,8 @@ def _sort_both(lib, ptr, tokens, experts, topk, unit, seed, use_mask):
     ws_bytes = lib.bolt_moe_sort_workspace_bytes(tokens, topk, experts)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
     _cabi.check(lib.bolt_moe_sort_ck(ptr(d_ids), ptr(d_w), ptr(d_mask), tokens, topk, experts, unit,
-                                     *(ptr(x) for x in ref), None, None, 0, ptr(ws), ws_bytes, stream))
+                                     *(ptr(x) for x in ref), None, None, None, 0, None, 0, ptr(ws), ws_bytes,
+                                     stream))
     got = outputs()
     _cabi.check(lib.bolt_moe_sort_ck_static(ptr(d_ids), ptr(d_w), ptr(d_mask), tokens, topk,
                                             experts, unit, *(ptr(x) for x in got), stream))
