@@ -501,6 +501,9 @@ def main():
     from boltops_b200.fused_moe import fused_experts, layer, ops
 
     _cabi.load()
+    config["gemm_schedule"] = layer.gemm_schedule(
+        _cabi.GEMM_BF16 if cfg["kind"] == "bf16" else _cabi.GEMM_FP8_BLOCK, m * cfg["K"] * world,
+        cfg["E"])
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     dist = None

@@ -80,11 +80,13 @@ def _chunk_size() -> int:
 
 
 def _use_tile_pairs(kind: int, routes: int, experts: int) -> bool:
-    """Schedule of the two grouped GEMMs.  From about three 128-row tiles per expert on, two
-    CTAs of a cluster take two row tiles of one expert and share its weight tile (tcgen05
-    ``cta_group::2``): each CTA then stages half of the weight tile, which lifts the
-    shared-memory bandwidth limit a single CTA meets at full tensor-core rate.  With fewer rows
-    per expert many pairs would hold one live tile, so single tiles stay.  The host knows only
+    """Schedule of the two grouped GEMMs.  In the tile-pair schedule two CTAs of a cluster take
+    two row tiles of one expert and share its weight tile (tcgen05 ``cta_group::2``): each CTA
+    stages half of the weight tile.  Measured on B200 (same box, same inputs, results bit
+    identical): +2-3 % for 16-bit experts with many row tiles per expert (Mixtral shape, 16
+    tiles), no change for per-channel 8-bit experts, and slower for the block-scaled kinds,
+    whose per-K-block promotion chain now has to wait for the epilogues of two CTAs.  So pairs
+    are used for bf16 / fp16 experts from three row tiles per expert on.  The host knows only
     the average (tokens * topk / experts).  ``BOLTOPS_B200_GEMM_SCHEDULE`` = ``tiles`` /
     ``pairs`` overrides the choice."""
     forced = os.environ.get("BOLTOPS_B200_GEMM_SCHEDULE", "auto")
@@ -92,6 +94,8 @@ def _use_tile_pairs(kind: int, routes: int, experts: int) -> bool:
         return False
     if forced == "pairs":
         return True
+    if kind not in (_cabi.GEMM_BF16, _cabi.GEMM_F16):
+        return False
     return routes >= _PAIR_MIN_AVG_ROWS * max(experts, 1)
 
 
