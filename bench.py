@@ -454,6 +454,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--measure-peaks", action="store_true",
                     help="measure the library GEMM peaks (bf16, e4m3, int8) on cuda:0 and exit")
+    ap.add_argument("--ep-chunks", type=int, default=2,
+                    help="N > 1: token chunks of the pipelined dispatch / return exchange (1 = serial)")
+    ap.add_argument("--ep-comm-sms", type=int, default=16,
+                    help="N > 1: SMs left to the exchange kernels while GEMMs run beside them "
+                         "(also the CTA limit given to NCCL)")
     ap.add_argument("--graph", action="store_true",
                     help="1 GPU only: replay the layer from a CUDA graph in the device-resident timing")
     args = ap.parse_args()
@@ -511,6 +516,9 @@ def main():
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        if args.ep_chunks > 1 and args.ep_comm_sms > 0:
+            # the exchange kernels run beside the expert GEMMs: keep them on the SMs left to them
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.ep_comm_sms))
         dist.init_process_group("nccl", device_id=device)
 
     E = cfg["E"]
@@ -530,6 +538,10 @@ def main():
         # every rank brings the same number of tokens here, so decode-sized batches may take the
         # replicated-token path (no host round trips); the headline batch stays on the dispatch
         ep.replicate_below = 4096
+        ep.pipeline_chunks = args.ep_chunks
+        ep.comm_sms = args.ep_comm_sms
+        config["ep_chunks"] = ep.num_chunks(m)
+        config["ep_comm_sms"] = args.ep_comm_sms
 
         def step(h, w, i):
             return ep.forward(h, w1, w2, w, i, **kwargs)

@@ -84,7 +84,11 @@ _SIGNATURES = {
                                       C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
                                       C.c_void_p]),
     "bolt_ep_dest_ranks": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
-                                     C.c_void_p, C.c_void_p]),
+                                     C.c_int64, C.c_void_p, C.c_void_p]),
+    "bolt_ep_wire_row_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int]),
+    "bolt_ep_pack_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                    C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64,
+                                    C.c_void_p, C.c_int64, C.c_void_p]),
     "bolt_quant_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "bolt_quant_scatter_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
@@ -97,9 +101,9 @@ _SIGNATURES = {
                                        C.c_int, C.c_void_p]),
     "bolt_mx_sf_layout": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
                                     C.c_void_p, C.c_void_p]),
-    "bolt_gather_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
-                                   C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
-                                   C.c_void_p]),
+    "bolt_gather_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_int64,
+                                   C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
+                                   C.c_void_p, C.c_int64, C.c_void_p]),
     "bolt_moe_activation": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,
                                       C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p]),
     "bolt_act_quant": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,

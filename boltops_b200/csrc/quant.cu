@@ -282,8 +282,9 @@ int dispatch_quant(const void* x, int64_t rows, int cols, int group, int q_dtype
 // ---- gather into expert-sorted rows ----------------------------------------------
 __global__ void __launch_bounds__(256) k_gather_rows(const uint4* __restrict__ src,
                                                      int num_tokens, int row_vecs,
+                                                     int64_t src_stride_vecs,
                                                      const float* __restrict__ src_scale,
-                                                     int groups,
+                                                     int64_t scale_stride, int groups,
                                                      const int32_t* __restrict__ sorted_ids,
                                                      const int32_t* __restrict__ num_valid,
                                                      int capacity, uint4* __restrict__ dst,
@@ -307,14 +308,14 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint4* __restrict__ s
       }
       continue;
     }
-    const uint4* s = src + (int64_t)token * row_vecs;
+    const uint4* s = src + (int64_t)token * src_stride_vecs;
     for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = __ldg(s + i);
     if (src_scale != nullptr) {
       if (groups == 1) {
-        if (threadIdx.x == 0) dst_scale[row] = src_scale[token];
+        if (threadIdx.x == 0) dst_scale[row] = src_scale[(int64_t)token * scale_stride];
       } else {
         for (int g = threadIdx.x; g < groups; g += blockDim.x)
-          dst_scale[(int64_t)g * dst_scale_ld + row] = src_scale[(int64_t)token * groups + g];
+          dst_scale[(int64_t)g * dst_scale_ld + row] = src_scale[(int64_t)token * scale_stride + g];
       }
     }
   }
@@ -703,12 +704,19 @@ extern "C" int bolt_quant_rows(const void* x, int x_dtype, int64_t rows, int col
 }
 
 extern "C" int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
-                                const float* src_scale, int groups, const int32_t* sorted_ids,
+                                int64_t src_stride_bytes, const float* src_scale,
+                                int64_t src_scale_stride, int groups, const int32_t* sorted_ids,
                                 const int32_t* num_valid_ids, int capacity, void* dst,
                                 float* dst_scale, int64_t dst_scale_ld, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "gather: row_bytes must be a multiple of 16");
+  if (src_stride_bytes == 0) src_stride_bytes = row_bytes;
+  if (src_scale_stride == 0) src_scale_stride = groups;
+  BOLT_REQUIRE(src_stride_bytes >= row_bytes && src_stride_bytes % 16 == 0,
+               "gather: source row stride must be a multiple of 16 bytes, at least one row");
+  BOLT_REQUIRE(src_scale == nullptr || src_scale_stride >= groups,
+               "gather: scale row stride below the group count");
   BOLT_REQUIRE(capacity >= 0 && num_tokens >= 0, "gather: bad sizes");
   if (capacity == 0 || num_tokens == 0) return BOLT_OK;
   BOLT_REQUIRE(src && dst && sorted_ids && num_valid_ids, "gather: null pointer");
@@ -716,9 +724,11 @@ extern "C" int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
                "gather: buffers must be 16-byte aligned");
   BOLT_REQUIRE(src_scale == nullptr || (dst_scale != nullptr && groups >= 1),
                "gather: scale arguments inconsistent");
-  const int grid = capacity < 148 * 16 ? capacity : 148 * 16;
+  const int max_grid = sm_count_of_current_device() * 16;
+  const int grid = capacity < max_grid ? capacity : max_grid;
   k_gather_rows<<<grid, 256, 0, st>>>(static_cast<const uint4*>(src), num_tokens, row_bytes / 16,
-                                      src_scale, groups, sorted_ids, num_valid_ids, capacity,
+                                      src_stride_bytes / 16, src_scale, src_scale_stride, groups,
+                                      sorted_ids, num_valid_ids, capacity,
                                       static_cast<uint4*>(dst), dst_scale, dst_scale_ld);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;

@@ -222,9 +222,12 @@ int launch_topk(const void* logits, int64_t tokens, int experts, int topk, int r
 __global__ void __launch_bounds__(256) k_dest_ranks(const int32_t* __restrict__ topk_ids,
                                                     int64_t num_tokens, int topk, int num_experts,
                                                     int experts_per_rank, int world,
+                                                    int64_t chunk_tokens,
                                                     int32_t* __restrict__ routes) {
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < num_tokens;
        t += (int64_t)gridDim.x * blockDim.x) {
+    // with token chunks the sort key is (chunk, rank): chunk-major send order
+    const int base = chunk_tokens > 0 ? (int)(t / chunk_tokens) * world : 0;
     unsigned long long mask[4] = {0ull, 0ull, 0ull, 0ull};
     for (int k = 0; k < topk; ++k) {
       const int e = topk_ids[t * topk + k];
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(256) k_dest_ranks(const int32_t* __restrict__ 
       }
     }
     for (int r = 0; r < world; ++r)
-      routes[t * world + r] = ((mask[r >> 6] >> (r & 63)) & 1ull) ? r : -1;
+      routes[t * world + r] = ((mask[r >> 6] >> (r & 63)) & 1ull) ? base + r : -1;
   }
 }
 
@@ -302,7 +305,7 @@ extern "C" int bolt_moe_fused_gate(const void* gating, int dtype, const float* b
 
 extern "C" int bolt_ep_dest_ranks(const int32_t* topk_ids, int64_t num_tokens, int topk,
                                   int num_experts, int experts_per_rank, int world,
-                                  int32_t* routes, void* stream) {
+                                  int64_t chunk_tokens, int32_t* routes, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(num_tokens >= 0 && topk > 0 && num_experts > 0 && experts_per_rank > 0,
@@ -316,8 +319,68 @@ extern "C" int bolt_ep_dest_ranks(const int32_t* topk_ids, int64_t num_tokens, i
   int64_t blocks = (num_tokens + 255) / 256;
   const int64_t cap = (int64_t)sm_count_of_current_device() * 8;
   if (blocks > cap) blocks = cap;
+  BOLT_REQUIRE(chunk_tokens >= 0, "ep_dest_ranks: negative chunk size");
   k_dest_ranks<<<(unsigned)blocks, 256, 0, st>>>(topk_ids, num_tokens, topk, num_experts,
-                                                 experts_per_rank, world, routes);
+                                                 experts_per_rank, world, chunk_tokens, routes);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+namespace bolt {
+namespace {
+// One warp per wire row: [row data | scales | top-k ids | top-k weights], every part padded to 16
+// bytes, row i taken from token send_ids[first + i] & 0xFFFFFF.
+__global__ void __launch_bounds__(256) k_ep_pack_rows(
+    const uint4* __restrict__ data, int data_vecs, const float* __restrict__ scales, int groups,
+    const int32_t* __restrict__ ids, const float* __restrict__ wts, int topk,
+    const int32_t* __restrict__ send_ids, int64_t first, int64_t rows, uint8_t* __restrict__ out,
+    int64_t out_stride) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int sc_bytes = (groups * 4 + 15) & ~15, k_bytes = (topk * 4 + 15) & ~15;
+  for (int64_t i = warp; i < rows; i += warps) {
+    const int64_t t = send_ids[first + i] & 0xFFFFFF;
+    uint8_t* o = out + i * out_stride;
+    const uint4* src = data + t * data_vecs;
+    for (int v = lane; v < data_vecs; v += 32) reinterpret_cast<uint4*>(o)[v] = __ldg(src + v);
+    o += (int64_t)data_vecs * 16;
+    for (int g = lane; g < groups; g += 32) reinterpret_cast<float*>(o)[g] = scales[t * groups + g];
+    o += sc_bytes;
+    for (int k = lane; k < topk; k += 32) {
+      reinterpret_cast<int32_t*>(o)[k] = ids[t * topk + k];
+      reinterpret_cast<float*>(o + k_bytes)[k] = wts[t * topk + k];
+    }
+  }
+}
+}  // namespace
+}  // namespace bolt
+
+extern "C" int64_t bolt_ep_wire_row_bytes(int row_bytes, int groups, int topk) {
+  return (int64_t)((row_bytes + 15) & ~15) + ((groups * 4 + 15) & ~15) + 2 * ((topk * 4 + 15) & ~15);
+}
+
+extern "C" int bolt_ep_pack_rows(const void* data, int row_bytes, const float* scales, int groups,
+                                 const int32_t* topk_ids, const float* topk_weights, int topk,
+                                 const int32_t* send_ids, int64_t first, int64_t rows, void* out,
+                                 int64_t out_stride, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "ep_pack: row_bytes must be a multiple of 16");
+  BOLT_REQUIRE(groups >= 0 && topk > 0 && rows >= 0 && first >= 0, "ep_pack: bad sizes");
+  BOLT_REQUIRE(out_stride >= bolt_ep_wire_row_bytes(row_bytes, groups, topk) && out_stride % 16 == 0,
+               "ep_pack: output row stride too small");
+  if (rows == 0) return BOLT_OK;
+  BOLT_REQUIRE(data && topk_ids && topk_weights && send_ids && out && (groups == 0 || scales),
+               "ep_pack: null pointer");
+  BOLT_REQUIRE((reinterpret_cast<uintptr_t>(data) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
+               "ep_pack: buffers must be 16-byte aligned");
+  int64_t blocks = (rows + 7) / 8;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 16;
+  if (blocks > cap) blocks = cap;
+  k_ep_pack_rows<<<(unsigned)blocks, 256, 0, st>>>(
+      static_cast<const uint4*>(data), row_bytes / 16, scales, groups, topk_ids, topk_weights, topk,
+      send_ids, first, rows, static_cast<uint8_t*>(out), out_stride);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }

@@ -62,58 +62,79 @@ class ExpertParallelMoE:
         # all-gather the tokens, run the masked local layer on all of them, reduce-scatter
         # the partial outputs.  0 = never (the caller must guarantee equal token counts).
         self.replicate_below = 0
+        # Pipelined exchange: batches of at least pipeline_min_tokens tokens are cut into
+        # pipeline_chunks token chunks; the all-to-alls of neighbouring chunks run on a second
+        # stream under the expert GEMMs of the current one.  The GEMMs then leave comm_sms SMs
+        # to the exchange kernels (a persistent GEMM on every SM would keep them waiting).
+        self.pipeline_chunks = 2
+        self.pipeline_min_tokens = 1024
+        self.comm_sms = 16
+        self._comm = None
 
     # -- index construction ---------------------------------------------------------------
-    def plan(self, topk_ids: torch.Tensor):
-        """Which token goes to which rank.  Returns ``(tok_idx [S], send_counts [R],
-        pos [M, R])``: rows to send ordered by (rank, token); ``pos[m, r]`` = row of token
-        m's partial result in the returned buffer, -1 if rank r owns none of its experts."""
-        if topk_ids.is_cuda and self.world <= 255:
-            return self._plan_cuda(topk_ids)
-        return self._plan_torch(topk_ids)
+    def plan(self, topk_ids: torch.Tensor, chunks: int = 1):
+        """Which token goes to which rank.  Returns ``(tok_idx [S], send_counts [chunks * R],
+        pos [M, R])``: rows to send ordered by (token chunk, rank, token); ``pos[m, r]`` = row
+        of token m's partial result in the returned buffer, -1 if rank r owns none of its
+        experts.  Token chunk c holds tokens ``[c * ceil(M / chunks), ...)``."""
+        if topk_ids.is_cuda and self.world * chunks <= 255:
+            return self._plan_cuda(topk_ids, chunks)
+        return self._plan_torch(topk_ids, chunks)
 
-    def _plan_cuda(self, topk_ids: torch.Tensor):
+    @staticmethod
+    def chunk_tokens(m: int, chunks: int) -> int:
+        return max((m + chunks - 1) // chunks, 1)
+
+    def _plan_cuda(self, topk_ids: torch.Tensor, chunks: int = 1):
         """Same result as :meth:`_plan_torch` without a host synchronisation: "token m goes
-        to rank r" is a route of token m to "expert" r, so the layer's own stable sort (unit
-        1, ranks as experts) yields the (rank, token) order, the per-rank counts and, as its
-        inverse permutation, ``pos``."""
+        to rank r" is a route of token m to "expert" (chunk, r), so the layer's own stable sort
+        (unit 1) yields the (chunk, rank, token) order, the counts and, as its inverse
+        permutation, ``pos``."""
         from . import ops
         m = topk_ids.shape[0]
-        routes = ops.ep_dest_ranks(topk_ids, self.num_experts, self.per_rank, self.world)
+        routes = ops.ep_dest_ranks(topk_ids, self.num_experts, self.per_rank, self.world,
+                                   self.chunk_tokens(m, chunks) if chunks > 1 else 0)
         dummy_w = torch.empty((m, self.world), dtype=torch.float32, device=topk_ids.device)
         pos = torch.empty((m, self.world), dtype=torch.int32, device=topk_ids.device)
         sorted_ids, _, _, _, counts, _ = ops.moe_sorting_ck(
-            routes, dummy_w, self.world, None, None, 1, None, alloc_moe_buf=False, route_pos=pos)
-        send_counts = counts[:self.world].long()
+            routes, dummy_w, self.world * chunks, None, None, 1, None, alloc_moe_buf=False,
+            route_pos=pos)
+        send_counts = counts[:self.world * chunks].long()
         # rows beyond the number of sent rows are cut by the caller once the counts are on the host
         tok_idx = (sorted_ids & 0xFFFFFF).long()
         return tok_idx, send_counts, pos
 
-    def _plan_torch(self, topk_ids: torch.Tensor):
+    def _plan_torch(self, topk_ids: torch.Tensor, chunks: int = 1):
         m = topk_ids.shape[0]
         dest = torch.div(topk_ids.long(), self.per_rank, rounding_mode="floor")
         valid = (topk_ids >= 0) & (topk_ids < self.num_experts)
         hit = torch.zeros((m, self.world + 1), dtype=torch.bool, device=topk_ids.device)
         hit.scatter_(1, torch.where(valid, dest, torch.full_like(dest, self.world)), True)
         hit = hit[:, :self.world]
-        rank_idx, tok_idx = hit.t().nonzero(as_tuple=True)          # sorted by rank, then token
-        send_counts = hit.sum(dim=0)
+        ct = self.chunk_tokens(m, chunks)
+        chunk_of = torch.div(torch.arange(m, device=topk_ids.device), ct, rounding_mode="floor")
+        # key (chunk, rank) per (token, rank) pair; a stable sort keeps tokens ascending
+        tok, rank = hit.nonzero(as_tuple=True)
+        key = chunk_of[tok] * self.world + rank
+        order = torch.sort(key, stable=True).indices
+        tok_idx, rank_idx, key = tok[order], rank[order], key[order]
+        send_counts = torch.bincount(key, minlength=self.world * chunks)[:self.world * chunks]
         pos = torch.full((m, self.world), -1, dtype=torch.int32, device=topk_ids.device)
         pos[tok_idx, rank_idx] = torch.arange(tok_idx.numel(), dtype=torch.int32,
                                               device=topk_ids.device)
         return tok_idx, send_counts, pos
 
-    def _exchange_counts(self, send_counts: torch.Tensor):
-        both = torch.empty((2, send_counts.numel()), dtype=send_counts.dtype,
-                           device=send_counts.device)
-        both[0].copy_(send_counts)
+    def _exchange_counts(self, send_counts: torch.Tensor, chunks: int = 1):
+        """All ranks learn how many rows every peer sends them per chunk.  Returns
+        ``(send_split, recv_split)``: lists ``[chunk][rank]``.  One small all-to-all and the
+        one host synchronisation of the dispatch."""
+        world = self.world
+        both = torch.empty((2, world, chunks), dtype=send_counts.dtype, device=send_counts.device)
+        both[0].copy_(send_counts.view(chunks, world).t())      # grouped by destination rank
         dist.all_to_all_single(both[1], both[0], group=self.group)
-        send_split, recv_split = both.tolist()          # one host synchronisation for both
-        if both.is_cuda:
-            # the host has just synchronised with the device anyway: a good moment to notice a
-            # bounded device-side wait that expired in an earlier layer
-            from . import ops
-            ops.check_device_status(both.device)
+        send_rc, recv_rc = both.tolist()                        # the host synchronisation
+        send_split = [[send_rc[r][c] for r in range(world)] for c in range(chunks)]
+        recv_split = [[recv_rc[r][c] for r in range(world)] for c in range(chunks)]
         return send_split, recv_split
 
     # -- small batches: replicated tokens, no dispatch ---------------------------------------
@@ -150,7 +171,49 @@ class ExpertParallelMoE:
         self.last_stats = dict(mode="replicated", tokens=m * world)
         return mine.to(out_dtype)
 
+    # -- wire format -------------------------------------------------------------------------
+    @staticmethod
+    def _a16(n: int) -> int:
+        return (n + 15) // 16 * 16
+
+    def _wire_layout(self, row_bytes: int, groups: int, topk: int):
+        """Byte offsets of the parts of a wire row: data, scales, ids, weights; total size."""
+        o_scale = self._a16(row_bytes)
+        o_ids = o_scale + self._a16(groups * 4)
+        o_w = o_ids + self._a16(topk * 4)
+        return o_scale, o_ids, o_w, o_w + self._a16(topk * 4)
+
+    def _pack(self, x, x_scale, ids32, w32, tok_idx, send_ids, first, rows, wire):
+        """Send buffer of one chunk: one wire row per (token, destination rank)."""
+        row_bytes = x.shape[1] * x.element_size()
+        groups = 0 if x_scale is None else x_scale.shape[1]
+        o_scale, o_ids, o_w, total = wire
+        out = torch.empty((rows, total), dtype=torch.uint8, device=x.device)
+        if rows == 0:
+            return out
+        if x.is_cuda:
+            from . import ops
+            ops.ep_pack_rows(x, x_scale, ids32, w32, send_ids, first, rows, out)
+            return out
+        sel = tok_idx[first:first + rows]            # CPU ranks (tests): same bytes with torch ops
+        out.zero_()
+        out[:, :row_bytes] = x.index_select(0, sel).view(torch.uint8).reshape(rows, row_bytes)
+        if groups:
+            out[:, o_scale:o_scale + groups * 4] = \
+                x_scale.index_select(0, sel).contiguous().view(torch.uint8).reshape(rows, -1)
+        k = ids32.shape[1]
+        out[:, o_ids:o_ids + 4 * k] = ids32.index_select(0, sel).view(torch.uint8).reshape(rows, -1)
+        out[:, o_w:o_w + 4 * k] = w32.index_select(0, sel).view(torch.uint8).reshape(rows, -1)
+        return out
+
     # -- the layer ----------------------------------------------------------------------------
+    def num_chunks(self, m: int) -> int:
+        """Token chunks of the pipelined exchange: chunk i+1 travels to the experts and chunk
+        i-1 travels back while chunk i is computed."""
+        if self.pipeline_chunks <= 1 or m < self.pipeline_min_tokens:
+            return 1
+        return max(1, min(self.pipeline_chunks, 255 // self.world, m))
+
     def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
         m, h = hidden_states.shape
         if self.replicate_below and m * self.world <= self.replicate_below \
@@ -158,28 +221,30 @@ class ExpertParallelMoE:
             return self.forward_replicated(hidden_states, w1_local, w2_local, topk_weights,
                                            topk_ids, **kwargs)
         k = topk_ids.shape[1]
+        world = self.world
+        dev = hidden_states.device
+        cuda = hidden_states.is_cuda
+        chunks = self.num_chunks(m)
         marks = []
 
         def mark(name):
-            if self.profile and hidden_states.is_cuda:
+            if self.profile and cuda:
                 ev = torch.cuda.Event(enable_timing=True)
                 ev.record()
                 marks.append((name, ev))
 
         mark("start")
-        tok_idx, send_counts, pos = self.plan(topk_ids)
-        send_split, recv_split = self._exchange_counts(send_counts)
-        n_recv = int(sum(recv_split))
-        tok_idx = tok_idx[: int(sum(send_split))]
-        mark("plan+counts")
+        tok_idx, send_counts, pos = self.plan(topk_ids, chunks)
+        send_ids = tok_idx.to(torch.int32) if cuda else None
 
         # Quantise before the wire when the experts are w8a8: the rows then cross NVLink as
         # 8-bit codes + scales instead of 16-bit values, and the local layer takes them as
-        # pre-quantised input (same codes it would have produced itself).
+        # pre-quantised input (same codes it would have produced itself).  Enqueued before the
+        # counts are read back, so the device works while the host waits for them.
         out_dtype = kwargs.get("output_dtype") or hidden_states.dtype
         x, x_scale = hidden_states, None
         w8a8 = kwargs.get("use_fp8_w8a8") or kwargs.get("use_int8_w8a8")
-        if (self.quantize_dispatch and w8a8 and hidden_states.is_cuda
+        if (self.quantize_dispatch and w8a8 and cuda
                 and hidden_states.dtype in (torch.float16, torch.bfloat16)
                 and not kwargs.get("use_ue8m0")):
             from . import ops
@@ -188,45 +253,113 @@ class ExpertParallelMoE:
                 x, x_scale = ops.per_token_quant(hidden_states, quant_dtype=qd)
             elif kwargs.get("block_shape") is not None:
                 x, x_scale = ops.per_block_quant(hidden_states, kwargs["block_shape"][1], qd)
-        dev = hidden_states.device
-        meta_cols = [topk_ids.to(torch.int32), topk_weights.to(torch.float32).view(torch.int32)]
         if x_scale is not None:
-            meta_cols.append(x_scale.reshape(m, -1).view(torch.int32))
-        meta = torch.cat(meta_cols, dim=1)
-        send_meta = meta.index_select(0, tok_idx)
-        send_x = x.view(torch.uint8).index_select(0, tok_idx) if x_scale is not None \
-            else x.index_select(0, tok_idx)
-        recv_x = torch.empty((n_recv, send_x.shape[1]), dtype=send_x.dtype, device=dev)
-        recv_meta = torch.empty((n_recv, meta.shape[1]), dtype=torch.int32, device=dev)
-        dist.all_to_all_single(recv_x, send_x, recv_split, send_split, group=self.group)
-        dist.all_to_all_single(recv_meta, send_meta, recv_split, send_split, group=self.group)
+            x_scale = x_scale.reshape(m, -1)
+        x = x.contiguous()
+        ids32 = topk_ids.to(torch.int32).contiguous()
+        w32 = topk_weights.to(torch.float32).contiguous()
+        row_bytes = x.shape[1] * x.element_size()
+        groups = 0 if x_scale is None else x_scale.shape[1]
+        wire = self._wire_layout(row_bytes, groups, k)
+        o_scale, o_ids, o_w, wire_bytes = wire
+
+        send_split, recv_split = self._exchange_counts(send_counts, chunks)
+        mark("plan+counts")
+
+        n_send = [sum(v) for v in send_split]
+        n_recv = [sum(v) for v in recv_split]
+        first = [sum(n_send[:c]) for c in range(chunks)]
+        total_send = sum(n_send)
+        back = torch.empty((total_send, h), dtype=out_dtype, device=dev)
+        main = torch.cuda.current_stream(dev) if cuda else None
+        comm = self._comm_stream(dev) if cuda and chunks > 1 else None
+        keep = []                                   # buffers shared between the two streams
+
+        def exchange(dst, src, dst_split, src_split, after):
+            """All-to-all of one chunk; on GPUs with several chunks it runs on the exchange
+            stream once `after` (an event of the main stream) has happened."""
+            keep.extend((dst, src))
+            if comm is None:
+                dist.all_to_all_single(dst, src, dst_split, src_split, group=self.group)
+                return None
+            with torch.cuda.stream(comm):
+                comm.wait_event(after)
+                work = dist.all_to_all_single(dst, src, dst_split, src_split, group=self.group,
+                                              async_op=True)
+            return work
+
+        def event():
+            ev = torch.cuda.Event()
+            ev.record(main)
+            return ev
+
+        # ---- dispatch of every chunk is enqueued first: chunk c + 1 crosses the wire while
+        # chunk c is computed
+        recv_bufs, d_work = [], []
+        for c in range(chunks):
+            send_buf = self._pack(x, x_scale, ids32, w32, tok_idx, send_ids, first[c], n_send[c],
+                                  wire)
+            recv_buf = torch.empty((n_recv[c], wire_bytes), dtype=torch.uint8, device=dev)
+            d_work.append(exchange(recv_buf, send_buf, recv_split[c], send_split[c],
+                                   event() if comm is not None else None))
+            recv_bufs.append(recv_buf)
         mark("dispatch")
 
-        r_ids = recv_meta[:, :k].contiguous()
-        r_w = recv_meta[:, k:2 * k].contiguous().view(torch.float32)
         local_kwargs = dict(kwargs)
         if x_scale is not None:
-            recv_x = recv_x.view(x.dtype)
-            local_kwargs["a1_scale"] = recv_meta[:, 2 * k:].contiguous().view(torch.float32)
             local_kwargs["output_dtype"] = out_dtype
-        if n_recv:
-            partial = self.local_fn(recv_x, w1_local, w2_local, r_w, r_ids,
-                                    expert_map=self.expert_map,
-                                    global_num_experts=self.num_experts, **local_kwargs)
-        else:
-            partial = torch.empty((0, h), dtype=out_dtype, device=dev)
+        r_work = []
+        limit_sms = comm is not None and self.comm_sms > 0
+        if limit_sms:
+            from . import ops
+            ops.set_gemm_sm_reserve(self.comm_sms)   # leave SMs to the exchange kernels
+        try:
+            for c in range(chunks):
+                if d_work[c] is not None:
+                    d_work[c].wait()                 # main stream waits for chunk c's rows
+                rb = recv_bufs[c]
+                if n_recv[c]:
+                    r_x = rb[:, :row_bytes].view(x.dtype)
+                    r_ids = rb[:, o_ids:o_ids + 4 * k].view(torch.int32)
+                    r_w = rb[:, o_w:o_w + 4 * k].view(torch.float32)
+                    r_ids, r_w = r_ids.contiguous(), r_w.contiguous()
+                    if x_scale is None or not cuda:
+                        # 16-bit rows are quantised (or used) by kernels that read dense rows;
+                        # pre-quantised rows are gathered from the receive buffer in place
+                        r_x = r_x.contiguous()
+                    if x_scale is not None:
+                        local_kwargs["a1_scale"] = rb[:, o_scale:o_scale + 4 * groups].view(
+                            torch.float32)
+                    partial = self.local_fn(r_x, w1_local, w2_local, r_w, r_ids,
+                                            expert_map=self.expert_map,
+                                            global_num_experts=self.num_experts, **local_kwargs)
+                else:
+                    partial = torch.empty((0, h), dtype=out_dtype, device=dev)
+                r_work.append(exchange(back[first[c]:first[c] + n_send[c]], partial.contiguous(),
+                                       send_split[c], recv_split[c],
+                                       event() if comm is not None else None))
+        finally:
+            if limit_sms:
+                ops.set_gemm_sm_reserve(0)
         mark("experts")
-        back = torch.empty((tok_idx.numel(), h), dtype=out_dtype, device=dev)
-        dist.all_to_all_single(back, partial.contiguous(), send_split, recv_split,
-                               group=self.group)
+        for w in r_work:
+            if w is not None:
+                w.wait()
         mark("return")
         out = torch.empty((m, h), dtype=out_dtype, device=dev)
         self.combine_fn(back, pos, out)
         mark("combine")
-        self.last_stats = dict(rows_sent=int(sum(send_split)), rows_received=n_recv,
-                               routes=m * k)
+        if comm is not None:
+            comm.wait_stream(main)      # buffers handed to the exchange stream die in order
+        self.last_stats = dict(rows_sent=total_send, rows_received=sum(n_recv), routes=m * k,
+                               chunks=chunks)
         if marks:
             torch.cuda.synchronize()
             self.last_stats["ms"] = {b[0]: a[1].elapsed_time(b[1])
                                      for a, b in zip(marks[:-1], marks[1:])}
         return out
+
+    def _comm_stream(self, device):
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=device)
+        return self._comm

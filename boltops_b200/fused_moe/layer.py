@@ -207,7 +207,13 @@ def fused_experts_impl(
 
     assert hidden_states.shape[1] == w1.shape[2], "Hidden size mismatch"
     assert topk_weights.shape == topk_ids.shape, "topk shape mismatch"
-    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    # (rows of pre-quantised or 16-bit input may also sit inside wider records -- the
+    # expert-parallel layer hands over rows of its receive buffer in place -- as long as the
+    # last dimension is dense; everything else must be contiguous as in the reference)
+    assert hidden_states.is_contiguous() or (
+        hidden_states.dim() == 2 and hidden_states.stride(1) == 1
+        and (hidden_states.stride(0) * hidden_states.element_size()) % 16 == 0
+    ), "Hidden_states must be contiguous"
     assert w1.stride(-1) == 1, "Stride of last dimension must be 1"
     assert w2.stride(-1) == 1, "Stride of last dimension must be 1"
     assert hidden_states.dtype in (torch.float32, torch.float16, torch.bfloat16, torch.int8,
@@ -305,6 +311,8 @@ def fused_experts_impl(
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
         a_scale = None
+        if quantised and x.dtype in (torch.float16, torch.bfloat16) and not x.is_contiguous():
+            x = x.contiguous()                      # the quantisers read dense rows
         if quantised and block_mode and x.dtype in (torch.float16, torch.bfloat16):
             # quantise each token once and write it straight to its sorted rows
             with _Stage("quant_a1"):

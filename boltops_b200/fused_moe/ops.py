@@ -191,13 +191,19 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Te
     lib = _cabi.load()
     m, cols = src.shape
     row_bytes = cols * src.element_size()
+    # rows (and their scales) may sit inside wider records: only the last dimension must be dense
+    assert src.stride(1) == 1, "gather_rows: the last dimension of src must be contiguous"
+    src_stride = src.stride(0) * src.element_size() if m > 1 else row_bytes
     dst = torch.empty((capacity, cols), dtype=src.dtype, device=src.device)
     dst_scale = None
     groups = 0
     ld = 0
+    scale_stride = 0
     if src_scale is not None:
-        src_scale = src_scale.reshape(m, -1).contiguous()
+        if src_scale.dim() != 2 or src_scale.shape[0] != m or src_scale.stride(1) != 1:
+            src_scale = src_scale.reshape(m, -1).contiguous()
         groups = src_scale.shape[1]
+        scale_stride = src_scale.stride(0) if m > 1 else groups
         if groups == 1:
             dst_scale = torch.empty(capacity, dtype=torch.float32, device=src.device)
             ld = capacity
@@ -205,9 +211,9 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Te
             dst_scale = torch.empty((groups, capacity), dtype=torch.float32, device=src.device)
             ld = capacity
     with torch.cuda.device(src.device):
-        check(lib.bolt_gather_rows(ptr(src), m, row_bytes, ptr(src_scale), groups,
-                                   ptr(sorted_ids), ptr(num_valid), capacity, ptr(dst),
-                                   ptr(dst_scale), ld, stream_of(src)))
+        check(lib.bolt_gather_rows(ptr(src), m, row_bytes, src_stride, ptr(src_scale),
+                                   scale_stride, groups, ptr(sorted_ids), ptr(num_valid),
+                                   capacity, ptr(dst), ptr(dst_scale), ld, stream_of(src)))
     _count()
     return dst, dst_scale
 
@@ -333,8 +339,9 @@ def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
 
 
 def ep_dest_ranks(topk_ids: torch.Tensor, num_experts: int, experts_per_rank: int,
-                  world: int) -> torch.Tensor:
-    """``routes[t, r] = r`` if one of token t's experts lives on rank r, else -1 (int32 [M, world])."""
+                  world: int, chunk_tokens: int = 0) -> torch.Tensor:
+    """``routes[t, r] = r`` if one of token t's experts lives on rank r, else -1 (int32 [M, world]);
+    with ``chunk_tokens`` the value is ``(t // chunk_tokens) * world + r``."""
     _require_cuda(topk_ids)
     lib = _cabi.load()
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
@@ -343,15 +350,53 @@ def ep_dest_ranks(topk_ids: torch.Tensor, num_experts: int, experts_per_rank: in
     routes = torch.empty((m, world), dtype=torch.int32, device=ids.device)
     with torch.cuda.device(ids.device):
         check(lib.bolt_ep_dest_ranks(ptr(ids), m, k, num_experts, experts_per_rank, world,
-                                     ptr(routes), stream_of(ids)))
+                                     chunk_tokens, ptr(routes), stream_of(ids)))
     _count()
     return routes
+
+
+def ep_wire_row_bytes(row_bytes: int, groups: int, topk: int) -> int:
+    """Bytes of one expert-parallel wire row: data, scales, top-k ids, top-k weights (each part
+    padded to 16 bytes)."""
+    return int(_cabi.load().bolt_ep_wire_row_bytes(row_bytes, groups, topk))
+
+
+def ep_pack_rows(data: torch.Tensor, scales: Optional[torch.Tensor], topk_ids: torch.Tensor,
+                 topk_weights: torch.Tensor, send_ids: torch.Tensor, first: int, rows: int,
+                 out: torch.Tensor) -> None:
+    """Fill ``out[:rows]`` (uint8 ``[*, wire_row_bytes]``) with the wire rows of the tokens
+    ``send_ids[first:first+rows] & 0xFFFFFF``: one kernel for the send buffer of a chunk."""
+    _require_cuda(data, scales, topk_ids, topk_weights, send_ids, out)
+    lib = _cabi.load()
+    assert data.is_contiguous() and topk_ids.is_contiguous() and topk_weights.is_contiguous()
+    assert topk_ids.dtype == torch.int32 and topk_weights.dtype == torch.float32
+    assert out.dtype == torch.uint8 and out.stride(1) == 1
+    groups = 0
+    if scales is not None:
+        scales = scales.reshape(data.shape[0], -1).contiguous()
+        groups = scales.shape[1]
+    with torch.cuda.device(data.device):
+        check(lib.bolt_ep_pack_rows(ptr(data), data.shape[1] * data.element_size(), ptr(scales),
+                                    groups, ptr(topk_ids), ptr(topk_weights), topk_ids.shape[1],
+                                    ptr(send_ids), first, rows, ptr(out), out.stride(0),
+                                    stream_of(data)))
+    _count()
 
 
 # ---------------------------------------------------------------------------
 # grouped GEMM
 # ---------------------------------------------------------------------------
 _status_words = {}
+_gemm_sm_reserve = 0
+
+
+def set_gemm_sm_reserve(sms: int) -> None:
+    """Number of SMs the grouped GEMMs leave free (0 = none).  The expert-parallel layer sets it
+    while exchange kernels run next to the GEMMs: a persistent GEMM with one CTA on every SM would
+    make a concurrently launched collective wait for it."""
+    global _gemm_sm_reserve
+    _gemm_sm_reserve = max(int(sms), 0)
+
 
 
 def device_status(device: torch.device) -> torch.Tensor:
@@ -414,6 +459,9 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
     args.sorted_expert_ids = ptr(sorted_expert_ids)
     args.num_valid_ids = ptr(num_valid)
     args.status = ptr(device_status(a.device))
+    if sm_count == 0 and _gemm_sm_reserve > 0:
+        total = torch.cuda.get_device_properties(a.device).multi_processor_count
+        sm_count = max(total - _gemm_sm_reserve, 1)
     args.sm_count = sm_count
     args.act_alpha = float(act_alpha)
     args.act_beta = float(act_beta)

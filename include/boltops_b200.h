@@ -202,10 +202,28 @@ int bolt_moe_fused_gate(const void* gating, int dtype, const float* bias, int64_
  * boltops/fused_moe/__init__.py:127-133).  routes[t][r] = r when one of token t's experts
  * lives on rank r (experts sharded contiguously, experts_per_rank each), else -1; ids outside
  * [0, num_experts) hit no rank.  Sorting these routes with bolt_moe_sort_ck (ranks as experts,
- * unit 1) yields the send order, the per-rank counts and the inverse permutation.
+ * unit 1) yields the send order, the per-rank counts and the inverse permutation.  With
+ * chunk_tokens > 0 the value is (t / chunk_tokens) * world + r, so the same sort orders the
+ * rows by (token chunk, rank, token) for a dispatch that is pipelined chunk by chunk.
  */
 int bolt_ep_dest_ranks(const int32_t* topk_ids, int64_t num_tokens, int topk, int num_experts,
-                       int experts_per_rank, int world, int32_t* routes, void* stream);
+                       int experts_per_rank, int world, int64_t chunk_tokens, int32_t* routes,
+                       void* stream);
+
+/* Expert-parallel wire format (no reference counterpart).  One row per (token, destination
+ * rank): [row data | fp32 scales of the row | top-k ids | top-k weights], each part padded to a
+ * multiple of 16 bytes; bolt_ep_wire_row_bytes gives the row size.  bolt_ep_pack_rows fills
+ * rows [0, rows) of `out` from the tokens send_ids[first + i] & 0xFFFFFF (send_ids = the sorted
+ * ids of the dispatch sort), so the whole send buffer of a chunk is written by one kernel and
+ * travels in one all-to-all.  The receiver reads the parts in place (bolt_gather_rows takes a
+ * source row stride).  data: [tokens, row_bytes] (quantised codes or 16-bit rows), scales:
+ * [tokens, groups] or NULL with groups = 0.
+ */
+int64_t bolt_ep_wire_row_bytes(int row_bytes, int groups, int topk);
+int bolt_ep_pack_rows(const void* data, int row_bytes, const float* scales, int groups,
+                      const int32_t* topk_ids, const float* topk_weights, int topk,
+                      const int32_t* send_ids, int64_t first, int64_t rows, void* out,
+                      int64_t out_stride, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Dynamic activation quantisation.
@@ -227,13 +245,15 @@ int bolt_quant_rows(const void* x, int x_dtype, int64_t rows, int cols, int grou
  *   If src_scale != NULL, scales are gathered too:
  *     groups > 1 : dst_scale[g * dst_scale_ld + i] = src_scale[token*groups + g]
  *     groups == 1: dst_scale[i] = src_scale[token]
+ *   src_stride_bytes / src_scale_stride: distance between source rows in bytes / in floats
+ *   (0 = dense rows), so rows and scales can be read in place from a wider record.
  * No counterpart in the reference (its GEMM gathers rows through pointer
  * arithmetic, boltops/fused_moe/triton/moe_op.py:1479,1611-1615).
  */
-int bolt_gather_rows(const void* src, int num_tokens, int row_bytes,
-                     const float* src_scale, int groups, const int32_t* sorted_ids,
-                     const int32_t* num_valid_ids, int capacity, void* dst,
-                     float* dst_scale, int64_t dst_scale_ld, void* stream);
+int bolt_gather_rows(const void* src, int num_tokens, int row_bytes, int64_t src_stride_bytes,
+                     const float* src_scale, int64_t src_scale_stride, int groups,
+                     const int32_t* sorted_ids, const int32_t* num_valid_ids, int capacity,
+                     void* dst, float* dst_scale, int64_t dst_scale_ld, void* stream);
 
 /* bolt_quant_rows and bolt_gather_rows in one pass for 1 x group quantisation (group a
  * multiple of the 16-byte input vector, at most 256 vectors: 128-wide blocks as well as whole

@@ -37,7 +37,7 @@ def _cpu_gather_sum(src, pos, out):
     return out
 
 
-def _worker(rank, world, port, E, K, H, I, M, zipf, ret):
+def _worker(rank, world, port, E, K, H, I, M, zipf, ret, chunks=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -54,12 +54,21 @@ def _worker(rank, world, port, E, K, H, I, M, zipf, ret):
             ids[0, 0] = -1                                   # an out-of-range id is ignored
         ep = ExpertParallelMoE(dist.group.WORLD, E, "cpu", local_fn=_local_oracle,
                                combine_fn=_cpu_gather_sum)
+        if chunks > 1:                                       # the pipelined exchange, in chunks
+            ep.pipeline_chunks, ep.pipeline_min_tokens = chunks, 0
+            if rank == world - 1:
+                ids[:] = ids % (E // world)                  # this rank sends to rank 0 only ...
+            else:
+                ids[:] = ids % (E - E // world)              # ... and nobody sends to the last rank
         out = ep.forward(hidden, w1[rank * per:(rank + 1) * per], w2[rank * per:(rank + 1) * per],
                          wts, ids)
         expect = O.moe_bf16(hidden, w1, w2, wts, ids)
         err = O.rel_l2(out, expect)
         stats = ep.last_stats
         assert stats["rows_sent"] <= stats["routes"]
+        assert stats["chunks"] == min(chunks, M)
+        if chunks > 1 and rank == world - 1:
+            assert stats["rows_received"] == 0               # a rank without any work
         ret[rank] = (err, stats["rows_sent"], stats["routes"])
     finally:
         dist.destroy_process_group()
@@ -76,6 +85,31 @@ def test_ep_dispatch_combine_matches_single_rank(world, E, K, zipf):
         err, sent, routes = ret[rank]
         assert err <= 1e-2, f"rank {rank}: rel-L2 {err}"
         assert 0 < sent <= routes
+
+
+@pytest.mark.parametrize("world,chunks,M", [(2, 2, 37), (4, 3, 50), (2, 4, 3)])
+def test_ep_chunked_exchange_matches_single_rank(world, chunks, M):
+    """Token chunks of the pipelined exchange: ragged last chunk (37 = 19 + 18, 50 = 17 + 17 +
+    16), more chunks than tokens allow (3 tokens, 4 chunks), a rank that receives nothing."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), 4 * world, 2, 64, 32, M, None, ret, chunks),
+             nprocs=world, join=True)
+    assert len(ret) == world
+    for rank in range(world):
+        err, sent, routes = ret[rank]
+        assert err <= 1e-2, f"rank {rank}: rel-L2 {err}"
+
+
+def test_ep_chunked_plan_orders_by_chunk_rank_token():
+    from boltops_b200.fused_moe.ep import ExpertParallelMoE
+    ep = ExpertParallelMoE.__new__(ExpertParallelMoE)
+    ep.world, ep.rank, ep.num_experts, ep.per_rank = 2, 0, 4, 2
+    ids = torch.tensor([[0, 3], [2, 3], [1, 0], [0, 2]], dtype=torch.int32)
+    tok, counts, pos = ep.plan(ids, chunks=2)                # chunks: tokens {0,1} and {2,3}
+    assert counts.tolist() == [1, 2, 2, 1]                   # (c0,r0) (c0,r1) (c1,r0) (c1,r1)
+    assert tok.tolist() == [0, 0, 1, 2, 3, 3]
+    assert pos.tolist() == [[0, 1], [-1, 2], [3, -1], [4, 5]]
 
 
 def _replicated_worker(rank, world, port, ret):

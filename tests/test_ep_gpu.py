@@ -42,6 +42,14 @@ def _worker(rank, world, port, ret):
         full = fused_experts(hidden.to(dev), fw1, fw2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
                              w1_scale=fw1s, w2_scale=fw2s, block_shape=[128, 128])
         torch.cuda.synchronize()
+        # pipelined exchange in three token chunks on a second stream: same result
+        ep.pipeline_chunks, ep.pipeline_min_tokens = 3, 0
+        piped = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
+                           w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+        torch.cuda.synchronize()
+        assert ep.last_stats["chunks"] == 3
+        assert torch.equal(piped, out), "chunked exchange changed the result"
+        ep.pipeline_chunks = 1
         # small-batch path: replicated tokens + reduce-scatter instead of the dispatch
         ep.replicate_below = 4096
         rep = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
