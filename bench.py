@@ -42,6 +42,8 @@ WORKLOADS = {
                                       zipf=1.2),
     # the DeepSeek-V3 shape in the native-MXFP8 recipe (E8M0 scale bytes per 32 K elements)
     "deepseek_v3_mxfp8": dict(kind="mxfp8", E=256, K=8, H=7168, I=2048, M=4096),
+    # ... and in the MXFP4 (w4a8) recipe: packed e2m1 weights, dynamic 1 x 128 activation groups
+    "deepseek_v3_mxfp4": dict(kind="mxfp4", E=256, K=8, H=7168, I=2048, M=4096),
 }
 DEFAULT_WORKLOAD = "deepseek_v3_fp8_block"
 
@@ -164,6 +166,19 @@ def _quant_mx(w):
     return q, e.to(torch.uint8)
 
 
+def _quant_mxfp4(w):
+    """1 x 32 groups, exponent byte = ceil(log2(amax/6)) + 127, e2m1 codes (nearest of
+    0, .5, 1, 1.5, 2, 3, 4, 6), two codes per byte, low nibble first."""
+    n, k = w.shape
+    v = w.float().reshape(n, k // 32, 32)
+    amax = v.abs().amax(-1).clamp_min(torch.finfo(torch.float32).tiny)
+    e = (torch.ceil(torch.log2(amax / 6.0)) + 127).clamp(0, 254)
+    y = (v * torch.exp2(127 - e)[..., None]).reshape(n, k)
+    lut = torch.tensor([0., .5, 1., 1.5, 2., 3., 4., 6.], device=w.device)
+    code = (y.abs()[..., None] - lut).abs().argmin(-1).to(torch.uint8) | ((y < 0).to(torch.uint8) << 3)
+    return code[:, 0::2] | (code[:, 1::2] << 4), e.to(torch.uint8)
+
+
 def _quant_channel_int8(w):
     amax = w.float().abs().amax(dim=-1, keepdim=True).clamp(min=1e-10)
     s = amax / 127.0
@@ -189,6 +204,11 @@ def make_weights(cfg, device, experts, seed):
         w2 = torch.empty(n, H, I, dtype=FP8, device=device)
         w1s = torch.empty(n, 2 * I, H // 32, dtype=torch.uint8, device=device)
         w2s = torch.empty(n, H, I // 32, dtype=torch.uint8, device=device)
+    elif kind == "mxfp4":
+        w1 = torch.empty(n, 2 * I, H // 2, dtype=torch.uint8, device=device)
+        w2 = torch.empty(n, H, I // 2, dtype=torch.uint8, device=device)
+        w1s = torch.empty(n, 2 * I, H // 32, dtype=torch.uint8, device=device)
+        w2s = torch.empty(n, H, I // 32, dtype=torch.uint8, device=device)
     else:
         w1 = torch.empty(n, 2 * I, H, dtype=torch.int8, device=device)
         w2 = torch.empty(n, H, I, dtype=torch.int8, device=device)
@@ -207,6 +227,9 @@ def make_weights(cfg, device, experts, seed):
         elif kind == "mxfp8":
             w1[j], w1s[j] = _quant_mx(m1)
             w2[j], w2s[j] = _quant_mx(m2)
+        elif kind == "mxfp4":
+            w1[j], w1s[j] = _quant_mxfp4(m1)
+            w2[j], w2s[j] = _quant_mxfp4(m2)
         else:
             w1[j], w1s[j] = _quant_channel_int8(m1)
             w2[j], w2s[j] = _quant_channel_int8(m2)
@@ -248,6 +271,9 @@ def layer_kwargs(cfg, w1s, w2s):
         return dict(use_int8_w8a8=True, per_channel_quant=True, w1_scale=w1s, w2_scale=w2s)
     if cfg["kind"] == "mxfp8":
         return dict(use_mxfp8=True, w1_scale=w1s, w2_scale=w2s, block_shape=[1, 32])
+    if cfg["kind"] == "mxfp4":
+        return dict(use_mxfp4_w4a8=True, use_ue8m0=True, w1_scale=w1s, w2_scale=w2s,
+                    block_shape=[1, 32])
     return {}
 
 
@@ -355,8 +381,8 @@ def gemm1_algorithmic(cfg, m, active_experts):
     """Algorithmic bytes and flops of one GEMM1 launch (gate/up GEMM + fused epilogue)."""
     K, H, I = cfg["K"], cfg["H"], cfg["I"]
     routes = m * K
-    wb = 2 if cfg["kind"] == "bf16" else 1
-    ab = 2 if cfg["kind"] == "bf16" else 1
+    wb = 2 if cfg["kind"] == "bf16" else (0.5 if cfg["kind"] == "mxfp4" else 1)
+    ab = 2 if cfg["kind"] in ("bf16", "mxfp4") else 1     # mxfp4: decoded 16-bit operands
     ob = 1 if cfg["kind"] in ("fp8_block", "mxfp8") else 2
     byts = active_experts * 2 * I * H * wb + routes * H * ab + routes * I * ob
     if cfg["kind"] == "fp8_block":
@@ -364,7 +390,9 @@ def gemm1_algorithmic(cfg, m, active_experts):
             + routes * (I // 128) * 4
     if cfg["kind"] == "mxfp8":    # one scale byte per 32 elements of weights, inputs and outputs
         byts += active_experts * 2 * I * (H // 32) + routes * (H // 32) + routes * (I // 32)
-    return byts, 4.0 * routes * H * I
+    if cfg["kind"] == "mxfp4":    # what the kernels stream today: weights decoded to 16 bits
+        byts = active_experts * 2 * I * H * 2 + routes * H * 2 + routes * 2 * I * 2
+    return int(byts), 4.0 * routes * H * I
 
 
 def layer_flops(cfg, m):
@@ -388,13 +416,14 @@ def cpu_reference(cfg, m, seed, budget_experts=None):
     if budget_experts is None:
         budget_experts = int(max(1, min(E, 15.0 * cores * 25e9 / max(per_expert_flops, 1.0))))
         budget_experts = max(1, min(budget_experts, 32 if cfg["kind"] != "bf16" else E))
-        if cfg["kind"] == "mxfp8":      # the oracle holds fp32 copies of the sampled experts
+        if cfg["kind"] in ("mxfp8", "mxfp4"):   # the oracle holds fp32 copies of the sampled experts
             budget_experts = min(budget_experts, 8)
     es = budget_experts
     hidden, wts, ids = make_tokens(cfg, m, seed)
     w1, w2, w1s, w2s = make_weights(cfg, "cpu", list(range(es)), seed)
     emap = torch.full((E,), -1, dtype=torch.int32)
     emap[:es] = torch.arange(es, dtype=torch.int32)
+    tok_sample = m
     t0 = time.perf_counter()
     if cfg["kind"] == "fp8_block":
         O.moe_block_fp8(hidden, w1, w2, w1s, w2s, wts, ids, (128, 128), expert_map=emap)
@@ -402,13 +431,19 @@ def cpu_reference(cfg, m, seed, budget_experts=None):
         O.moe_per_channel(hidden, w1, w2, w1s, w2s, wts, ids, torch.int8, expert_map=emap)
     elif cfg["kind"] == "mxfp8":
         O.moe_mxfp8(hidden, w1, w2, w1s, w2s, wts, ids, expert_map=emap)
+    elif cfg["kind"] == "mxfp4":
+        # (this oracle walks the routes one by one: a token sample bounds its time)
+        tok_sample = min(m, 512)
+        O.moe_mxfp4(hidden[:tok_sample], w1, w2, w1s, w2s, wts[:tok_sample], ids[:tok_sample],
+                    expert_map=emap)
     else:
         sel_ids = torch.where(ids < es, ids, torch.full_like(ids, -1))
         O.moe_bf16(hidden, w1, w2, wts, sel_ids)
     dt = time.perf_counter() - t0
-    full = dt * E / es
-    sample = (f"oracle port of the reference torch path on {es} of {E} experts of the "
-              f"M={m} batch ({dt:.1f} s), scaled by {E}/{es}")
+    full = dt * E / es * (m / tok_sample)
+    sample = (f"oracle port of the reference torch path on {es} of {E} experts of "
+              + (f"the M={m} batch" if tok_sample == m else f"{tok_sample} tokens of the M={m} batch")
+              + f" ({dt:.1f} s), scaled by {E}/{es}" + ("" if tok_sample == m else f" x {m}/{tok_sample}"))
     return m / full, cores, sample, full
 
 
@@ -431,6 +466,8 @@ def spot_check(cfg, out, hidden_h, wts_h, ids_h, device, seed, tokens=4):
         expect, tol = O.moe_per_channel(h, w1, w2, w1s, w2s, w, loc, torch.int8), 2e-2
     elif cfg["kind"] == "mxfp8":
         expect, tol = O.moe_mxfp8(h, w1, w2, w1s, w2s, w, loc), 2e-2
+    elif cfg["kind"] == "mxfp4":
+        expect, tol = O.moe_mxfp4(h, w1, w2, w1s, w2s, w, loc), 2e-2
     else:
         expect, tol = O.moe_bf16(h, w1, w2, w, loc), 1e-2
     torch.cuda.synchronize()
@@ -481,7 +518,7 @@ def main():
                   parallelism=f"ep{world}" if world > 1 else "single",
                   l2="inputs larger than L2 (weights stream from HBM every step)")
     dtype = {"bf16": "bf16", "fp8_block": "fp8_e4m3", "int8_channel": "int8",
-             "mxfp8": "mxfp8_e4m3"}[cfg["kind"]]
+             "mxfp8": "mxfp8_e4m3", "mxfp4": "mxfp4_e2m1_x_e4m3"}[cfg["kind"]]
 
     if args.impl == "reference":
         if rank != 0:
@@ -540,6 +577,7 @@ def main():
         ep.replicate_below = 4096
         ep.pipeline_chunks = args.ep_chunks
         ep.comm_sms = args.ep_comm_sms
+        ep.topk_hint = cfg["K"]
         config["ep_chunks"] = ep.num_chunks(m)
         config["ep_comm_sms"] = args.ep_comm_sms
 

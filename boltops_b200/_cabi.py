@@ -101,6 +101,19 @@ _SIGNATURES = {
                                        C.c_int, C.c_void_p]),
     "bolt_mx_sf_layout": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
                                     C.c_void_p, C.c_void_p]),
+    "bolt_mxfp4_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p,
+                                    C.c_int, C.c_void_p]),
+    "bolt_mx4_act_quant": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
+                                     C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                     C.c_void_p, C.c_void_p, C.c_void_p]),
+    "bolt_fp8_group_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+                                        C.c_void_p, C.c_int, C.c_void_p]),
+    "bolt_mx4_swiglu_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                         C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_float,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "bolt_mx4_affine_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "bolt_gather_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_int64,
                                    C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
                                    C.c_void_p, C.c_int64, C.c_void_p]),

@@ -68,6 +68,8 @@ class ExpertParallelMoE:
         # to the exchange kernels (a persistent GEMM on every SM would keep them waiting).
         self.pipeline_chunks = 2
         self.pipeline_min_tokens = 1024
+        self.pipeline_rows_per_expert = 384   # expected rows per local expert and chunk, at least
+        self.topk_hint = 0                    # set by forward() from topk_ids
         self.comm_sms = 16
         self._comm = None
 
@@ -212,7 +214,13 @@ class ExpertParallelMoE:
         i-1 travels back while chunk i is computed."""
         if self.pipeline_chunks <= 1 or m < self.pipeline_min_tokens:
             return 1
-        return max(1, min(self.pipeline_chunks, 255 // self.world, m))
+        chunks = min(self.pipeline_chunks, 255 // self.world, m)
+        if self.pipeline_rows_per_expert > 0 and self.topk_hint > 0:
+            # every chunk streams the local expert weights once more, which only pays while the
+            # GEMMs are bound by the tensor cores: keep enough rows per local expert per chunk
+            rows = m * self.topk_hint * self.world // self.num_experts
+            chunks = min(chunks, rows // self.pipeline_rows_per_expert)
+        return max(1, chunks)
 
     def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
         m, h = hidden_states.shape
@@ -224,6 +232,7 @@ class ExpertParallelMoE:
         world = self.world
         dev = hidden_states.device
         cuda = hidden_states.is_cuda
+        self.topk_hint = k
         chunks = self.num_chunks(m)
         marks = []
 

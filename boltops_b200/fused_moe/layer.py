@@ -166,10 +166,24 @@ def fused_experts_impl(
             raise ValueError(f"{name} cannot be combined with other quantization flags")
         if use_mxfp8 and use_mxfp4_w4a8:
             raise ValueError("MXFP8 and MXFP4 are mutually exclusive")
-        if use_mxfp4_w4a8:
-            raise NotImplementedError("MXFP4 experts are not built in boltops_b200")
-        from . import mxfp8
         activation, is_gated = normalize_moe_activation(activation, is_gated)
+        if use_mxfp4_w4a8:
+            from . import mxfp4
+            static = mxfp4.validate(hidden_states, w1, w2, topk_ids, w1_scale, w2_scale, a1_scale,
+                                    a2_scale, b1, b2, apply_router_weight_on_input, output_dtype,
+                                    block_shape, activation, is_gated, inplace, no_combine,
+                                    gemm1_alpha, gemm1_beta)
+            return mxfp4.fused_experts_mxfp4(
+                hidden_states, w1, w2, topk_weights, topk_ids, w1_scale=w1_scale,
+                w2_scale=w2_scale, a1_scale=a1_scale, a2_scale=a2_scale, b1=b1, b2=b2,
+                static=static, activation=activation, output_dtype=output_dtype, inplace=inplace,
+                no_combine=no_combine, apply_router_weight_on_input=apply_router_weight_on_input,
+                global_num_experts=global_num_experts, expert_map=expert_map,
+                routed_scaling_factor=1.0 if routed_scaling_factor is None else routed_scaling_factor,
+                gemm1_alpha=gemm1_alpha, gemm1_limit=gemm1_limit,
+                activation_situ_beta=activation_situ_beta,
+                activation_situ_linear_beta=activation_situ_linear_beta, chunk=_chunk_size())
+        from . import mxfp8
         mxfp8.validate(hidden_states, w1, w2, w1_scale, w2_scale, a1_scale, a2_scale, b1, b2,
                        apply_router_weight_on_input, output_dtype, block_shape, activation,
                        is_gated, inplace, no_combine)

@@ -185,6 +185,8 @@ def fused_experts_mxfp8(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
                 ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
                 alloc_moe_buf=False, route_pos=route_pos)
+        if expert_map is not None:
+            expert_ids = ops.relabel_tiles(expert_ids, expert_map)
         cap = sorted_ids.shape[0]
         common = dict(kind=kind, sorted_expert_ids=expert_ids, num_valid=num_valid,
                       sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)

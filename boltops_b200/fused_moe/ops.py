@@ -108,6 +108,20 @@ def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_exper
     return sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf
 
 
+def relabel_tiles(sorted_expert_ids: torch.Tensor, expert_map: torch.Tensor) -> torch.Tensor:
+    """Per-tile expert ids of a masked CK sort -> local expert ids under an ARBITRARY
+    ``expert_map``.  The masked sort numbers the enabled experts densely in ascending global
+    order; a map such as ``[1, -1, 0]`` (the MX paths of the reference take any map, through
+    ``moe_align_block_size``: boltops/fused_moe/triton/fused_moe.py:1116-1117,436-437) stores
+    them in another order.  Entries of tiles beyond the padded total are arbitrary and stay
+    harmless (clamped before the look-up).  No host synchronisation."""
+    emap = expert_map.to(torch.int32)
+    order = torch.argsort((emap < 0).to(torch.int8), stable=True)      # enabled experts first
+    local_of_label = emap[order]
+    idx = sorted_expert_ids.clamp(0, emap.numel() - 1).long()
+    return local_of_label[idx].contiguous()
+
+
 def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int,
                          expert_map: Optional[torch.Tensor] = None
                          ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:

@@ -340,6 +340,46 @@ int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* ou
                         int64_t num_tokens, int slots, int n, float scale, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * MXFP4 (w4a8) experts.  Replace the element-wise parts of fused_experts_mxfp_impl with
+ * use_mxfp4_w4a8 (boltops/fused_moe/triton/fused_moe.py:923-1197): weight decoding
+ * (boltops/fused_moe/triton/mxfp4.py:61-157 reads packed e2m1 nibbles, low nibble first, with
+ * one E8M0 byte per 32 K elements), the activation quantisers
+ * (per_token_group_quant_fp8_mxfp4 and silu_mul_quant_fp8_packed_triton,
+ * boltops/fused_moe/triton/mxfp4_quant.py:38-80,206-317; static_per_tensor_quant_fp8_i8,
+ * boltops/fused_moe/triton/quant.py:33-82) and the fused epilogues of the static recipe
+ * (moe_gemm_mxfp4 with fuse_swiglu / quant_scale / bias, mxfp4.py:194-286).  The contractions
+ * themselves run through bolt_grouped_gemm on decoded operands (exact, see csrc/mxfp4.cu).
+ *
+ * bolt_mxfp4_decode: packed [rows, cols/2] + scales [rows, cols/32] -> out [rows, cols].
+ * bolt_mx4_act_quant: x [rows, cols] (or [rows, 2*cols] = [gate | up] with gated != 0: SiLU(gate)
+ *   * up, optional clamp, rounded through bf16) -> e4m3 per 1 x 128 group with the power-of-two
+ *   scale at or above max(amax, 1e-10)/448 (mode 0) or with *static_scale (mode 1; e4m3 input is
+ *   taken as already quantised); deq (decoded values), codes, scales [rows, cols/128] optional.
+ * bolt_fp8_group_decode: codes [rows, cols] * scales [rows, cols/group] -> out.
+ * bolt_mx4_swiglu_static: g1 fp32 [capacity, 2*inter] in sorted rows -> decoded e4m3 of
+ *   swigluoai(g1 * a1_scale + bias[expert]) [* row_weight] / a2_scale, [capacity, inter].
+ * bolt_mx4_affine_rows: out = cast((g2 * scale + bias[expert]) [* row_weight]) for the live
+ *   rows; scatter != 0 writes row i to token * topk + slot.
+ */
+int bolt_mxfp4_decode(const uint8_t* packed, const uint8_t* scales, int64_t rows, int cols,
+                      void* out, int out_dtype, void* stream);
+int bolt_mx4_act_quant(const void* x, int x_dtype, int64_t rows, int cols, int gated,
+                       int has_limit, float limit, int mode, const float* static_scale, void* deq,
+                       int deq_dtype, uint8_t* codes, float* scales, void* stream);
+int bolt_fp8_group_decode(const uint8_t* codes, const float* scales, int64_t rows, int cols,
+                          int group, void* out, int out_dtype, void* stream);
+int bolt_mx4_swiglu_static(const float* g1, const int32_t* sorted_expert_ids,
+                           const int32_t* num_valid_ids, int capacity, int inter, int num_experts,
+                           const float* a1_scale, const float* bias, float alpha, float limit,
+                           const float* row_weight, const float* a2_scale, void* out,
+                           int out_dtype, void* stream);
+int bolt_mx4_affine_rows(const float* g2, const int32_t* sorted_expert_ids,
+                         const int32_t* sorted_ids, const int32_t* num_valid_ids, int capacity,
+                         int cols, int num_experts, int num_tokens, int topk, const float* scale,
+                         const float* bias, const float* row_weight, int scatter, void* out,
+                         int out_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Grouped expert GEMM (tcgen05 / TMEM / TMA, persistent).
  * Replaces moe_op.fused_moe + fused_moe_kernel
  * (boltops/fused_moe/triton/moe_op.py:2846-3417, 1294-1914) for the bf16/f16,

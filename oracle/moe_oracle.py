@@ -556,6 +556,117 @@ def moe_mxfp8(x, w1, w2, s1, s2, topk_weights, topk_ids, *, expert_map=None, act
     return (expected if no_combine else expected.sum(1)).to(x.dtype)
 
 
+# ---------------------------------------------------------------------------
+# MXFP4 (w4a8): packed e2m1 weights with E8M0 bytes per 32 K elements, e4m3 activations
+# ---------------------------------------------------------------------------
+def mxfp4_decode(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """Packed e2m1 codes (low nibble first) with one E8M0 byte per 32 values -> fp32
+    (test/fused_moe/test_fused_moe.py:1441-1445 `_decode_mxfp4_reference`)."""
+    codes = torch.stack((packed & 15, packed >> 4), -1).flatten(-2).long()
+    lut = torch.tensor([0., .5, 1., 1.5, 2., 3., 4., 6.])
+    values = lut[codes & 7] * torch.where(codes & 8 != 0, -1., 1.)
+    return values * torch.exp2(scales.float() - 127).repeat_interleave(32, -1)
+
+
+def mxfp4_quant_g128(x: torch.Tensor):
+    """Dynamic 1 x 128 activation quantisation of the MXFP4 recipe: scale = the power of two
+    at or above max(amax, 1e-10) / 448 (itself floored at 1e-10), q = e4m3(clamp(x / scale)).
+    Returns (codes, fp32 scales [rows, K/128], dequantised values)
+    (test/fused_moe/test_fused_moe.py:1424-1438 `_quantize_mxfp4_reference`, group 128;
+    kernel: boltops/fused_moe/triton/mxfp4_quant.py:48-54)."""
+    groups = x.float().reshape(x.shape[0], -1, 128)
+    amax = groups.abs().amax(-1)
+    raw = (amax.clamp_min(1.e-10) / 448).clamp_min(1.e-10)
+    bits = raw.contiguous().view(torch.int32)
+    exponent = ((bits >> 23) & 255) + ((bits & 0x7fffff) != 0).int()
+    scale = (exponent << 23).view(torch.float32)
+    q = (groups / scale[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    deq = (q.float() * scale[..., None]).reshape(x.shape)
+    return q.reshape(x.shape), scale, deq
+
+
+def _gemm_k32(a: torch.Tensor, w: torch.Tensor, dtype) -> torch.Tensor:
+    """fp32 accumulation in K chunks of 32, one output conversion
+    (test/fused_moe/test_fused_moe.py:1448-1453 `_mxfp4_reference_gemm`)."""
+    result = torch.zeros(a.shape[0], w.shape[0])
+    for k in range(0, a.shape[-1], 32):
+        result += a[:, k:k + 32] @ w[:, k:k + 32].T
+    return result.to(dtype)
+
+
+def moe_mxfp4(x, w1, w2, s1, s2, topk_weights, topk_ids, *, activation="silu", expert_map=None,
+              a1_scale=None, a2_scale=None, b1=None, b2=None, alpha=None, limit=None,
+              apply_router_weight_on_input=False, no_combine=False, routed_scaling_factor=1.0):
+    """The reference's CPU statement of the MXFP4 layer
+    (test/fused_moe/test_fused_moe.py:1506-1563).  Dynamic recipe (a2_scale None): activations
+    quantised per 1 x 128 group with power-of-two scales, both GEMMs rounded to the input dtype,
+    router weights applied in the fp32 sum over the routes (or to the input when
+    apply_router_weight_on_input, top-1 only).  Static recipe (a1_scale / a2_scale one fp32 value
+    each): e4m3(x / a1_scale), GEMM1 * a1_scale (+ bias), SwiGLU-OAI with alpha and limit, times the
+    router weight when it is applied on the input, e4m3(act / a2_scale), GEMM2 * a2_scale
+    (+ bias), times the router weight otherwise; routes summed in fp32."""
+    static = a2_scale is not None
+    m, hidden = x.shape
+    topk = topk_ids.shape[1]
+    input_router = apply_router_weight_on_input
+    d1, d2 = mxfp4_decode(w1, s1), mxfp4_decode(w2, s2)
+    if static:
+        alpha = 1.702 if alpha is None else alpha
+        a = (x.float() / a1_scale).to(torch.float8_e4m3fn).float()
+    else:
+        prepared = x * topk_weights.to(x.dtype) if input_router else x
+        a = mxfp4_quant_g128(prepared)[2]
+    routes = []
+    for token in range(m):
+        for rank, ge in enumerate(topk_ids[token].tolist()):
+            expert = ge if expert_map is None else int(expert_map[ge])
+            if expert == -1:
+                routes.append(torch.zeros(w2.shape[1], dtype=x.dtype))
+                continue
+            g1 = _gemm_k32(a[token:token + 1], d1[expert], torch.float32 if static else x.dtype)
+            if static:
+                g1 = g1 * a1_scale
+                if b1 is not None:
+                    g1 = g1 + b1[expert]
+            gate, up = g1.float().chunk(2, -1)
+            if static:
+                lim = 7. if limit is None else limit
+                gate, up = gate.clamp(max=lim), up.clamp(-lim, lim)
+                act = gate * torch.sigmoid(alpha * gate) * (up + 1.)
+                if input_router:
+                    act = act * topk_weights[token, rank]
+            elif activation == "situ":
+                act = (1.5 * torch.tanh(gate / 1.5) * torch.sigmoid(gate)
+                       * (2.0 * torch.tanh(up / 2.0)))
+            elif activation == "swiglustep":
+                act = (gate / (1 + torch.exp(-gate))).clamp(max=7.) * up.clamp(-7., 7.)
+            else:
+                if limit is not None:
+                    gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+                act = up * gate / (1 + torch.exp(-gate))
+            if not static:
+                act = act.bfloat16() if activation == "silu" else act.to(x.dtype)
+                qa = mxfp4_quant_g128(act)[2]
+            else:
+                qa = (act / a2_scale).to(torch.float8_e4m3fn).float()
+            g2 = _gemm_k32(qa, d2[expert], torch.float32 if static else x.dtype)[0]
+            if static:
+                g2 = g2 * a2_scale
+                if b2 is not None:
+                    g2 = g2 + b2[expert]
+                if not no_combine and not input_router:
+                    g2 = g2 * topk_weights[token, rank]
+            routes.append(g2.to(x.dtype))
+    route_output = torch.stack(routes).reshape(m, topk, w2.shape[1])
+    if no_combine:
+        return route_output
+    combined = torch.zeros(m, w2.shape[1])
+    for k in range(topk):
+        combined += route_output[:, k].float() * (
+            1. if input_router or static else topk_weights[:, k, None])
+    return (combined * routed_scaling_factor).to(x.dtype)
+
+
 def rel_l2(actual: torch.Tensor, expected: torch.Tensor) -> float:
     a = actual.double().flatten()
     e = expected.double().flatten()

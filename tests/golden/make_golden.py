@@ -74,6 +74,72 @@ def make_mxfp8(ref: Path) -> None:
     np.savez_compressed(HERE / "mxfp8.npz", **mx)
 
 
+MXFP4_CASES = (
+    "dense", "sparse_routing", "clamp_no_combine", "chunked", "prequantized_chunked",
+    "static", "static_bias", "static_clamp", "static_input_router",
+    "static_input_router_zero", "static_prequantized_chunked",
+    "static_expert_map_chunked", "static_no_combine", "static_input_router_no_combine",
+    "prequantized_g128_swiglustep", "prequantized_g128_situ",
+    "expert_map_chunked", "swiglustep", "situ",
+    "input_router", "input_router_chunked", "input_router_inplace",
+    "input_router_no_combine", "input_router_fp16",
+    "input_router_zero", "input_router_inplace_chunked",
+    "input_router_expert_map_chunked",
+)
+
+
+def make_mxfp4(ref: Path) -> None:
+    """MXFP4 (w4a8) layer: the CPU statement inside test_public_mxfp4_cpu_reference for every
+    case of its parametrisation (from `static = ...` down to the line that forms `expected`),
+    plus the pre-quantised inputs the test derives with its own quantiser.  The device half of
+    the test is not executed."""
+    path = ref / "test/fused_moe/test_fused_moe.py"
+    text = path.read_text().splitlines()
+    start = next(i for i, l in enumerate(text) if l.strip() == "static = case.startswith('static')")
+    stop = next(i for i in range(start, len(text))
+                if text[i].startswith("        expected = (combined * 1.25).to(x.dtype)"))
+    body = textwrap.dedent("\n".join(text[start:stop + 1]))
+    helpers = load_defs(path, ["_quantize_mxfp4_reference", "_decode_mxfp4_reference",
+                               "_mxfp4_reference_gemm"])
+
+    class _Env:                      # the test sets the chunk size through monkeypatch
+        def __init__(self):
+            self.env = {}
+
+        def setenv(self, k, v):
+            self.env[k] = v
+
+    out = {}
+    for case in MXFP4_CASES:
+        mp = _Env()
+        ns = dict(helpers)
+        ns.update(torch=torch, case=case, monkeypatch=mp)
+        exec(compile(body, "mxfp4_cpu_reference", "exec"), ns)
+        group = ns["group_size"]
+        q, qs = helpers["_quantize_mxfp4_reference"](ns["x"], return_scales=True, group_size=group)
+        if ns["static"]:
+            q = (ns["x"].float() / ns["static_s1"]).to(torch.float8_e4m3fn)
+            qs = ns["static_s1"]
+        rec = dict(x=ns["x"], w1=ns["w1"], w2=ns["w2"], s1=ns["s1"], s2=ns["s2"], ids=ns["ids"],
+                   weights=ns["weights"], expected=ns["expected"], input_q=q, input_scale=qs,
+                   static_s1=ns["static_s1"], static_s2=ns["static_s2"],
+                   alpha=torch.tensor(float(ns["alpha"])),
+                   clamp=torch.tensor(float("nan") if ns["clamp"] is None else float(ns["clamp"])),
+                   chunk=torch.tensor(int(mp.env.get("TRITON_FUSED_MOE_CHUNK_SIZE", 0))))
+        for name in ("expert_map", "bias1", "bias2"):
+            if ns.get(name) is not None:
+                rec[name] = ns[name]
+        for name, v in rec.items():
+            if v.dtype == torch.float8_e4m3fn:
+                v = v.view(torch.uint8)
+            key = f"{case}__{name}"
+            if v.dtype == torch.float16:
+                out[key + "__f16"] = v.numpy()
+            else:
+                out[key] = t2n(v)
+    np.savez_compressed(HERE / "mxfp4.npz", **out)
+
+
 def make_signatures(ref: Path) -> None:
     """Parameter lists of the public functions (name, kind, default as source text), read from
     the reference's package file with ``ast`` -- the drop-in signature contract."""
@@ -269,6 +335,7 @@ def main(ref_root: str) -> None:
     np.savez_compressed(HERE / "activations.npz", **acts)
 
     make_mxfp8(ref)
+    make_mxfp4(ref)
     make_signatures(ref)
     print("golden fixtures written to", HERE)
 
@@ -280,6 +347,8 @@ if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ["BOLTOPS_REFERENCE"]
     if len(sys.argv) > 2 and sys.argv[2] == "mxfp8":      # only one fixture
         make_mxfp8(Path(root))
+    elif len(sys.argv) > 2 and sys.argv[2] == "mxfp4":
+        make_mxfp4(Path(root))
     elif len(sys.argv) > 2 and sys.argv[2] == "signatures":
         make_signatures(Path(root))
     else:

@@ -56,6 +56,7 @@ def _worker(rank, world, port, E, K, H, I, M, zipf, ret, chunks=1):
                                combine_fn=_cpu_gather_sum)
         if chunks > 1:                                       # the pipelined exchange, in chunks
             ep.pipeline_chunks, ep.pipeline_min_tokens = chunks, 0
+            ep.pipeline_rows_per_expert = 0
             if rank == world - 1:
                 ids[:] = ids % (E // world)                  # this rank sends to rank 0 only ...
             else:

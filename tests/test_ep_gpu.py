@@ -43,7 +43,7 @@ def _worker(rank, world, port, ret):
                              w1_scale=fw1s, w2_scale=fw2s, block_shape=[128, 128])
         torch.cuda.synchronize()
         # pipelined exchange in three token chunks on a second stream: same result
-        ep.pipeline_chunks, ep.pipeline_min_tokens = 3, 0
+        ep.pipeline_chunks, ep.pipeline_min_tokens, ep.pipeline_rows_per_expert = 3, 0, 0
         piped = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
                            w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
         torch.cuda.synchronize()

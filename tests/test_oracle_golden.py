@@ -189,3 +189,26 @@ def test_mxfp8_layer_fixture(case):
                       **MX_CASES[case])
     assert out.dtype == c["expected"].dtype
     assert torch.equal(out.float(), c["expected"].float())
+
+
+@pytest.mark.parametrize("case", __import__("tests.helpers", fromlist=["MXFP4_CASES"]).MXFP4_CASES)
+def test_mxfp4_layer_fixture(case):
+    """The oracle's MXFP4 layer reproduces the reference's CPU statement bit for bit on every
+    case of test_public_mxfp4_cpu_reference (fixture written by make_golden.py)."""
+    from tests.helpers import load_mxfp4_case
+    c = load_mxfp4_case(case)
+    got = O.moe_mxfp4(
+        c["x"], c["w1"], c["w2"], c["s1"], c["s2"], c["weights"], c["ids"],
+        activation=c["activation"], expert_map=c["expert_map"],
+        a1_scale=c["static_s1"] if c["static"] else None,
+        a2_scale=c["static_s2"] if c["static"] else None, b1=c["bias1"], b2=c["bias2"],
+        alpha=c["alpha"] if c["static"] else None, limit=c["clamp"],
+        apply_router_weight_on_input=c["input_router"], no_combine=c["no_combine"],
+        routed_scaling_factor=1.25)
+    assert got.dtype == c["expected"].dtype and got.shape == c["expected"].shape
+    assert torch.equal(got, c["expected"])
+    # the test's pre-quantised inputs are the oracle quantiser's codes and scales
+    if not c["static"]:
+        q, scale, _ = O.mxfp4_quant_g128(c["x"])
+        assert torch.equal(q.view(torch.uint8), c["input_q"].view(torch.uint8))
+        assert torch.equal(scale, c["input_scale"])
