@@ -52,7 +52,7 @@ DEFAULT_WORKLOAD = "deepseek_v3_fp8_block"
 # The capture ran on 64 of the 256 experts with the same rows per expert; DRAM traffic of this
 # kernel is proportional to the expert count, so the figure is that capture's times 256/64.
 NCU_TRAFFIC_BYTES = {
-    ("deepseek_v3_fp8_block", 4096): 8.78e9,
+    ("deepseek_v3_fp8_block", 4096): 8.68e9,
 }
 
 # Dense 8-bit tensor-core peaks of this pool's B200s, measured with the recipe of the bf16

@@ -175,3 +175,24 @@ def ptr(t) -> int | None:
 def stream_of(t: torch.Tensor) -> int:
     """Raw handle of torch's current stream on the tensor's device."""
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def on_device(device: torch.device):
+    """Context that makes `device` current for a C-ABI call; free when it already is (the
+    common case: entering torch.cuda.device costs several microseconds per kernel launch, which
+    is most of a decode-sized layer's host time)."""
+    index = device.index
+    if index is None or index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)

@@ -34,7 +34,7 @@ struct SortParams {
   int32_t* expert_ids;       // per block
   int32_t* positions;        // [2E] (CK) or nullptr
   int32_t* num_valid;        // [1]
-  int32_t* route_pos;        // [R] sorted position of every route (optional, pre-filled with -1)
+  int32_t* route_pos;        // [R] sorted position of every route, -1 if it has none (optional)
   int32_t* segments;         // optional [*][4]: {expert label, first row, rows, 0} per run of at
                              // most segment_rows live rows of one expert, in sorted order
   int32_t* num_segments;     // [1]
@@ -228,9 +228,10 @@ __device__ void cta_scatter(const SortParams& p, int cta, int* warp_cnt, const i
         const int token = r / p.topk, slot = r - token * p.topk;
         p.sorted_ids[dst] = (int32_t)((uint32_t)token | ((uint32_t)slot << 24));
         p.sorted_weights[dst] = p.weights[r];
-        if (p.route_pos != nullptr) p.route_pos[r] = dst;
       }
     }
+    // every route is visited exactly once here: routes to masked or out-of-range experts get -1
+    if (!p.vllm && p.route_pos != nullptr && r < end) p.route_pos[r] = dst;
   }
 }
 
@@ -465,8 +466,6 @@ extern "C" int bolt_moe_sort_ck(const int32_t* topk_ids, const float* topk_weigh
   p.vllm = 0;
   if (moe_buf != nullptr && moe_buf_bytes > 0)
     BOLT_CUDA(cudaMemsetAsync(moe_buf, 0, moe_buf_bytes, st));
-  if (route_pos != nullptr && p.R > 0)   // routes of masked / out-of-range experts stay -1
-    BOLT_CUDA(cudaMemsetAsync(route_pos, 0xFF, (size_t)p.R * sizeof(int32_t), st));
   return run_sort(p, workspace, workspace_bytes, st);
 }
 

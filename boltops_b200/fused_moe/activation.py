@@ -119,7 +119,7 @@ def apply_activation(activation: str, is_gated: bool, activated_out: torch.Tenso
                                         activation_situ_beta, activation_situ_linear_beta)
     lib = _cabi.load()
     rows, n_out = activated_out.shape
-    with torch.cuda.device(ffn1_out_2d.device):
+    with _cabi.on_device(ffn1_out_2d.device):
         check(lib.bolt_moe_activation(ptr(ffn1_out_2d), ptr(activated_out),
                                       dtype_code(ffn1_out_2d.dtype), rows, n_out, kind,
                                       int(is_gated), alpha, limit, ptr(rows_dev),
@@ -171,7 +171,7 @@ def activation_quant(ffn1_out_2d: torch.Tensor, activation: str, is_gated: bool,
     scale = torch.empty((rows, 1), dtype=torch.float32, device=ffn1_out_2d.device)
     if row_multiplier is not None:
         row_multiplier = row_multiplier.to(torch.float32).contiguous()
-    with torch.cuda.device(ffn1_out_2d.device):
+    with _cabi.on_device(ffn1_out_2d.device):
         check(lib.bolt_act_quant(ptr(ffn1_out_2d), dtype_code(ffn1_out_2d.dtype), rows, n_out, kind,
                                  int(is_gated), dtype_code(quant_dtype), ptr(row_multiplier),
                                  ptr(q), ptr(scale), ptr(rows_dev), stream_of(ffn1_out_2d)))

@@ -46,7 +46,7 @@ def _decode_weights(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     e, n, kp = w.shape
     out = torch.empty((e, n, 2 * kp), dtype=torch.bfloat16, device=w.device)
     wc, sc = w.contiguous(), scale.contiguous()
-    with torch.cuda.device(w.device):
+    with _cabi.on_device(w.device):
         check(_cabi.load().bolt_mxfp4_decode(ptr(wc), ptr(sc), e * n, 2 * kp, ptr(out),
                                              _cabi.BF16, stream_of(w)))
     ops._count()
@@ -66,7 +66,7 @@ def act_quant(x: torch.Tensor, *, gated: bool = False, limit: Optional[float] = 
     static = static_scale is not None or x.dtype == torch.float8_e4m3fn
     scales = None if static or not want_codes else \
         torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _cabi.on_device(x.device):
         check(_cabi.load().bolt_mx4_act_quant(
             ptr(x), dtype_code(x.dtype), rows, cols, int(gated), int(limit is not None),
             float(limit or 0.0), int(static), ptr(static_scale), ptr(deq), _cabi.BF16, ptr(codes),
@@ -80,7 +80,7 @@ def group_decode(codes: torch.Tensor, scales: torch.Tensor, group: int) -> torch
     rows, cols = codes.shape
     out = torch.empty((rows, cols), dtype=torch.bfloat16, device=codes.device)
     codes, scales = codes.contiguous(), scales.contiguous()
-    with torch.cuda.device(codes.device):
+    with _cabi.on_device(codes.device):
         check(_cabi.load().bolt_fp8_group_decode(ptr(codes), ptr(scales), rows, cols, group,
                                                  ptr(out), _cabi.BF16, stream_of(codes)))
     ops._count()
@@ -243,7 +243,7 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             g1 = torch.empty((cap, n1), device=dev, dtype=torch.float32)
             ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1_d, c=g1, **common)
             act = torch.empty((cap, inter), device=dev, dtype=torch.bfloat16)
-            with torch.cuda.device(dev):
+            with _cabi.on_device(dev):
                 check(lib.bolt_mx4_swiglu_static(
                     ptr(g1), ptr(expert_ids), ptr(num_valid), cap, inter, e_local, ptr(a1_scale),
                     ptr(b1f), float(alpha), float(limit),
@@ -273,7 +273,7 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             else:
                 dst = torch.empty((cap, model_dim), device=dev, dtype=out_dtype)
                 scatter = 0
-            with torch.cuda.device(dev):
+            with _cabi.on_device(dev):
                 check(lib.bolt_mx4_affine_rows(
                     ptr(g2), ptr(expert_ids), ptr(sorted_ids), ptr(num_valid), cap, model_dim,
                     e_local, m, topk, ptr(a2_scale), ptr(b2f),

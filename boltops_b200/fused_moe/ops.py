@@ -79,29 +79,38 @@ def moe_sorting_ck(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_exper
     cap = m * topk + num_experts * block_size - topk
     cap_alloc = ceil_to(max(cap, 0), block_size)
     blocks = cap_alloc // block_size
-    sorted_ids = torch.empty(cap_alloc, dtype=torch.int32, device=dev)
-    sorted_weights = torch.empty(cap_alloc, dtype=torch.float32, device=dev)
-    sorted_expert_ids = torch.empty(max(blocks, 1), dtype=torch.int32, device=dev)
-    positions = torch.empty(2 * num_experts, dtype=torch.int32, device=dev)
-    num_valid = torch.empty(1, dtype=torch.int32, device=dev)
+    # one allocation for every int32 / fp32 output and the scratch (a decode-sized layer is bound
+    # by host time per call; each separate allocation costs microseconds)
+    ws_bytes = lib.bolt_moe_sort_workspace_bytes(m, topk, num_experts)
+    max_segments = (min(num_experts, m * topk) + (m * topk) // segment_rows) if segment_rows > 0 else 0
+    n_blocks = max(blocks, 1)
+    sizes = (cap_alloc, cap_alloc, n_blocks, 2 * num_experts, 4, 4 * max(max_segments, 1) if
+             segment_rows > 0 else 0, 4 if segment_rows > 0 else 0, (ws_bytes + 3) // 4)
+    offs = [0]
+    for n in sizes:
+        offs.append(offs[-1] + ceil_to(n, 4))                 # 16-byte aligned parts
+    buf = torch.empty(offs[-1], dtype=torch.int32, device=dev)
+    sorted_ids = buf[offs[0]:offs[0] + cap_alloc]
+    sorted_weights = buf[offs[1]:offs[1] + cap_alloc].view(torch.float32)
+    sorted_expert_ids = buf[offs[2]:offs[2] + n_blocks]
+    positions = buf[offs[3]:offs[3] + 2 * num_experts]
+    num_valid = buf[offs[4]:offs[4] + 1]
+    segments = num_segments = None
+    if segment_rows > 0:
+        segments = buf[offs[5]:offs[5] + 4 * max(max_segments, 1)].view(-1, 4)
+        num_segments = buf[offs[6]:offs[6] + 1]
+    ws = buf[offs[7]:offs[7] + (ws_bytes + 3) // 4]
     moe_buf = None
     if alloc_moe_buf and model_dim is not None and moebuf_dtype is not None:
         moe_buf = torch.empty((m, model_dim), dtype=moebuf_dtype, device=dev)
-    ws_bytes = lib.bolt_moe_sort_workspace_bytes(m, topk, num_experts)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    segments = num_segments = None
-    if segment_rows > 0:
-        max_segments = min(num_experts, m * topk) + (m * topk) // segment_rows
-        segments = torch.empty((max(max_segments, 1), 4), dtype=torch.int32, device=dev)
-        num_segments = torch.empty(1, dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _cabi.on_device(dev):
         check(lib.bolt_moe_sort_ck(
             ptr(topk_ids), ptr(topk_weights), ptr(expert_mask), m, topk, num_experts, block_size,
             ptr(sorted_ids), ptr(sorted_weights), ptr(sorted_expert_ids), ptr(positions),
             ptr(num_valid), ptr(route_pos), ptr(segments), ptr(num_segments), segment_rows,
             ptr(moe_buf), 0 if moe_buf is None else moe_buf.numel() * moe_buf.element_size(),
             ptr(ws), ws_bytes, stream_of(topk_ids)))
-    _count((1 if ws_bytes <= 16 else 3) + (1 if route_pos is not None else 0))
+    _count(1 if ws_bytes <= 16 else 3)
     if segment_rows > 0:
         return (sorted_ids, sorted_weights, sorted_expert_ids, num_valid, positions, moe_buf,
                 segments, num_segments)
@@ -140,7 +149,7 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
         expert_map = expert_map.to(torch.int32).contiguous()
     ws_bytes = lib.bolt_moe_sort_workspace_bytes(numel, 1, num_experts)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _cabi.on_device(dev):
         check(lib.bolt_moe_align_block_size(
             ptr(ids), numel, num_experts, block_size, ptr(expert_map), ptr(sorted_ids),
             ptr(expert_ids), ptr(num_post), ptr(ws), ws_bytes, stream_of(ids)))
@@ -167,7 +176,7 @@ def quant_rows(x: torch.Tensor, quant_dtype: torch.dtype, group: Optional[int] =
     q = torch.empty((rows, cols), dtype=quant_dtype, device=x.device)
     shape = (cols // g, rows) if group_major else (rows, cols // g)
     scales = torch.empty(shape, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _cabi.on_device(x.device):
         check(lib.bolt_quant_rows(ptr(x), dtype_code(x.dtype), rows, cols, g,
                                   dtype_code(quant_dtype), int(scale_ue8m0), ptr(q), ptr(scales),
                                   rows if group_major else 0, stream_of(x)))
@@ -224,7 +233,7 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Te
         else:
             dst_scale = torch.empty((groups, capacity), dtype=torch.float32, device=src.device)
             ld = capacity
-    with torch.cuda.device(src.device):
+    with _cabi.on_device(src.device):
         check(lib.bolt_gather_rows(ptr(src), m, row_bytes, src_stride, ptr(src_scale),
                                    scale_stride, groups, ptr(sorted_ids), ptr(num_valid),
                                    capacity, ptr(dst), ptr(dst_scale), ld, stream_of(src)))
@@ -245,7 +254,7 @@ def quant_scatter_rows(x: torch.Tensor, group: int, q_dtype: torch.dtype, route_
     assert route_pos.dtype == torch.int32 and route_pos.is_contiguous() and route_pos.shape[0] == m
     dst = torch.empty((capacity, cols), dtype=q_dtype, device=x.device)
     dst_scale = torch.empty((cols // group, capacity), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _cabi.on_device(x.device):
         check(lib.bolt_quant_scatter_rows(ptr(x), dtype_code(x.dtype), m, cols, group,
                                           dtype_code(q_dtype), int(scale_ue8m0), ptr(route_pos),
                                           route_pos.shape[1], ptr(sorted_ids), ptr(num_valid),
@@ -269,7 +278,7 @@ def mx_quant_rows(x: torch.Tensor, *, gated: bool = False, alpha: float = 1.0, b
     q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device) if want_codes else None
     s = torch.empty((rows, cols // 32), dtype=torch.uint8, device=x.device) if want_codes else None
     deq = torch.empty((rows, cols), dtype=deq_dtype, device=x.device) if deq_dtype is not None else None
-    with torch.cuda.device(x.device):
+    with _cabi.on_device(x.device):
         check(lib.bolt_mx_quant_rows(ptr(x), dtype_code(x.dtype), rows, cols, int(gated),
                                      float(alpha), float(beta), int(limit is not None),
                                      float(limit or 0.0), ptr(q), ptr(s), ptr(deq),
@@ -289,7 +298,7 @@ def mx_dequant_rows(q: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtyp
     rows = q.numel() // cols
     assert scales.dtype == torch.uint8 and scales.numel() == rows * (cols // 32)
     out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
-    with torch.cuda.device(q.device):
+    with _cabi.on_device(q.device):
         check(lib.bolt_mx_dequant_rows(ptr(q), ptr(scales), rows, cols, ptr(out),
                                        dtype_code(out_dtype), stream_of(q)))
     _count()
@@ -306,7 +315,7 @@ def mx_sf_layout(scales: torch.Tensor, dst_rows: int, row_ids: Optional[torch.Te
     rows, sf_cols = scales.shape
     assert scales.dtype == torch.uint8 and sf_cols % 4 == 0 and dst_rows % 128 == 0
     dst = torch.empty((dst_rows // 128, sf_cols // 4, 512), dtype=torch.uint8, device=scales.device)
-    with torch.cuda.device(scales.device):
+    with _cabi.on_device(scales.device):
         check(lib.bolt_mx_sf_layout(ptr(scales), rows, sf_cols, ptr(row_ids), ptr(num_valid),
                                     dst_rows, ptr(dst), stream_of(scales)))
     _count()
@@ -327,7 +336,7 @@ def moe_sum(input_tensor: torch.Tensor, output_tensor: torch.Tensor,
     if router_weights is not None:
         router_weights = router_weights.to(torch.float32).contiguous()
     lib = _cabi.load()
-    with torch.cuda.device(input_tensor.device):
+    with _cabi.on_device(input_tensor.device):
         check(lib.bolt_moe_sum(ptr(input_tensor), dtype_code(input_tensor.dtype),
                                ptr(output_tensor), dtype_code(output_tensor.dtype), m, topk, n,
                                float(routed_scaling_factor), ptr(router_weights),
@@ -344,7 +353,7 @@ def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
     m, slots = pos.shape
     assert pos.dtype == torch.int32 and pos.is_contiguous()
     assert src.is_contiguous() and out.is_contiguous()
-    with torch.cuda.device(out.device):
+    with _cabi.on_device(out.device):
         check(lib.bolt_moe_gather_sum(ptr(src), dtype_code(src.dtype), ptr(pos), ptr(out),
                                       dtype_code(out.dtype), m, slots, out.shape[1], float(scale),
                                       stream_of(out)))
@@ -362,7 +371,7 @@ def ep_dest_ranks(topk_ids: torch.Tensor, num_experts: int, experts_per_rank: in
     ids = ids.contiguous()
     m, k = ids.shape
     routes = torch.empty((m, world), dtype=torch.int32, device=ids.device)
-    with torch.cuda.device(ids.device):
+    with _cabi.on_device(ids.device):
         check(lib.bolt_ep_dest_ranks(ptr(ids), m, k, num_experts, experts_per_rank, world,
                                      chunk_tokens, ptr(routes), stream_of(ids)))
     _count()
@@ -389,7 +398,7 @@ def ep_pack_rows(data: torch.Tensor, scales: Optional[torch.Tensor], topk_ids: t
     if scales is not None:
         scales = scales.reshape(data.shape[0], -1).contiguous()
         groups = scales.shape[1]
-    with torch.cuda.device(data.device):
+    with _cabi.on_device(data.device):
         check(lib.bolt_ep_pack_rows(ptr(data), data.shape[1] * data.element_size(), ptr(scales),
                                     groups, ptr(topk_ids), ptr(topk_weights), topk_ids.shape[1],
                                     ptr(send_ids), first, rows, ptr(out), out.stride(0),
@@ -486,6 +495,6 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
         args.max_segments = segments.shape[0]
         args.segments = ptr(segments)
         args.num_segments = ptr(num_segments)
-    with torch.cuda.device(a.device):
+    with _cabi.on_device(a.device):
         check(lib.bolt_grouped_gemm(C.byref(args), stream_of(a)))
     _count()

@@ -26,7 +26,7 @@ def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: i
     dev = gating_output.device
     weights = torch.empty((m, topk), dtype=torch.float32, device=dev)
     ids = torch.empty((m, topk), dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _cabi.on_device(dev):
         check(lib.bolt_fused_topk(ptr(gating_output), dtype_code(gating_output.dtype), m, e, topk,
                                   int(renormalize), int(is_softmax), ptr(weights), ptr(ids),
                                   stream_of(gating_output)))
@@ -55,7 +55,7 @@ def moe_fused_gate(input: torch.Tensor, bias: torch.Tensor, topk_weights: torch.
     m, e = input.shape
     x = input.contiguous()
     b = bias.float().contiguous()
-    with torch.cuda.device(x.device):
+    with _cabi.on_device(x.device):
         check(lib.bolt_moe_fused_gate(ptr(x), dtype_code(x.dtype), ptr(b), m, e, num_expert_group,
                                       topk_group, topk, num_fused_shared_experts,
                                       float(routed_scaling_factor), ptr(topk_weights),
