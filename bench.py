@@ -447,13 +447,16 @@ def cpu_reference(cfg, m, seed, budget_experts=None):
     return m / full, cores, sample, full
 
 
-def spot_check(cfg, out, hidden_h, wts_h, ids_h, device, seed, tokens=4):
-    """rel-L2 of ``out`` against the CPU oracle on a few tokens; only the experts those tokens
-    use are built (on the device, from the per-expert seed) and copied to the host."""
+def spot_check(cfg, out, hidden_h, wts_h, ids_h, device, seed, tokens=8):
+    """``out`` against the CPU oracle on a few tokens; only the experts those tokens use are built
+    (on the device, from the per-expert seed) and copied to the host.  Criterion: 8-bit kinds, the
+    reference's own for its w8a8 layer test -- mean |actual - expected| / mean |expected| < 0.02
+    (test/fused_moe/test_fused_moe.py:639-645 of the reference project); 16-bit experts, relative
+    L2 error <= 1e-2.  Both figures are reported."""
     from oracle import moe_oracle as O
 
     m = hidden_h.shape[0]
-    toks = sorted({0, m // 3, (2 * m) // 3, m - 1})[:tokens]
+    toks = sorted({(i * (m - 1)) // max(tokens - 1, 1) for i in range(tokens)})
     used = sorted(set(ids_h[toks].reshape(-1).tolist()))
     remap = {e: j for j, e in enumerate(used)}
     w1, w2, w1s, w2s = (None if t is None else t.cpu()
@@ -461,19 +464,25 @@ def spot_check(cfg, out, hidden_h, wts_h, ids_h, device, seed, tokens=4):
     loc = torch.tensor([[remap[int(e)] for e in row] for row in ids_h[toks]], dtype=torch.int32)
     h, w = hidden_h[toks], wts_h[toks]
     if cfg["kind"] == "fp8_block":
-        expect, tol = O.moe_block_fp8(h, w1, w2, w1s, w2s, w, loc, (128, 128)), 2e-2
+        expect = O.moe_block_fp8(h, w1, w2, w1s, w2s, w, loc, (128, 128))
     elif cfg["kind"] == "int8_channel":
-        expect, tol = O.moe_per_channel(h, w1, w2, w1s, w2s, w, loc, torch.int8), 2e-2
+        expect = O.moe_per_channel(h, w1, w2, w1s, w2s, w, loc, torch.int8)
     elif cfg["kind"] == "mxfp8":
-        expect, tol = O.moe_mxfp8(h, w1, w2, w1s, w2s, w, loc), 2e-2
+        expect = O.moe_mxfp8(h, w1, w2, w1s, w2s, w, loc)
     elif cfg["kind"] == "mxfp4":
-        expect, tol = O.moe_mxfp4(h, w1, w2, w1s, w2s, w, loc), 2e-2
+        expect = O.moe_mxfp4(h, w1, w2, w1s, w2s, w, loc)
     else:
-        expect, tol = O.moe_bf16(h, w1, w2, w, loc), 1e-2
+        expect = O.moe_bf16(h, w1, w2, w, loc)
     torch.cuda.synchronize()
-    err = O.rel_l2(out[toks].cpu(), expect)
-    return dict(rel_l2=err, tolerance=tol, tokens=len(toks), experts_rebuilt=len(used),
-                ok=bool(err <= tol))
+    actual = out[toks].cpu()
+    err = O.rel_l2(actual, expect)
+    mean_rel = float((actual.float() - expect.float()).abs().mean() / expect.float().abs().mean())
+    if cfg["kind"] == "bf16":
+        criterion, tol, ok = "rel_l2", 1e-2, err <= 1e-2
+    else:
+        criterion, tol, ok = "mean_rel", 2e-2, mean_rel < 2e-2
+    return dict(rel_l2=err, mean_rel=mean_rel, criterion=criterion, tolerance=tol,
+                tokens=len(toks), experts_rebuilt=len(used), ok=bool(ok))
 
 
 # ---------------------------------------------------------------------------

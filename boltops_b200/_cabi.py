@@ -22,7 +22,7 @@ BF16, F16, F32, FP8_E4M3, INT8 = 0, 1, 2, 3, 4
  ACT_SWIGLU_OAI_INTERLEAVED, ACT_SITU) = range(9)
 # enum bolt_gemm_kind
 GEMM_BF16, GEMM_F16, GEMM_FP8_BLOCK, GEMM_INT8_CHANNEL, GEMM_FP8_CHANNEL, GEMM_INT8_BLOCK, \
-    GEMM_MXFP8 = range(7)
+    GEMM_MXFP8, GEMM_MXFP4 = range(8)
 # enum bolt_gemm_epilogue
 EPI_STORE, EPI_SILU_MUL, EPI_SILU_MUL_QUANT = range(3)
 # enum bolt_gemm_schedule, BOLT_PAIR_SEGMENT_ROWS
@@ -60,6 +60,25 @@ class GemmArgs(C.Structure):
         ("act_has_limit", C.c_int),
         ("schedule", C.c_int), ("max_segments", C.c_int),
         ("segments", C.c_void_p), ("num_segments", C.c_void_p),
+        ("a_gather", C.c_int), ("a_rows", C.c_int), ("a_pad_row", C.c_int),
+        ("a_row_bytes", C.c_int64),
+    ]
+
+
+class LayerArgs(C.Structure):
+    """struct bolt_layer_args"""
+    _fields_ = [
+        ("kind", C.c_int), ("x_dtype", C.c_int), ("out_dtype", C.c_int),
+        ("num_tokens", C.c_int), ("topk", C.c_int),
+        ("hidden", C.c_int), ("inter", C.c_int), ("model_dim", C.c_int),
+        ("num_experts", C.c_int), ("global_num_experts", C.c_int),
+        ("hidden_states", C.c_void_p), ("w1", C.c_void_p), ("w2", C.c_void_p),
+        ("w1_scale", C.c_void_p), ("w2_scale", C.c_void_p), ("b1", C.c_void_p), ("b2", C.c_void_p),
+        ("bias_dtype", C.c_int), ("apply_router_weight_on_input", C.c_int),
+        ("topk_weights", C.c_void_p), ("topk_ids", C.c_void_p), ("expert_mask", C.c_void_p),
+        ("routed_scaling_factor", C.c_float),
+        ("out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("status", C.c_void_p),
     ]
 
 
@@ -105,7 +124,7 @@ _SIGNATURES = {
                                     C.c_int, C.c_void_p]),
     "bolt_mx4_act_quant": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
                                      C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
-                                     C.c_void_p, C.c_void_p, C.c_void_p]),
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "bolt_fp8_group_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int,
                                         C.c_void_p, C.c_int, C.c_void_p]),
     "bolt_mx4_swiglu_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
@@ -127,6 +146,8 @@ _SIGNATURES = {
     "bolt_moe_gather_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                       C.c_int64, C.c_int, C.c_int, C.c_float, C.c_void_p]),
     "bolt_grouped_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "bolt_moe_layer_workspace_bytes": (C.c_size_t, [C.POINTER(LayerArgs)]),
+    "bolt_moe_layer": (C.c_int, [C.POINTER(LayerArgs), C.c_void_p]),
 }
 
 EXPORTS = tuple(_SIGNATURES)

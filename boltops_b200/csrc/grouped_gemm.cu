@@ -100,6 +100,10 @@ struct GemmParams {
   int kb_scale_cols;  // k/128 (block-scaled kinds)
   uint32_t idesc;
   int group_m;
+  // gathered row operand: A is in TOKEN order; sorted position p reads row (sorted_ids[p] & 0xFFFFFF),
+  // or row a_pad_row when that id is not a token (tile padding)
+  int a_gather;
+  int a_pad_row;
   // tile-pair schedule: work list of the sort (runs of at most 256 rows of one expert)
   const int32_t* segments;     // [max_segments][4] = {expert, first row, rows, -}
   const int32_t* num_segments;
@@ -108,6 +112,7 @@ struct GemmParams {
   const uint8_t* sfa;   // [capacity/128][num_kb][512]
   const uint8_t* sfb;   // [num_experts][n_blocks128][num_kb][512]
   int n_blocks128;
+  int mx_stage_tx;      // operand bytes one K block brings (packed 4-bit weights count as stored)
   float act_alpha, act_beta, act_limit;   // MX gated epilogue
   int act_has_limit;
 };
@@ -455,6 +460,52 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             for (int j2 = 0; j2 < 2; ++j2)
               tma_load_3d_pair(sa + kABytes + j2 * (kBBytes / 4), &tma_b, full0, kb * kBKElems,
                                brow[j2], expert);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+          }
+        }
+      } else if (!PAIR && p.a_gather) {
+        // Row operand gathered from token order: lane l owns rows 4l .. 4l+3 of the tile and
+        // brings them with one four-row gather per K block (32 gathers fill the 128 x 128-byte
+        // stage: the swizzle follows the shared-memory address, so four rows at 512-byte steps
+        // land where the one-box copy would put them).  Lane 0 also waits for the stage, arms
+        // the barrier and issues the weight boxes.
+        int s = 0;
+        uint32_t ph = 0, kbi = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
+          const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+          const int expert = p.expert_ids[tc.m_blk];
+          if (expert < 0 || expert >= p.num_experts) continue;
+          const int4 sid4 =
+              *reinterpret_cast<const int4*>(p.sorted_ids + (int64_t)tc.m_blk * kBM + 4 * lane);
+          int r[4] = {sid4.x & 0xFFFFFF, sid4.y & 0xFFFFFF, sid4.z & 0xFFFFFF, sid4.w & 0xFFFFFF};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) r[j] = r[j] < p.num_tokens ? r[j] : p.a_pad_row;
+          int brow[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            brow[j] = GATED ? ((j & 1) ? p.n_half : 0) + tc.n_blk * 128 + (j >> 1) * 64
+                            : tc.n_blk * 256 + j * 64;
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            int okl = 1;
+            if (lane == 0) okl = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+            if (!ok) break;
+            const uint32_t full = bar_full + 8 * s;
+            const uint32_t sa = smem_base + s * kStageBytes;
+            if (lane == 0) {
+              mbar_expect_tx(full, kStageBytes + (BS ? 512 : 0));
+              if (BS)
+                bulk_load(smem_u32(as_ring) + (kbi % kScaleSlots) * 512,
+                          p.a_scale + (int64_t)kb * p.a_scale_ld + tc.m_blk * kBM, 512, full);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                tma_load_3d(sa + kABytes + j * (kBBytes / 4), &tma_b, full, kb * kBKElems, brow[j],
+                            expert);
+            }
+            ++kbi;
+            __syncwarp();
+            tma_gather4_2d(sa + lane * 512, &tma_a, full, kb * kBKElems, r[0], r[1], r[2], r[3]);
             if (++s == kStages) { s = 0; ph ^= 1; }
           }
         }
@@ -1063,7 +1114,7 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
           const uint32_t sa = smem_base + s * kStageBytes;
           const uint32_t sf = smem_u32(sf_ring) + (kbi % kMxSfSlots) * kMxSfSlotBytes;
           ++kbi;
-          mbar_expect_tx(full, kStageBytes + kMxSfSlotBytes);
+          mbar_expect_tx(full, p.mx_stage_tx + kMxSfSlotBytes);
           bulk_load(sf, sfa_t + (int64_t)kb * 512, 512, full);
           bulk_load(sf + 512, sfb0 + (int64_t)kb * 512, 512, full);
           bulk_load(sf + 1024, sfb1 + (int64_t)kb * 512, 512, full);
@@ -1357,8 +1408,9 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   const bool is16 = a->kind == BOLT_GEMM_BF16 || a->kind == BOLT_GEMM_F16;
   const bool block = a->kind == BOLT_GEMM_FP8_BLOCK || a->kind == BOLT_GEMM_INT8_BLOCK;
   const bool is_int = a->kind == BOLT_GEMM_INT8_CHANNEL || a->kind == BOLT_GEMM_INT8_BLOCK;
-  const bool mx = a->kind == BOLT_GEMM_MXFP8;
-  BOLT_REQUIRE(a->kind >= BOLT_GEMM_BF16 && a->kind <= BOLT_GEMM_MXFP8,
+  const bool mx4 = a->kind == BOLT_GEMM_MXFP4;      // e4m3 rows x packed e2m1 weights
+  const bool mx = a->kind == BOLT_GEMM_MXFP8 || mx4;
+  BOLT_REQUIRE(a->kind >= BOLT_GEMM_BF16 && a->kind <= BOLT_GEMM_MXFP4,
                "grouped_gemm: unknown kind %d", a->kind);
   if (mx) {
     BOLT_REQUIRE(a->epilogue == BOLT_EPI_STORE || a->epilogue == BOLT_EPI_SILU_MUL_QUANT,
@@ -1367,6 +1419,10 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
                  "grouped_gemm: the MX gated epilogue needs n/2 a multiple of 128");
     BOLT_REQUIRE(a->k % 128 == 0, "grouped_gemm: the MX kind needs k a multiple of 128");
     BOLT_REQUIRE(a->bias == nullptr, "grouped_gemm: the MX kind takes no bias");
+    BOLT_REQUIRE(!mx4 || a->epilogue == BOLT_EPI_STORE,
+                 "grouped_gemm: the MXFP4 kind has the plain epilogue");
+    BOLT_REQUIRE(!mx4 || reinterpret_cast<uintptr_t>(a->b) % 32 == 0,
+                 "grouped_gemm: packed e2m1 weights must be 32-byte aligned");
   }
   const int elem = is16 ? 2 : 1;
   BOLT_REQUIRE(((int64_t)a->k * elem) % 16 == 0, "grouped_gemm: k*elem_size must be a multiple of 16");
@@ -1410,6 +1466,18 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
                  "grouped_gemm: the tile-pair schedule needs the segment list of bolt_moe_sort_ck");
   }
 
+  const bool gather = a->a_gather != 0;
+  if (gather) {
+    BOLT_REQUIRE(!pair && !mx, "grouped_gemm: the gathered row operand needs the single-tile "
+                               "schedule of the plain kinds");
+    BOLT_REQUIRE(a->sorted_ids != nullptr && a->a_rows > 0 && a->a_pad_row >= 0 &&
+                     a->a_pad_row < a->a_rows,
+                 "grouped_gemm: gathered row operand needs sorted_ids, a_rows and a pad row inside it");
+    BOLT_REQUIRE(a->a_row_bytes == 0 ||
+                     (a->a_row_bytes % 16 == 0 && a->a_row_bytes >= (int64_t)a->k * elem),
+                 "grouped_gemm: a_row_bytes must be a multiple of 16 and cover a row");
+  }
+
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) {
     set_error("grouped_gemm: cuTensorMapEncodeTiled is unavailable");
@@ -1421,9 +1489,11 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   const cuuint32_t bk = is16 ? 64 : 128;
   CUtensorMap ma, mb;
   {
-    cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)a->capacity};
-    cuuint64_t strides[1] = {(cuuint64_t)a->k * elem};
-    cuuint32_t box[2] = {bk, (cuuint32_t)kBM};
+    // gathered row operand: the tensor is the token-order matrix, the box one row high
+    cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)(gather ? a->a_rows : a->capacity)};
+    cuuint64_t strides[1] = {gather && a->a_row_bytes > 0 ? (cuuint64_t)a->a_row_bytes
+                                                          : (cuuint64_t)a->k * elem};
+    cuuint32_t box[2] = {bk, gather ? 1u : (cuuint32_t)kBM};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(&ma, dt, 2, const_cast<void*>(a->a), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1434,11 +1504,15 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     }
   }
   {
+    // packed e2m1 weights: two values per byte in global memory; the copy spreads every 8 bytes
+    // (16 values) over 16 bytes of shared memory, the form the f8f6f4 instruction reads
+    const CUtensorMapDataType dtb = mx4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : dt;
+    const cuuint64_t row_bytes = mx4 ? (cuuint64_t)a->k / 2 : (cuuint64_t)a->k * elem;
     cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
-    cuuint64_t strides[2] = {(cuuint64_t)a->k * elem, (cuuint64_t)a->k * elem * a->n};
+    cuuint64_t strides[2] = {row_bytes, row_bytes * a->n};
     cuuint32_t box[3] = {bk, 64, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = encode(&mb, dt, 3, const_cast<void*>(a->b), dims, strides, box, estr,
+    CUresult r = encode(&mb, dtb, 3, const_cast<void*>(a->b), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -1508,6 +1582,8 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     p.group_m = g < 4 ? 4 : (g > 16 ? 16 : g);
     if (pair) p.group_m = (p.group_m + 1) / 2;   // the unit of the tile order is a pair of row tiles
   }
+  p.a_gather = gather ? 1 : 0;
+  p.a_pad_row = a->a_pad_row;
   p.segments = a->segments;
   p.num_segments = a->num_segments;
   p.max_segments = a->max_segments;
@@ -1519,6 +1595,10 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     // block-scaled descriptor: e4m3 x e4m3 (formats 0), K-major, N >> 3 at bit 17, E8M0 scales
     // (bit 23), M >> 4 at bit 24; the scale-byte selectors (bits 4-5, 29-30) are set per K step
     p.idesc = ((uint32_t)(kAccCols >> 3) << 17) | (1u << 23) | ((uint32_t)(kBM >> 4) << 24);
+    if (mx4) p.idesc |= 5u << 10;      // B format e2m1 (A stays e4m3 = 0)
+    // the copy of packed 4-bit values completes the barrier by the bytes it read (half of the
+    // shared-memory footprint it writes)
+    p.mx_stage_tx = kABytes + (mx4 ? kBBytes / 2 : kBBytes);
     p.sfa = reinterpret_cast<const uint8_t*>(a->a_scale);
     p.sfb = reinterpret_cast<const uint8_t*>(a->b_scale);
     p.n_blocks128 = gated ? 2 * p.tiles_n : (a->n + 127) / 128;

@@ -75,12 +75,13 @@ __device__ __forceinline__ float load_as(const T* p) { return to_f32(*p); }
 //            1e-10), q = e4m3(clamp(v * (1 / scale)))
 //   mode 1 : static  -- q = e4m3(v / *static_scale); the decoded value is the code itself
 //   x8     : x holds e4m3 codes (static recipe, pre-quantised): decoded as they are
-// Outputs (each optional): deq = decoded values, codes, scales (fp32, dynamic mode).
+// Outputs (each optional): deq = decoded values, codes, scales (fp32, dynamic mode), sf32 = the
+// scale's exponent byte repeated per 32 elements ([rows, cols/32], dynamic mode).
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256) k_mx4_act_quant(
     const TIn* __restrict__ x, int64_t rows, int cols, int gated, int has_limit, float limit,
     int mode, const float* __restrict__ static_scale, int x8, TOut* __restrict__ deq,
-    uint8_t* __restrict__ codes, float* __restrict__ scales) {
+    uint8_t* __restrict__ codes, float* __restrict__ scales, uint8_t* __restrict__ sf32) {
   const int lane = threadIdx.x & 31;
   const int groups = cols / 128;
   const int64_t total = rows * groups;
@@ -127,6 +128,8 @@ __global__ void __launch_bounds__(256) k_mx4_act_quant(
 #pragma unroll
       for (int j = 0; j < 4; ++j) q[j] = fminf(fmaxf(v[j] * inv, -448.0f), 448.0f);
       if (scales != nullptr && lane == 0) scales[g] = scale;
+      // the same scale as four E8M0 bytes (one per 32 elements) for the tensor core's block scaling
+      if (sf32 != nullptr && lane == 0) reinterpret_cast<uint32_t*>(sf32)[g] = e * 0x01010101u;
     }
     uint32_t packed = 0;
 #pragma unroll
@@ -246,7 +249,7 @@ extern "C" int bolt_mxfp4_decode(const uint8_t* packed, const uint8_t* scales, i
 extern "C" int bolt_mx4_act_quant(const void* x, int x_dtype, int64_t rows, int cols, int gated,
                                   int has_limit, float limit, int mode, const float* static_scale,
                                   void* deq, int deq_dtype, uint8_t* codes, float* scales,
-                                  void* stream) {
+                                  uint8_t* sf32, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(rows >= 0 && cols > 0 && cols % 128 == 0,
@@ -264,7 +267,7 @@ extern "C" int bolt_mx4_act_quant(const void* x, int x_dtype, int64_t rows, int 
   BOLT_DISPATCH_OUT(deq_dtype, (k_mx4_act_quant<TIN, TOut><<<grid, 256, 0, st>>>(               \
                                    static_cast<const TIN*>(x), rows, cols, gated, has_limit,   \
                                    limit, mode, static_scale, x8, static_cast<TOut*>(deq), codes, \
-                                   scales)))
+                                   scales, sf32)))
   switch (x_dtype) {
     case BOLT_BF16: BOLT_MX4_LAUNCH(__nv_bfloat16); break;
     case BOLT_F16: BOLT_MX4_LAUNCH(__half); break;

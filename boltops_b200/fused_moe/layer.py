@@ -54,6 +54,9 @@ class StageTimer:
 
 
 STAGE_TIMER: Optional[StageTimer] = None
+# BOLTOPS_B200_ONE_CALL=0 drives the kernels one by one from Python (same results; used by the
+# tests to hold the two orchestrations against each other)
+_ONE_CALL = os.environ.get("BOLTOPS_B200_ONE_CALL", "1") != "0"
 
 
 class _Stage:
@@ -300,6 +303,54 @@ def fused_experts_impl(
     w2_scale_c = w2_scale.contiguous().float() if quantised else None
 
     chunk = _chunk_size()
+    # ---- the whole layer in one native call -------------------------------------------------
+    # Same kernels, same order, same arithmetic as the loop below; one foreign call and one
+    # workspace instead of one of each per kernel, which is what a decode-sized layer's time is
+    # made of.  Used whenever the variant is the common one.
+    if (_ONE_CALL and STAGE_TIMER is None and fused_silu and not no_combine
+            and num_tokens <= chunk and not use_ue8m0 and hidden_states.is_contiguous()
+            and hidden_states.dtype in (torch.float16, torch.bfloat16)
+            and output_dtype == hidden_states.dtype
+            and (b1 is None or b2 is None or b1.dtype == b2.dtype)
+            and (not quantised or (w1_scale_c.dtype == torch.float32))
+            and not _use_tile_pairs(kind, num_tokens * topk, global_num_experts)):
+        args = _cabi.LayerArgs()
+        args.kind = kind
+        args.x_dtype = _cabi.dtype_code(hidden_states.dtype)
+        args.out_dtype = _cabi.dtype_code(output_dtype)
+        args.num_tokens, args.topk = num_tokens, topk
+        args.hidden, args.inter, args.model_dim = hidden, act_dim, model_dim
+        args.num_experts, args.global_num_experts = e_local, global_num_experts
+        ids32 = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+        ids32 = ids32.contiguous()
+        wts32 = topk_weights.contiguous()
+        bias = b1 if b1 is not None else b2
+        b1c = b1.contiguous() if b1 is not None else None
+        b2c = b2.contiguous() if b2 is not None else None
+        args.hidden_states = hidden_states.data_ptr()
+        args.w1, args.w2 = w1.data_ptr(), w2.data_ptr()
+        args.w1_scale = _cabi.ptr(w1_scale_c)
+        args.w2_scale = _cabi.ptr(w2_scale_c)
+        args.b1, args.b2 = _cabi.ptr(b1c), _cabi.ptr(b2c)
+        args.bias_dtype = _cabi.dtype_code(bias.dtype) if bias is not None else _cabi.F32
+        args.apply_router_weight_on_input = int(apply_router_weight_on_input)
+        args.topk_weights, args.topk_ids = wts32.data_ptr(), ids32.data_ptr()
+        args.expert_mask = _cabi.ptr(expert_mask)
+        args.routed_scaling_factor = float(routed_scaling_factor)
+        args.out = out.data_ptr()
+        args.status = ops.device_status(dev).data_ptr()
+        lib = _cabi.load()
+        need = lib.bolt_moe_layer_workspace_bytes(args)
+        if need == 0:
+            _cabi.check(1)
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        args.workspace, args.workspace_bytes = workspace.data_ptr(), need
+        with _cabi.on_device(dev):
+            _cabi.check(lib.bolt_moe_layer(args, _cabi.stream_of(hidden_states)))
+        ops._count(ops.sort_launches(lib, num_tokens, topk, global_num_experts)
+                   + (4 if not quantised or block_mode else 6))
+        return out
+
     for begin in range(0, num_tokens, chunk):
         end = min(begin + chunk, num_tokens)
         m = end - begin

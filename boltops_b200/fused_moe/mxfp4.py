@@ -13,14 +13,20 @@ test/fused_moe/test_fused_moe.py:1411-1563 of the reference project).  Two recip
   when it is applied on the input, ``e4m3(act / a2_scale)``, GEMM2 times ``a2_scale`` plus bias,
   times the router weight otherwise; fp32 sum.
 
-How it runs here: an e2m1 or e4m3 code times a power of two is exact in bf16 and products of two
-such values are exact in fp32, so the K-grouped scaled contraction of the reference equals a
-bf16 tensor-core GEMM with fp32 accumulation over DECODED operands.  Weights are decoded once per
-(weight, scale) pair and cached; activations are decoded by the kernel that quantises them.
+How it runs here.  The dynamic recipe on 16-bit input runs on the tensor core's block-scaled
+kind (``BOLT_GEMM_MXFP4``): the packed weights and their E8M0 bytes are read as stored (a quarter
+of the bytes of a decoded copy), the activation codes carry their power-of-two group scale as four
+equal E8M0 bytes, and the tensor core applies both scales per 32 K elements.  The other variants
+(static scales, pre-quantised input) and ``BOLTOPS_B200_MXFP4=decoded`` use the fact that an e2m1
+or e4m3 code times a power of two is exact in bf16 and that products of two such values are exact
+in fp32: the K-grouped scaled contraction then equals a bf16 tensor-core GEMM with fp32
+accumulation over DECODED operands; weights are decoded once per (weight, scale) pair and cached,
+activations by the kernel that quantises them.
 """
 from __future__ import annotations
 
 import ctypes as C
+import os
 import weakref
 from typing import Optional
 
@@ -32,6 +38,7 @@ from . import ops
 from .activation import apply_activation
 
 _decoded = {}
+_NATIVE = os.environ.get("BOLTOPS_B200_MXFP4", "native") != "decoded"
 
 
 def _decode_weights(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -55,14 +62,17 @@ def _decode_weights(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 
 
 def act_quant(x: torch.Tensor, *, gated: bool = False, limit: Optional[float] = None,
-              static_scale: Optional[torch.Tensor] = None, want_codes: bool = False):
+              static_scale: Optional[torch.Tensor] = None, want_codes: bool = False,
+              want_deq: bool = True, want_sf: bool = False):
     """Quantise-and-decode ``x`` [rows, cols] (``[rows, 2 * cols]`` = [gate | up] with ``gated``).
-    Returns ``(decoded bf16 [rows, cols], codes or None, fp32 scales [rows, cols/128] or None)``."""
+    Returns ``(decoded bf16 [rows, cols], codes or None, fp32 scales [rows, cols/128] or None)``;
+    with ``want_sf`` a fourth value, the E8M0 byte of every 32 elements ``[rows, cols/32]``."""
     rows = x.shape[0]
     cols = x.shape[1] // 2 if gated else x.shape[1]
     x = x.contiguous()
-    deq = torch.empty((rows, cols), dtype=torch.bfloat16, device=x.device)
+    deq = torch.empty((rows, cols), dtype=torch.bfloat16, device=x.device) if want_deq else None
     codes = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device) if want_codes else None
+    sf = torch.empty((rows, cols // 32), dtype=torch.uint8, device=x.device) if want_sf else None
     static = static_scale is not None or x.dtype == torch.float8_e4m3fn
     scales = None if static or not want_codes else \
         torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
@@ -70,8 +80,10 @@ def act_quant(x: torch.Tensor, *, gated: bool = False, limit: Optional[float] = 
         check(_cabi.load().bolt_mx4_act_quant(
             ptr(x), dtype_code(x.dtype), rows, cols, int(gated), int(limit is not None),
             float(limit or 0.0), int(static), ptr(static_scale), ptr(deq), _cabi.BF16, ptr(codes),
-            ptr(scales), stream_of(x)))
+            ptr(scales), ptr(sf), stream_of(x)))
     ops._count()
+    if want_sf:
+        return deq, codes, scales, sf
     return deq, codes, scales
 
 
@@ -195,8 +207,16 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
         a1_scale, a2_scale = a1_scale.view(-1), a2_scale.view(-1)
     else:
         limit = 7. if activation == "swiglustep" else gemm1_limit
-    w1_d = _decode_weights(w1, w1_scale)
-    w2_d = _decode_weights(w2, w2_scale)
+    native = (_NATIVE and not static and hidden_states.dtype != torch.float8_e4m3fn
+              and w1.is_contiguous() and w2.is_contiguous()
+              and w1.data_ptr() % 32 == 0 and w2.data_ptr() % 32 == 0)
+    if native:
+        from .mxfp8 import _tile_weight_scales
+        sfb1 = _tile_weight_scales(w1, w1_scale.contiguous())
+        sfb2 = _tile_weight_scales(w2, w2_scale.contiguous())
+    else:
+        w1_d = _decode_weights(w1, w1_scale)
+        w2_d = _decode_weights(w2, w2_scale)
     expert_mask = (expert_map >= 0).to(torch.int32) if expert_map is not None else None
     ids_all = topk_ids.to(torch.int32)
     wts_all = topk_weights.to(torch.float32)
@@ -227,7 +247,10 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             if apply_router_weight_on_input:
                 # multiplied in the input dtype before the quantiser, as the reference prepares it
                 x = x * topk_weights[begin:end].to(x.dtype)
-            a_tok = act_quant(x)[0]
+            if native:
+                _, a_tok, _, a_sf = act_quant(x, want_codes=True, want_deq=False, want_sf=True)
+            else:
+                a_tok = act_quant(x)[0]
         route_pos = torch.empty((m, topk), device=dev, dtype=torch.int32)
         sorted_ids, sorted_w, expert_ids, num_valid, _, _ = ops.moe_sorting_ck(
             ids, wts, global_num_experts, None, None, ops.SORT_UNIT, expert_mask,
@@ -236,8 +259,14 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             expert_ids = ops.relabel_tiles(expert_ids, expert_map)
         cap = sorted_ids.shape[0]
         a_sorted, _ = ops.gather_rows(a_tok, sorted_ids, num_valid, cap)
-        common = dict(kind=_cabi.GEMM_BF16, sorted_expert_ids=expert_ids, num_valid=num_valid,
+        common = dict(kind=_cabi.GEMM_MXFP4 if native else _cabi.GEMM_BF16,
+                      sorted_expert_ids=expert_ids, num_valid=num_valid,
                       sorted_ids=sorted_ids, sorted_weights=sorted_w, num_tokens=m, topk=topk)
+        if native:
+            gemm1 = dict(b=w1, a_scale=ops.mx_sf_layout(a_sf, cap, sorted_ids, num_valid),
+                         b_scale=sfb1)
+        else:
+            gemm1 = dict(b=w1_d)
         # ---- GEMM1, activation, second quantisation ------------------------------------------
         if static:
             g1 = torch.empty((cap, n1), device=dev, dtype=torch.float32)
@@ -252,15 +281,20 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
             ops._count()
         else:
             g1 = torch.empty((cap, n1), device=dev, dtype=out_dtype)
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1_d, c=g1, **common)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, c=g1, **gemm1, **common)
+            want = dict(want_codes=True, want_deq=False, want_sf=True) if native else {}
             if activation == "silu":
-                act = act_quant(g1, gated=True, limit=limit)[0]
+                q2 = act_quant(g1, gated=True, limit=limit, **want)
             else:
                 activated = torch.empty((cap, inter), device=dev, dtype=out_dtype)
                 apply_activation(activation, True, activated, g1, None, limit,
                                  activation_situ_beta, activation_situ_linear_beta,
                                  rows_dev=num_valid)
-                act = act_quant(activated)[0]
+                q2 = act_quant(activated, **want)
+            if native:
+                gemm2 = dict(a=q2[1], b=w2, a_scale=ops.mx_sf_layout(q2[3], cap), b_scale=sfb2)
+            else:
+                gemm2 = dict(a=q2[0], b=w2_d)
         # ---- GEMM2 and the sum over the routes ------------------------------------------------
         if static:
             g2 = torch.empty((cap, model_dim), device=dev, dtype=torch.float32)
@@ -285,8 +319,8 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
         else:
             routes = (torch.zeros if expert_map is not None else torch.empty)(
                 (m, topk, model_dim), device=dev, dtype=out_dtype)
-            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2_d,
-                             c=routes.view(m * topk, model_dim), scatter=True, **common)
+            ops.grouped_gemm(epilogue=_cabi.EPI_STORE, c=routes.view(m * topk, model_dim),
+                             scatter=True, **gemm2, **common)
             if no_combine:
                 out[begin:end].copy_(routes)
             else:

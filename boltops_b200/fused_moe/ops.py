@@ -39,6 +39,11 @@ def _require_cuda(*tensors):
             raise ValueError("boltops_b200 kernels need CUDA tensors (there is no CPU path)")
 
 
+def sort_launches(lib, m: int, topk: int, num_experts: int) -> int:
+    """Kernels one sort launches: one CTA does everything for small inputs, three kernels else."""
+    return 1 if lib.bolt_moe_sort_workspace_bytes(m, topk, num_experts) <= 16 else 3
+
+
 def ceil_to(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
@@ -449,16 +454,27 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
                  sorted_weights: Optional[torch.Tensor] = None, sm_count: int = 0,
                  act_alpha: float = 1.0, act_beta: float = 0.0,
                  act_limit: Optional[float] = None, segments: Optional[torch.Tensor] = None,
-                 num_segments: Optional[torch.Tensor] = None) -> None:
+                 num_segments: Optional[torch.Tensor] = None,
+                 a_pad_row: Optional[int] = None) -> None:
     """One grouped expert GEMM launch (see ``bolt_grouped_gemm``).  With ``segments`` (from
-    ``moe_sorting_ck(..., segment_rows=PAIR_SEGMENT_ROWS)``) the tile-pair schedule runs."""
+    ``moe_sorting_ck(..., segment_rows=PAIR_SEGMENT_ROWS)``) the tile-pair schedule runs.  With
+    ``a_pad_row`` the row operand ``a`` is in TOKEN order and the kernel gathers its rows through
+    ``sorted_ids`` (padding positions read row ``a_pad_row``)."""
     lib = _cabi.load()
     args = _cabi.GemmArgs()
     args.kind = kind
     args.epilogue = epilogue
-    args.capacity = a.shape[0]
+    if a_pad_row is not None:
+        assert a.stride(1) == 1 and sorted_ids is not None
+        args.a_gather = 1
+        args.a_rows = a.shape[0]
+        args.a_pad_row = a_pad_row
+        args.a_row_bytes = a.stride(0) * a.element_size()
+        args.capacity = sorted_ids.shape[0]
+    else:
+        args.capacity = a.shape[0]
     args.n = b.shape[1]
-    args.k = b.shape[2]
+    args.k = a.shape[1]            # (packed 4-bit weights hold two K elements per byte)
     args.num_experts = b.shape[0]
     args.a = ptr(a)
     args.b = ptr(b)

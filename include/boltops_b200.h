@@ -64,11 +64,15 @@ enum bolt_gemm_kind {
   BOLT_GEMM_INT8_CHANNEL = 3, /* int8, per-row activation / per-output-channel weight   */
   BOLT_GEMM_FP8_CHANNEL = 4,  /* e4m3, per-row activation / per-output-channel weight   */
   BOLT_GEMM_INT8_BLOCK = 5,   /* int8, [128,128] weight blocks, 1x128 activation groups */
-  BOLT_GEMM_MXFP8 = 6         /* e4m3 with one E8M0 byte per 32 K elements on both operands,
+  BOLT_GEMM_MXFP8 = 6,        /* e4m3 with one E8M0 byte per 32 K elements on both operands,
                                  applied by the tensor core; a_scale / b_scale carry BYTE
                                  arrays in the tiled layout of bolt_mx_sf_layout; plain
                                  epilogue or the gated activation + MX re-quantisation
                                  (BOLT_EPI_SILU_MUL_QUANT); k a multiple of 128            */
+  BOLT_GEMM_MXFP4 = 7         /* e4m3 rows x PACKED e2m1 weights ([E, n, k/2] bytes, low nibble
+                                 first, 32-byte aligned), one E8M0 byte per 32 K elements on
+                                 both operands in the same tiled layout as BOLT_GEMM_MXFP8;
+                                 plain epilogue, k a multiple of 128                        */
 };
 
 /* grouped-GEMM schedules */
@@ -354,7 +358,8 @@ int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* ou
  * bolt_mx4_act_quant: x [rows, cols] (or [rows, 2*cols] = [gate | up] with gated != 0: SiLU(gate)
  *   * up, optional clamp, rounded through bf16) -> e4m3 per 1 x 128 group with the power-of-two
  *   scale at or above max(amax, 1e-10)/448 (mode 0) or with *static_scale (mode 1; e4m3 input is
- *   taken as already quantised); deq (decoded values), codes, scales [rows, cols/128] optional.
+ *   taken as already quantised); deq (decoded values), codes, scales [rows, cols/128] and sf32
+ *   (the scale's E8M0 byte repeated per 32 elements, [rows, cols/32]) optional.
  * bolt_fp8_group_decode: codes [rows, cols] * scales [rows, cols/group] -> out.
  * bolt_mx4_swiglu_static: g1 fp32 [capacity, 2*inter] in sorted rows -> decoded e4m3 of
  *   swigluoai(g1 * a1_scale + bias[expert]) [* row_weight] / a2_scale, [capacity, inter].
@@ -365,7 +370,7 @@ int bolt_mxfp4_decode(const uint8_t* packed, const uint8_t* scales, int64_t rows
                       void* out, int out_dtype, void* stream);
 int bolt_mx4_act_quant(const void* x, int x_dtype, int64_t rows, int cols, int gated,
                        int has_limit, float limit, int mode, const float* static_scale, void* deq,
-                       int deq_dtype, uint8_t* codes, float* scales, void* stream);
+                       int deq_dtype, uint8_t* codes, float* scales, uint8_t* sf32, void* stream);
 int bolt_fp8_group_decode(const uint8_t* codes, const float* scales, int64_t rows, int cols,
                           int group, void* out, int out_dtype, void* stream);
 int bolt_mx4_swiglu_static(const float* g1, const int32_t* sorted_expert_ids,
@@ -439,9 +444,61 @@ typedef struct bolt_gemm_args {
   int max_segments;
   const int32_t* segments;
   const int32_t* num_segments;
+  /* Gathered row operand (plain kinds, single-tile schedule).  With a_gather != 0, `a` is NOT in
+     sorted order: it is the token-order matrix [a_rows, k] (a_row_bytes between rows, 0 = dense),
+     and sorted position p reads row sorted_ids[p] & 0xFFFFFF, or row a_pad_row where that id is
+     not a token (id >= num_tokens: tile padding; the row should hold zeros).  a_scale stays in
+     sorted order.  The reference gathers the same way, by pointer arithmetic inside its kernel
+     (boltops/fused_moe/triton/moe_op.py:1479,1611-1615).                                      */
+  int a_gather;
+  int a_rows;
+  int a_pad_row;
+  int64_t a_row_bytes;
 } bolt_gemm_args;
 
 int bolt_grouped_gemm(const bolt_gemm_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * One whole layer in one call.  Replaces fused_experts_impl
+ * (boltops/fused_moe/triton/fused_moe.py:1200-1777) for its common variant: gated SiLU,
+ * combined [num_tokens, model_dim] output, unquantised bf16 / f16 hidden_states, experts in
+ * bf16 / f16, fp8 / int8 with [128,128] blocks or fp8 / int8 per channel; optional biases,
+ * expert mask (expert parallelism) and router weight applied on the input.  Same kernels and
+ * the same arithmetic as driving bolt_moe_sort_ck, bolt_quant_scatter_rows / bolt_gather_rows,
+ * bolt_grouped_gemm (twice) and bolt_moe_gather_sum one by one; the point is the host cost of
+ * a decode-sized layer: one foreign call and one workspace instead of one of each per kernel.
+ * The workspace (bolt_moe_layer_workspace_bytes(), 256-byte aligned) is scratch: nothing in it
+ * has to be initialised and nothing survives the call.  out may alias hidden_states.
+ */
+typedef struct bolt_layer_args {
+  int kind;                    /* enum bolt_gemm_kind, BF16 .. INT8_BLOCK                    */
+  int x_dtype;                 /* BOLT_BF16 / BOLT_F16                                        */
+  int out_dtype;               /* output and intermediate dtype (BF16 / F16 / F32)            */
+  int num_tokens, topk;
+  int hidden, inter, model_dim;        /* w1 [E, 2*inter, hidden], w2 [E, model_dim, inter]   */
+  int num_experts;             /* experts in w1 / w2 (local experts under a mask)             */
+  int global_num_experts;      /* range of topk_ids                                           */
+  const void* hidden_states;   /* [num_tokens, hidden]                                        */
+  const void* w1;
+  const void* w2;
+  const float* w1_scale;       /* block: [E, 2*inter/128, hidden/128]; channel: [E, 2*inter]  */
+  const float* w2_scale;
+  const void* b1;              /* optional [E, 2*inter]                                       */
+  const void* b2;              /* optional [E, model_dim]                                     */
+  int bias_dtype;
+  int apply_router_weight_on_input;
+  const float* topk_weights;   /* [num_tokens, topk] fp32                                     */
+  const int32_t* topk_ids;     /* [num_tokens, topk]                                          */
+  const int32_t* expert_mask;  /* optional [global_num_experts]: 1 = expert is local          */
+  float routed_scaling_factor;
+  void* out;                   /* [num_tokens, model_dim] in out_dtype                        */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;             /* optional, as in bolt_gemm_args                              */
+} bolt_layer_args;
+
+size_t bolt_moe_layer_workspace_bytes(const bolt_layer_args* args);
+int bolt_moe_layer(const bolt_layer_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -52,6 +52,25 @@ def test_gemm_args_struct_matches_header(tmp_path):
         assert getattr(_cabi.GemmArgs, f).offset == off, f
 
 
+def test_layer_args_struct_matches_header(tmp_path):
+    from boltops_b200 import _cabi
+    fields = [f[0] for f in _cabi.LayerArgs._fields_]
+    prog = ['#include <stdio.h>', '#include <stddef.h>',
+            f'#include "{ROOT / "include" / "boltops_b200.h"}"', "int main(void){",
+            'printf("%zu\\n", sizeof(bolt_layer_args));']
+    prog += [f'printf("%zu\\n", offsetof(bolt_layer_args, {f}));' for f in fields]
+    prog += ["return 0;}"]
+    src = tmp_path / "abi_layer.c"
+    src.write_text("\n".join(prog))
+    exe = tmp_path / "abi_layer"
+    subprocess.run(["gcc", str(src), "-o", str(exe)], check=True)
+    nums = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True,
+                                           check=True).stdout.split()]
+    assert nums[0] == ctypes.sizeof(_cabi.LayerArgs)
+    for f, off in zip(fields, nums[1:]):
+        assert getattr(_cabi.LayerArgs, f).offset == off, f
+
+
 def test_workspace_query_is_host_only(lib):
     assert lib.bolt_moe_sort_workspace_bytes(64, 2, 8) == 16          # single-CTA path
     big = lib.bolt_moe_sort_workspace_bytes(16384, 8, 128)

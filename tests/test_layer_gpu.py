@@ -385,3 +385,68 @@ def test_layer_tile_pair_schedule(monkeypatch, kind):
                              expert_map=emap.cuda(), global_num_experts=e, **loc)
         total += _finish(part).float()
     assert O.rel_l2(total, outs["pairs"].float()) <= 1e-2
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8_block", "int8_block", "int8_channel", "fp8_channel"])
+def test_layer_one_call_equals_kernel_by_kernel(monkeypatch, kind):
+    """The native one-call layer (sort, row placement, both GEMMs and the combine enqueued by one
+    C-ABI call) and the kernel-by-kernel Python orchestration give bit-identical outputs: plain
+    call, biases + expert mask, router weight on the input (top-1), in place."""
+    from boltops_b200.fused_moe import fused_experts, layer, ops
+    m, e, topk, h, i = 77, 8, 2, 512, 256
+    g = torch.Generator().manual_seed(31)
+    hidden = torch.randn(m, h, generator=g).bfloat16()
+    m1 = torch.randn(e, 2 * i, h, generator=g) * 0.05
+    m2 = torch.randn(e, h, i, generator=g) * 0.05
+    wts, ids = O.make_routing(m, e, topk, 12)
+    if kind == "bf16":
+        w1, w2, kw = m1.bfloat16(), m2.bfloat16(), {}
+    elif kind == "fp8_block":
+        w1, w1s = O.quantize_weight_block_fp8(m1)
+        w2, w2s = O.quantize_weight_block_fp8(m2)
+        kw = dict(use_fp8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128])
+    elif kind == "int8_block":
+        def qi(wm):
+            v = wm.view(wm.shape[0], wm.shape[1] // 128, 128, wm.shape[2] // 128, 128)
+            s = v.abs().amax(dim=(2, 4), keepdim=True).clamp(min=1e-10) / 127.0
+            return ((v / s).round().clamp(-128, 127).to(torch.int8).view_as(wm),
+                    s.view(wm.shape[0], wm.shape[1] // 128, wm.shape[2] // 128))
+        w1, w1s = qi(m1)
+        w2, w2s = qi(m2)
+        kw = dict(use_int8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128])
+    else:
+        w1, w1s = O.quantize_weight_channel_int8(m1)
+        w2, w2s = O.quantize_weight_channel_int8(m2)
+        if kind == "fp8_channel":
+            w1, w2 = (w1.float() * 3).to(FP8), (w2.float() * 3).to(FP8)
+            kw = dict(use_fp8_w8a8=True, per_channel_quant=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda())
+        else:
+            kw = dict(use_int8_w8a8=True, per_channel_quant=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda())
+    args = _dev(hidden, w1, w2, wts, ids)
+    emap = torch.full((e,), -1, dtype=torch.int32)
+    emap[2:6] = torch.arange(4, dtype=torch.int32)
+    b1 = (torch.randn(4, 2 * i, generator=g) / 4).bfloat16().cuda()
+    b2 = (torch.randn(4, h, generator=g) / 4).bfloat16().cuda()
+    loc = {k: (v[2:6] if k.endswith("_scale") else v) for k, v in kw.items()}
+    variants = [
+        (args, kw),
+        ((args[0], args[1][2:6], args[2][2:6], args[3], args[4]),
+         dict(loc, expert_map=emap.cuda(), global_num_experts=e, b1=b1, b2=b2,
+              routed_scaling_factor=2.5)),
+        ((args[0], args[1], args[2], args[3][:, :1].contiguous(), args[4][:, :1].contiguous()),
+         dict(kw, apply_router_weight_on_input=True)),
+    ]
+    for a, k in variants:
+        outs = []
+        for one_call in (True, False):
+            monkeypatch.setattr(layer, "_ONE_CALL", one_call)
+            before = ops.launch_count()
+            outs.append(_finish(fused_experts(*a, **k)))
+            assert ops.launch_count() - before >= 5
+        assert torch.equal(outs[0], outs[1])
+    monkeypatch.setattr(layer, "_ONE_CALL", True)
+    x = args[0].clone()
+    out = fused_experts(x, *args[1:], inplace=True, **kw)
+    assert out.data_ptr() == x.data_ptr()
+    monkeypatch.setattr(layer, "_ONE_CALL", False)
+    assert torch.equal(_finish(out), _finish(fused_experts(*args, **kw)))

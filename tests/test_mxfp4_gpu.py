@@ -12,9 +12,13 @@ FP8 = torch.float8_e4m3fn
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("path", ["native", "decoded"])
 @pytest.mark.parametrize("case", MXFP4_CASES)
-def test_public_mxfp4_matches_reference_cpu_statement(monkeypatch, case):
-    from boltops_b200.fused_moe import fused_experts, ops
+def test_public_mxfp4_matches_reference_cpu_statement(monkeypatch, case, path):
+    """path: the tensor core's block-scaled kind on the packed weights (taken by the dynamic recipe
+    on 16-bit input; the other cases run the decoded form either way), or decoded operands."""
+    from boltops_b200.fused_moe import fused_experts, mxfp4, ops
+    monkeypatch.setattr(mxfp4, "_NATIVE", path == "native")
     c = load_mxfp4_case(case)
     if c["chunk"]:
         monkeypatch.setenv("TRITON_FUSED_MOE_CHUNK_SIZE", str(c["chunk"]))
@@ -75,6 +79,38 @@ def test_mxfp4_weight_decode_and_quantiser_bit_exact():
     same = (deq.float().cpu() == ref)
     assert same.float().mean() > 0.995
     torch.testing.assert_close(deq.float().cpu(), ref, rtol=0.13, atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(300, 1024, 512, 768, 8, 4), (64, 7168, 256, 7168, 16, 8)])
+def test_mxfp4_packed_weights_on_the_tensor_core_equal_decoded_operands(monkeypatch, shape):
+    """The block-scaled kind on packed e2m1 weights against the 16-bit kind on decoded operands:
+    the same exact products summed in fp32, so the layer outputs agree to accumulation order;
+    the quantiser's four equal E8M0 bytes are the power-of-two group scale."""
+    from boltops_b200.fused_moe import fused_experts, mxfp4
+    m, hidden, inter, model_dim, experts, topk = shape
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn(m, hidden, generator=g)).bfloat16().cuda()
+    w1 = torch.randint(0, 256, (experts, 2 * inter, hidden // 2), dtype=torch.uint8, generator=g).cuda()
+    w2 = torch.randint(0, 256, (experts, model_dim, inter // 2), dtype=torch.uint8, generator=g).cuda()
+    s1 = torch.randint(116, 122, (experts, 2 * inter, hidden // 32), dtype=torch.uint8, generator=g).cuda()
+    s2 = torch.randint(116, 122, (experts, model_dim, inter // 32), dtype=torch.uint8, generator=g).cuda()
+    logits = torch.randn(m, experts, generator=g)
+    wts, ids = torch.topk(torch.softmax(logits, -1), topk)
+    outs = {}
+    for path in ("native", "decoded"):
+        monkeypatch.setattr(mxfp4, "_NATIVE", path == "native")
+        outs[path] = fused_experts(x, w1, w2, wts.cuda(), ids.int().cuda(), use_mxfp4_w4a8=True,
+                                   w1_scale=s1, w2_scale=s2, block_shape=[1, 32]).float()
+    torch.cuda.synchronize()
+    from boltops_b200.fused_moe import ops
+    ops.check_device_status(x.device)
+    assert torch.isfinite(outs["native"]).all()
+    err = (outs["native"] - outs["decoded"]).norm() / outs["decoded"].norm()
+    assert err < 2e-3, float(err)
+    _, codes, scales, sf = mxfp4.act_quant(x, want_codes=True, want_deq=False, want_sf=True)
+    assert torch.equal(torch.exp2(sf.float() - 127.0),
+                       scales.repeat_interleave(4, dim=1))
 
 
 def test_mxfp4_argument_contract_matches_reference_messages():
