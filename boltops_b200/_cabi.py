@@ -60,8 +60,7 @@ class GemmArgs(C.Structure):
         ("act_has_limit", C.c_int),
         ("schedule", C.c_int), ("max_segments", C.c_int),
         ("segments", C.c_void_p), ("num_segments", C.c_void_p),
-        ("a_gather", C.c_int), ("a_rows", C.c_int), ("a_pad_row", C.c_int),
-        ("a_row_bytes", C.c_int64),
+        ("a_gather", C.c_int), ("a_rows", C.c_int), ("a_row_bytes", C.c_int64),
     ]
 
 
@@ -112,7 +111,8 @@ _SIGNATURES = {
                                   C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "bolt_quant_scatter_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
-                                          C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+                                          C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int,
+                                          C.c_void_p]),
     "bolt_mx_quant_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_float,
                                      C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_int, C.c_void_p]),
@@ -147,6 +147,7 @@ _SIGNATURES = {
                                       C.c_int64, C.c_int, C.c_int, C.c_float, C.c_void_p]),
     "bolt_grouped_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "bolt_moe_layer_workspace_bytes": (C.c_size_t, [C.POINTER(LayerArgs)]),
+    "bolt_moe_layer_kernel_count": (C.c_int, [C.POINTER(LayerArgs)]),
     "bolt_moe_layer": (C.c_int, [C.POINTER(LayerArgs), C.c_void_p]),
 }
 

@@ -101,9 +101,11 @@ struct GemmParams {
   uint32_t idesc;
   int group_m;
   // gathered row operand: A is in TOKEN order; sorted position p reads row (sorted_ids[p] & 0xFFFFFF),
-  // or row a_pad_row when that id is not a token (tile padding)
+  // or zeros when that id is not a token (tile padding)
   int a_gather;
-  int a_pad_row;
+  const void* a_base;
+  int a_row_units;   // 16-byte units between rows
+  int k_bytes;
   // tile-pair schedule: work list of the sort (runs of at most 256 rows of one expert)
   const int32_t* segments;     // [max_segments][4] = {expert, first row, rows, -}
   const int32_t* num_segments;
@@ -356,10 +358,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int lane = threadIdx.x & 31;
   // CTA pair: rank 0 issues the MMAs and owns the "full" / "tempty" barriers of the pair
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  // row operand gathered by warps 2 and 3: their 64 threads arrive on "full" beside the producer
+  const bool gathered = !PAIR && p.a_gather != 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, gathered ? 65 : 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -463,52 +467,6 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (++s == kStages) { s = 0; ph ^= 1; }
           }
         }
-      } else if (!PAIR && p.a_gather) {
-        // Row operand gathered from token order: lane l owns rows 4l .. 4l+3 of the tile and
-        // brings them with one four-row gather per K block (32 gathers fill the 128 x 128-byte
-        // stage: the swizzle follows the shared-memory address, so four rows at 512-byte steps
-        // land where the one-box copy would put them).  Lane 0 also waits for the stage, arms
-        // the barrier and issues the weight boxes.
-        int s = 0;
-        uint32_t ph = 0, kbi = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
-          const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
-          const int expert = p.expert_ids[tc.m_blk];
-          if (expert < 0 || expert >= p.num_experts) continue;
-          const int4 sid4 =
-              *reinterpret_cast<const int4*>(p.sorted_ids + (int64_t)tc.m_blk * kBM + 4 * lane);
-          int r[4] = {sid4.x & 0xFFFFFF, sid4.y & 0xFFFFFF, sid4.z & 0xFFFFFF, sid4.w & 0xFFFFFF};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) r[j] = r[j] < p.num_tokens ? r[j] : p.a_pad_row;
-          int brow[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            brow[j] = GATED ? ((j & 1) ? p.n_half : 0) + tc.n_blk * 128 + (j >> 1) * 64
-                            : tc.n_blk * 256 + j * 64;
-          for (int kb = 0; kb < p.num_kb; ++kb) {
-            int okl = 1;
-            if (lane == 0) okl = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-            if (!ok) break;
-            const uint32_t full = bar_full + 8 * s;
-            const uint32_t sa = smem_base + s * kStageBytes;
-            if (lane == 0) {
-              mbar_expect_tx(full, kStageBytes + (BS ? 512 : 0));
-              if (BS)
-                bulk_load(smem_u32(as_ring) + (kbi % kScaleSlots) * 512,
-                          p.a_scale + (int64_t)kb * p.a_scale_ld + tc.m_blk * kBM, 512, full);
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                tma_load_3d(sa + kABytes + j * (kBBytes / 4), &tma_b, full, kb * kBKElems, brow[j],
-                            expert);
-            }
-            ++kbi;
-            __syncwarp();
-            tma_gather4_2d(sa + lane * 512, &tma_a, full, kb * kBKElems, r[0], r[1], r[2], r[3]);
-            if (++s == kStages) { s = 0; ph ^= 1; }
-          }
-        }
       } else if (lane == 0) {
         int s = 0;
         uint32_t ph = 0, kbi = 0;
@@ -534,7 +492,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (!ok) break;
             const uint32_t full = bar_full + 8 * s;
             const uint32_t sa = smem_base + s * kStageBytes;
-            mbar_expect_tx(full, kStageBytes + (BS ? 512 : 0));
+            mbar_expect_tx(full, (gathered ? kBBytes : kStageBytes) + (BS ? 512 : 0));
             if (BS) {
               // activation scales of this K block for the tile's 128 rows.  Ring slot reuse is
               // safe without a barrier of its own: this copy is issued at most kStages K blocks
@@ -543,7 +501,7 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                         p.a_scale + (int64_t)kb * p.a_scale_ld + tc.m_blk * kBM, 512, full);
               ++kbi;
             }
-            tma_load_2d(sa, &tma_a, full, kb * kBKElems, tc.m_blk * kBM);
+            if (!gathered) tma_load_2d(sa, &tma_a, full, kb * kBKElems, tc.m_blk * kBM);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               tma_load_3d(sa + kABytes + j * (kBBytes / 4), &tma_b, full, kb * kBKElems, brow[j],
@@ -552,6 +510,49 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           }
         }
       }
+    } else if (warp >= 2 && gathered) {
+      // ---------------- row operand gathered from token order (warps 2 and 3) ----------------
+      // Sorted position p of the tile reads token row sorted_ids[p] & 0xFFFFFF; positions that
+      // only pad the tile read nothing and are filled with zeros.  64 threads bring the
+      // 128 rows x 128 bytes of a K block with sixteen 16-byte asynchronous copies each (eight
+      // neighbouring threads cover one row's 128 bytes), placed where the 128-byte-swizzled box
+      // copy would put them: 16-byte column c of row r at r * 128 + ((c ^ (r & 7)) << 4).  The
+      // copies of a thread arrive on the stage's "full" barrier when they have landed.
+      const int t = (int)threadIdx.x - 64;
+      const int c16 = t & 7;
+      const int r0 = t >> 3;                                  // rows r0 + 8 i, i = 0..15
+      const uint32_t dst0 = (uint32_t)r0 * 128u + (uint32_t)((c16 ^ (r0 & 7)) << 4);
+      const uint8_t* abase = static_cast<const uint8_t*>(p.a_base) + c16 * 16;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
+        const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
+        const int expert = p.expert_ids[tc.m_blk];
+        if (expert < 0 || expert >= p.num_experts) continue;
+        int roff[16];                          // row offset in 16-byte units, -1 = padding
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int tok = p.sorted_ids[(int64_t)tc.m_blk * kBM + r0 + 8 * i] & 0xFFFFFF;
+          roff[i] = tok < p.num_tokens ? tok * p.a_row_units : -1;
+        }
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 5);
+          if (!ok) break;
+          const uint32_t sa = smem_base + s * kStageBytes + dst0;
+          const int kbyte = kb * 128 + c16 * 16;
+          const bool in_k = kbyte < p.k_bytes;                // reduction tail: zeros
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const bool live = in_k && roff[i] >= 0;
+            cp_async_16(sa + i * 1024, abase + (live ? (int64_t)roff[i] * 16 + kb * 128 : 0),
+                        live ? 16u : 0u);
+          }
+          cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+      cp_async_wait_all();
     } else if (warp == 1) {
       // ------------------------------ MMA issuer --------------------------------
       if (PAIR && lane == 0 && cta_rank == 0) {
@@ -616,6 +617,9 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
             if (!ok) break;
             tc_fence_after();
+            // gathered rows were written through the generic proxy, the MMA reads through the
+            // asynchronous one
+            if (gathered) fence_async_smem();
             const uint32_t sa = smem_base + s * kStageBytes;
             const uint64_t adesc = make_smem_desc(sa);
             const uint64_t bdesc = make_smem_desc(sa + kABytes);
@@ -1470,9 +1474,11 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   if (gather) {
     BOLT_REQUIRE(!pair && !mx, "grouped_gemm: the gathered row operand needs the single-tile "
                                "schedule of the plain kinds");
-    BOLT_REQUIRE(a->sorted_ids != nullptr && a->a_rows > 0 && a->a_pad_row >= 0 &&
-                     a->a_pad_row < a->a_rows,
-                 "grouped_gemm: gathered row operand needs sorted_ids, a_rows and a pad row inside it");
+    BOLT_REQUIRE(a->sorted_ids != nullptr && a->a_rows >= a->num_tokens && a->a_rows > 0,
+                 "grouped_gemm: gathered row operand needs sorted_ids and a_rows >= num_tokens");
+    BOLT_REQUIRE((a->a_row_bytes > 0 ? a->a_row_bytes : (int64_t)a->k * elem) / 16 * a->a_rows <
+                     (1ll << 31),
+                 "grouped_gemm: gathered row operand larger than 32 GiB");
     BOLT_REQUIRE(a->a_row_bytes == 0 ||
                      (a->a_row_bytes % 16 == 0 && a->a_row_bytes >= (int64_t)a->k * elem),
                  "grouped_gemm: a_row_bytes must be a multiple of 16 and cover a row");
@@ -1489,11 +1495,11 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   const cuuint32_t bk = is16 ? 64 : 128;
   CUtensorMap ma, mb;
   {
-    // gathered row operand: the tensor is the token-order matrix, the box one row high
+    // (with a gathered row operand this map is not used by the kernel)
     cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)(gather ? a->a_rows : a->capacity)};
     cuuint64_t strides[1] = {gather && a->a_row_bytes > 0 ? (cuuint64_t)a->a_row_bytes
                                                           : (cuuint64_t)a->k * elem};
-    cuuint32_t box[2] = {bk, gather ? 1u : (cuuint32_t)kBM};
+    cuuint32_t box[2] = {bk, (cuuint32_t)kBM};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(&ma, dt, 2, const_cast<void*>(a->a), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1583,7 +1589,9 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     if (pair) p.group_m = (p.group_m + 1) / 2;   // the unit of the tile order is a pair of row tiles
   }
   p.a_gather = gather ? 1 : 0;
-  p.a_pad_row = a->a_pad_row;
+  p.a_base = a->a;
+  p.a_row_units = (int)((a->a_row_bytes > 0 ? a->a_row_bytes : (int64_t)a->k * elem) / 16);
+  p.k_bytes = a->k * elem;
   p.segments = a->segments;
   p.num_segments = a->num_segments;
   p.max_segments = a->max_segments;

@@ -330,12 +330,14 @@ __device__ __forceinline__ void zero_pad_rows(const int32_t* __restrict__ sorted
                                               int64_t num_tokens, int valid, int row_vecs,
                                               int groups, QTy* __restrict__ dst,
                                               float* __restrict__ dst_scale, int64_t dst_scale_ld,
-                                              int pad_warp, int pad_warps) {
+                                              int pad_warp, int pad_warps, bool token_order) {
   using VOut = Vec<QTy, VEC>;
   const int lane = threadIdx.x & 31;
   VOut zero;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) zero.v[i] = 0;
+  // token_order: the codes live in token order and the GEMM fills padding positions with zeros
+  // itself; only the padding positions' scales are written here
   for (int row0 = pad_warp * 32; row0 < valid; row0 += pad_warps * 32) {
     const int row = row0 + lane;
     const bool is_pad = row < valid && (sorted_ids[row] & 0xFFFFFF) >= num_tokens;
@@ -343,8 +345,10 @@ __device__ __forceinline__ void zero_pad_rows(const int32_t* __restrict__ sorted
     while (mask) {
       const int r = row0 + __ffs(mask) - 1;
       mask &= mask - 1;
-      VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)r * row_vecs;
-      for (int i = lane; i < row_vecs; i += 32) d[i] = zero;
+      if (!token_order) {
+        VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)r * row_vecs;
+        for (int i = lane; i < row_vecs; i += 32) d[i] = zero;
+      }
       for (int g = lane; g < groups; g += 32) dst_scale[(int64_t)g * dst_scale_ld + r] = 0.f;
     }
   }
@@ -362,7 +366,7 @@ __global__ void __launch_bounds__(256) k_quant_scatter(
     const int32_t* __restrict__ route_pos, int slots, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_valid, int capacity,
     typename QTraits<QT>::type* __restrict__ dst, float* __restrict__ dst_scale,
-    int64_t dst_scale_ld, int64_t quant_blocks) {
+    int64_t dst_scale_ld, int64_t quant_blocks, int token_order) {
   // a thread owns W input vectors = EPT consecutive elements (EPT = 16: one 16-byte store per
   // route); tpg threads share a group
   constexpr int VEC = 16 / sizeof(TIn);
@@ -398,6 +402,11 @@ __global__ void __launch_bounds__(256) k_quant_scatter(
         o.v[w * VEC + i] = quant_one<QT, POW2>(to_f32(v[w].v[i]), inv);
     const bool leader = (unit_in_row % tpg) == 0;
     const int grp = unit_in_row / tpg;
+    if (token_order) {
+      // codes once, in token order (the GEMM gathers rows itself); only scales go to the routes
+      reinterpret_cast<VOut*>(dst)[token * row_units + unit_in_row] = o;
+      if (!leader) return;
+    }
     // eight routes at a time: all positions first, then the independent stores
     for (int k0 = 0; k0 < slots; k0 += 8) {
       int pos[8];
@@ -407,7 +416,8 @@ __global__ void __launch_bounds__(256) k_quant_scatter(
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (pos[j] < 0 || pos[j] >= capacity) continue;
-        reinterpret_cast<VOut*>(dst)[(int64_t)pos[j] * row_units + unit_in_row] = o;
+        if (!token_order)
+          reinterpret_cast<VOut*>(dst)[(int64_t)pos[j] * row_units + unit_in_row] = o;
         if (leader) dst_scale[(int64_t)grp * dst_scale_ld + pos[j]] = scale;
       }
     }
@@ -418,7 +428,7 @@ __global__ void __launch_bounds__(256) k_quant_scatter(
   zero_pad_rows<typename QTraits<QT>::type, EPT>(
       sorted_ids, num_tokens, min(*num_valid, capacity), row_units, row_units / tpg, dst,
       dst_scale, dst_scale_ld, (int)(blockIdx.x - quant_blocks) * 8 + (threadIdx.x >> 5),
-      pad_blocks * 8);
+      pad_blocks * 8, token_order != 0);
 }
 
 // Same for groups that span up to 8 x 32 vectors (per-token quantisation of mid-sized rows): one
@@ -429,7 +439,7 @@ __global__ void __launch_bounds__(256) k_quant_scatter_warp(
     const int32_t* __restrict__ route_pos, int slots, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_valid, int capacity,
     typename QTraits<QT>::type* __restrict__ dst, float* __restrict__ dst_scale,
-    int64_t dst_scale_ld, int quant_blocks) {
+    int64_t dst_scale_ld, int quant_blocks, int token_order) {
   constexpr int VEC = 16 / sizeof(TIn);
   using VIn = Vec<TIn, VEC>;
   using VOut = Vec<typename QTraits<QT>::type, VEC>;
@@ -468,6 +478,12 @@ __global__ void __launch_bounds__(256) k_quant_scatter_warp(
             out[j].v[e] = quant_one<QT, POW2>(to_f32(cache[j].v[e]), inv);
         }
       }
+      if (token_order) {
+        VOut* d = reinterpret_cast<VOut*>(dst) + token * row_vecs + grp * nvec;
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+          if (lane + j * 32 < nvec) d[lane + j * 32] = out[j];
+      }
       // lane k holds the position of route k (slots <= 32 per pass)
       for (int k0 = 0; k0 < slots; k0 += 32) {
         const int mine = (k0 + lane < slots) ? __ldg(route_pos + token * slots + k0 + lane) : -1;
@@ -475,10 +491,12 @@ __global__ void __launch_bounds__(256) k_quant_scatter_warp(
         for (int k = 0; k < nk; ++k) {
         const int pos = __shfl_sync(0xffffffffu, mine, k);
         if (pos < 0 || pos >= capacity) continue;
-        VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)pos * row_vecs + grp * nvec;
+        if (!token_order) {
+          VOut* d = reinterpret_cast<VOut*>(dst) + (int64_t)pos * row_vecs + grp * nvec;
 #pragma unroll
-        for (int j = 0; j < NV; ++j)
-          if (lane + j * 32 < nvec) d[lane + j * 32] = out[j];
+          for (int j = 0; j < NV; ++j)
+            if (lane + j * 32 < nvec) d[lane + j * 32] = out[j];
+        }
         if (lane == 0) dst_scale[(int64_t)grp * dst_scale_ld + pos] = scale;
         }
       }
@@ -488,17 +506,20 @@ __global__ void __launch_bounds__(256) k_quant_scatter_warp(
   const int pad_blocks = gridDim.x - quant_blocks;
   zero_pad_rows<typename QTraits<QT>::type, VEC>(
       sorted_ids, num_tokens, min(*num_valid, capacity), row_vecs, groups, dst, dst_scale,
-      dst_scale_ld, ((int)blockIdx.x - quant_blocks) * 8 + (threadIdx.x >> 5), pad_blocks * 8);
+      dst_scale_ld, ((int)blockIdx.x - quant_blocks) * 8 + (threadIdx.x >> 5), pad_blocks * 8,
+      token_order != 0);
 }
 
 template <typename TIn, int QT, bool POW2>
 int launch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group,
                          const int32_t* route_pos, int slots, const int32_t* sorted_ids,
                          const int32_t* num_valid, int capacity, void* dst, float* dst_scale,
-                         int64_t dst_scale_ld, cudaStream_t st) {
+                         int64_t dst_scale_ld, int token_order, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(TIn);
   const int tpg = group / VEC;
-  const int pad_blocks = sm_count_of_current_device() * 4;
+  // (with codes in token order the padding job is a few scale words per row: fewer blocks)
+  const int pad_blocks = token_order ? sm_count_of_current_device() / 2
+                                     : sm_count_of_current_device() * 4;
   if (tpg > 32 || (tpg & (tpg - 1)) != 0) {
     // a warp per group, groups strided over a capped grid
     const int64_t num_groups = num_tokens * (cols / group);
@@ -509,7 +530,7 @@ int launch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group,
     k_quant_scatter_warp<TIn, QT, POW2, 8><<<(unsigned)(qb + pad_blocks), 256, 0, st>>>(
         static_cast<const TIn*>(x), num_tokens, cols, group, route_pos, slots, sorted_ids,
         num_valid, capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale,
-        dst_scale_ld, (int)qb);
+        dst_scale_ld, (int)qb, token_order);
     BOLT_LAUNCH_CHECK();
     return BOLT_OK;
   }
@@ -524,12 +545,12 @@ int launch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group,
     k_quant_scatter<TIn, QT, POW2, W16><<<(unsigned)(quant_blocks + pad_blocks), 256, 0, st>>>(
         static_cast<const TIn*>(x), num_tokens, cols, group / 16, route_pos, slots, sorted_ids,
         num_valid, capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale,
-        dst_scale_ld, quant_blocks);
+        dst_scale_ld, quant_blocks, token_order);
   } else {
     k_quant_scatter<TIn, QT, POW2, 1><<<(unsigned)(quant_blocks + pad_blocks), 256, 0, st>>>(
         static_cast<const TIn*>(x), num_tokens, cols, tpg, route_pos, slots, sorted_ids,
         num_valid, capacity, static_cast<typename QTraits<QT>::type*>(dst), dst_scale,
-        dst_scale_ld, quant_blocks);
+        dst_scale_ld, quant_blocks, token_order);
   }
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
@@ -539,7 +560,8 @@ template <typename TIn>
 int dispatch_quant_scatter(const void* x, int64_t num_tokens, int cols, int group, int q_dtype,
                            int power2, const int32_t* route_pos, int slots,
                            const int32_t* sorted_ids, const int32_t* num_valid, int capacity,
-                           void* dst, float* dst_scale, int64_t dst_scale_ld, cudaStream_t st) {
+                           void* dst, float* dst_scale, int64_t dst_scale_ld, int token_order,
+                           cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(TIn);
   const int tpg = group / VEC;
   BOLT_REQUIRE(group % VEC == 0 && tpg >= 1 && tpg <= 8 * 32,
@@ -548,7 +570,7 @@ int dispatch_quant_scatter(const void* x, int64_t num_tokens, int cols, int grou
 #define BOLT_QS(QT, P2)                                                                         \
   return launch_quant_scatter<TIn, QT, P2>(x, num_tokens, cols, group, route_pos, slots,        \
                                            sorted_ids, num_valid, capacity, dst, dst_scale,     \
-                                           dst_scale_ld, st)
+                                           dst_scale_ld, token_order, st)
   if (q_dtype == BOLT_FP8_E4M3) {
     if (power2) BOLT_QS(BOLT_FP8_E4M3, true);
     BOLT_QS(BOLT_FP8_E4M3, false);
@@ -739,7 +761,8 @@ extern "C" int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_t
                                        const int32_t* route_pos, int slots,
                                        const int32_t* sorted_ids, const int32_t* num_valid_ids,
                                        int capacity, void* dst, float* dst_scale,
-                                       int64_t dst_scale_ld, void* stream) {
+                                       int64_t dst_scale_ld, int codes_in_token_order,
+                                       void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(num_tokens >= 0 && cols > 0 && capacity >= 0 && slots > 0,
@@ -761,15 +784,16 @@ extern "C" int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_t
     case BOLT_BF16:
       return dispatch_quant_scatter<__nv_bfloat16>(x, num_tokens, cols, group, q_dtype, power2,
                                                    route_pos, slots, sorted_ids, num_valid_ids,
-                                                   capacity, dst, dst_scale, dst_scale_ld, st);
+                                                   capacity, dst, dst_scale, dst_scale_ld,
+                                                   codes_in_token_order, st);
     case BOLT_F16:
       return dispatch_quant_scatter<__half>(x, num_tokens, cols, group, q_dtype, power2,
                                             route_pos, slots, sorted_ids, num_valid_ids, capacity,
-                                            dst, dst_scale, dst_scale_ld, st);
+                                            dst, dst_scale, dst_scale_ld, codes_in_token_order, st);
     case BOLT_F32:
       return dispatch_quant_scatter<float>(x, num_tokens, cols, group, q_dtype, power2, route_pos,
                                            slots, sorted_ids, num_valid_ids, capacity, dst,
-                                           dst_scale, dst_scale_ld, st);
+                                           dst_scale, dst_scale_ld, codes_in_token_order, st);
     default:
       set_error("quant_scatter: unsupported input dtype %d", x_dtype);
       return BOLT_ERR_INVALID;

@@ -57,6 +57,20 @@ STAGE_TIMER: Optional[StageTimer] = None
 # BOLTOPS_B200_ONE_CALL=0 drives the kernels one by one from Python (same results; used by the
 # tests to hold the two orchestrations against each other)
 _ONE_CALL = os.environ.get("BOLTOPS_B200_ONE_CALL", "1") != "0"
+# 16-bit and block-scaled experts: GEMM1 can gather its rows from token order itself (the 16-bit
+# input as it is, 8-bit codes written once per token instead of once per route) instead of
+# reading a copy in sorted order; same results.  It wins while the sorted layout is mostly tile
+# padding and loses once experts have more than a tile of rows (the extra copy instructions slow
+# the accumulator promotion down), so it is used up to _GATHER_MAX_AVG_ROWS routes per expert --
+# the rule of bolt_moe_layer.  BOLTOPS_B200_GATHER=0 / 1 forces it off / on.
+_GATHER = {"0": False, "1": True}.get(os.environ.get("BOLTOPS_B200_GATHER", ""), None)
+_GATHER_MAX_AVG_ROWS = 64
+
+
+def _use_gather(routes: int, experts: int) -> bool:
+    if _GATHER is not None:
+        return _GATHER
+    return routes <= _GATHER_MAX_AVG_ROWS * experts
 
 
 class _Stage:
@@ -347,8 +361,7 @@ def fused_experts_impl(
         args.workspace, args.workspace_bytes = workspace.data_ptr(), need
         with _cabi.on_device(dev):
             _cabi.check(lib.bolt_moe_layer(args, _cabi.stream_of(hidden_states)))
-        ops._count(ops.sort_launches(lib, num_tokens, topk, global_num_experts)
-                   + (4 if not quantised or block_mode else 6))
+        ops._count(lib.bolt_moe_layer_kernel_count(args))
         return out
 
     for begin in range(0, num_tokens, chunk):
@@ -376,14 +389,18 @@ def fused_experts_impl(
 
         # ---- A1: quantise once per token, then gather into sorted rows --------------------
         a_scale = None
+        gemm1_rows = {}
         if quantised and x.dtype in (torch.float16, torch.bfloat16) and not x.is_contiguous():
             x = x.contiguous()                      # the quantisers read dense rows
         if quantised and block_mode and x.dtype in (torch.float16, torch.bfloat16):
             # quantise each token once and write it straight to its sorted rows
+            in_gemm = segments is None and _use_gather(m * topk, global_num_experts)
             with _Stage("quant_a1"):
                 a_sorted, a_scale = ops.quant_scatter_rows(
                     x, 128, q_dtype, route_pos, sorted_ids, num_valid, cap,
-                    scale_ue8m0=use_ue8m0)
+                    scale_ue8m0=use_ue8m0, token_order=in_gemm)
+            if in_gemm:
+                gemm1_rows = dict(a_gather=True)   # a_sorted is [m, H] in token order
         elif quantised:
             # per-token scales: quantise, then gather (a row-centric gather writes the sorted rows
             # faster than a token-centric scatter of whole rows; measured 0.131 vs 0.157 ms at
@@ -401,6 +418,10 @@ def fused_experts_impl(
                     x_s = x_s.float()
             with _Stage("gather"):
                 a_sorted, a_scale = ops.gather_rows(x_q, sorted_ids, num_valid, cap, x_s)
+        elif (segments is None and _use_gather(m * topk, global_num_experts)
+              and x.stride(1) == 1 and x.data_ptr() % 16 == 0
+              and (x.stride(0) * x.element_size()) % 16 == 0):
+            a_sorted, gemm1_rows = x, dict(a_gather=True)   # GEMM1 reads the token rows itself
         else:
             with _Stage("gather"):
                 a_sorted, _ = ops.gather_rows(x, sorted_ids, num_valid, cap)
@@ -419,7 +440,8 @@ def fused_experts_impl(
               ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, b=w1, c=act,
                              a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
                              c_scale=act_scale, c_scale_ld=cap, mid_dtype=mid_dtype,
-                             mul_routed_weight=apply_router_weight_on_input, **common)
+                             mul_routed_weight=apply_router_weight_on_input, **gemm1_rows,
+                             **common)
         else:
             if fused_silu:
                 act_f = torch.empty((cap, act_dim), device=dev, dtype=mid_dtype)
@@ -427,13 +449,15 @@ def fused_experts_impl(
                   ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL, a=a_sorted, b=w1, c=act_f,
                                  a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
                                  mid_dtype=mid_dtype,
-                                 mul_routed_weight=apply_router_weight_on_input, **common)
+                                 mul_routed_weight=apply_router_weight_on_input, **gemm1_rows,
+                                 **common)
             else:
                 c1 = torch.empty((cap, n1), device=dev, dtype=mid_dtype)
                 with _Stage("gemm1"):
                   ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, b=w1, c=c1,
                                  a_scale=a_scale, a_scale_ld=cap, b_scale=w1_scale_c, bias=b1,
-                                 mul_routed_weight=apply_router_weight_on_input, **common)
+                                 mul_routed_weight=apply_router_weight_on_input, **gemm1_rows,
+                                 **common)
                 act_f = torch.empty((cap, act_dim), device=dev, dtype=mid_dtype)
                 apply_activation(activation, is_gated, act_f, c1, gemm1_alpha, gemm1_limit,
                                  activation_situ_beta, activation_situ_linear_beta,

@@ -248,23 +248,25 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_valid: torch.Te
 
 def quant_scatter_rows(x: torch.Tensor, group: int, q_dtype: torch.dtype, route_pos: torch.Tensor,
                        sorted_ids: torch.Tensor, num_valid: torch.Tensor, capacity: int,
-                       scale_ue8m0: bool = False):
+                       scale_ue8m0: bool = False, token_order: bool = False):
     """Quantise ``x`` [M, cols] per 1 x ``group`` block and write every token to the sorted rows
     ``route_pos[m, k] >= 0`` in one pass.  Returns ``(dst [capacity, cols], dst_scale
-    [cols/group, capacity])``; tile-padding rows are zero."""
+    [cols/group, capacity])``; tile-padding rows are zero.  ``token_order``: for a GEMM that
+    gathers its rows itself -- ``dst`` is ``[M, cols]``, every token once in token order; the
+    scales still go to the sorted positions."""
     _require_cuda(x, route_pos, sorted_ids, num_valid)
     lib = _cabi.load()
     x = x.contiguous()
     m, cols = x.shape
     assert route_pos.dtype == torch.int32 and route_pos.is_contiguous() and route_pos.shape[0] == m
-    dst = torch.empty((capacity, cols), dtype=q_dtype, device=x.device)
+    dst = torch.empty((m if token_order else capacity, cols), dtype=q_dtype, device=x.device)
     dst_scale = torch.empty((cols // group, capacity), dtype=torch.float32, device=x.device)
     with _cabi.on_device(x.device):
         check(lib.bolt_quant_scatter_rows(ptr(x), dtype_code(x.dtype), m, cols, group,
                                           dtype_code(q_dtype), int(scale_ue8m0), ptr(route_pos),
                                           route_pos.shape[1], ptr(sorted_ids), ptr(num_valid),
                                           capacity, ptr(dst), ptr(dst_scale), capacity,
-                                          stream_of(x)))
+                                          int(token_order), stream_of(x)))
     _count()
     return dst, dst_scale
 
@@ -455,20 +457,19 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
                  act_alpha: float = 1.0, act_beta: float = 0.0,
                  act_limit: Optional[float] = None, segments: Optional[torch.Tensor] = None,
                  num_segments: Optional[torch.Tensor] = None,
-                 a_pad_row: Optional[int] = None) -> None:
+                 a_gather: bool = False) -> None:
     """One grouped expert GEMM launch (see ``bolt_grouped_gemm``).  With ``segments`` (from
     ``moe_sorting_ck(..., segment_rows=PAIR_SEGMENT_ROWS)``) the tile-pair schedule runs.  With
-    ``a_pad_row`` the row operand ``a`` is in TOKEN order and the kernel gathers its rows through
-    ``sorted_ids`` (padding positions read row ``a_pad_row``)."""
+    ``a_gather`` the row operand ``a`` is in TOKEN order and the kernel gathers its rows through
+    ``sorted_ids`` (padding positions read zeros)."""
     lib = _cabi.load()
     args = _cabi.GemmArgs()
     args.kind = kind
     args.epilogue = epilogue
-    if a_pad_row is not None:
+    if a_gather:
         assert a.stride(1) == 1 and sorted_ids is not None
         args.a_gather = 1
         args.a_rows = a.shape[0]
-        args.a_pad_row = a_pad_row
         args.a_row_bytes = a.stride(0) * a.element_size()
         args.capacity = sorted_ids.shape[0]
     else:

@@ -266,13 +266,16 @@ int bolt_gather_rows(const void* src, int num_tokens, int row_bytes, int64_t src
  * bolt_moe_sort_ck, [num_tokens, slots]); rows below num_valid_ids[0] that hold no token are
  * zero-filled.  dst [capacity, cols] 8-bit, dst_scale [cols/group, dst_scale_ld] fp32 (one
  * group per row: a plain [capacity] vector).
+ * codes_in_token_order != 0: for a GEMM that gathers its rows itself (bolt_gemm_args.a_gather).
+ * dst is then [num_tokens, cols]: every token's codes once, in token order; the scales still go
+ * to the sorted positions (zeros for the padding positions).
  * Same arithmetic and the same reference functions as bolt_quant_rows.
  */
 int bolt_quant_scatter_rows(const void* x, int x_dtype, int64_t num_tokens, int cols, int group,
                             int q_dtype, int power2, const int32_t* route_pos, int slots,
                             const int32_t* sorted_ids, const int32_t* num_valid_ids,
                             int capacity, void* dst, float* dst_scale, int64_t dst_scale_ld,
-                            void* stream);
+                            int codes_in_token_order, void* stream);
 
 /* MX (microscaling) e4m3 quantisation with 1 x 32 groups and E8M0 exponent bytes.  Replaces
  * mxfp8_e4m3_quantize (boltops/fused_moe/triton/mxfp8.py:122-175): byte =
@@ -445,14 +448,13 @@ typedef struct bolt_gemm_args {
   const int32_t* segments;
   const int32_t* num_segments;
   /* Gathered row operand (plain kinds, single-tile schedule).  With a_gather != 0, `a` is NOT in
-     sorted order: it is the token-order matrix [a_rows, k] (a_row_bytes between rows, 0 = dense),
-     and sorted position p reads row sorted_ids[p] & 0xFFFFFF, or row a_pad_row where that id is
-     not a token (id >= num_tokens: tile padding; the row should hold zeros).  a_scale stays in
+     sorted order: it is the token-order matrix [a_rows >= num_tokens, k] (a_row_bytes between
+     rows, a multiple of 16; 0 = dense), and sorted position p reads row sorted_ids[p] & 0xFFFFFF,
+     or zeros where that id is not a token (id >= num_tokens: tile padding).  a_scale stays in
      sorted order.  The reference gathers the same way, by pointer arithmetic inside its kernel
      (boltops/fused_moe/triton/moe_op.py:1479,1611-1615).                                      */
   int a_gather;
   int a_rows;
-  int a_pad_row;
   int64_t a_row_bytes;
 } bolt_gemm_args;
 
@@ -497,6 +499,8 @@ typedef struct bolt_layer_args {
   int32_t* status;             /* optional, as in bolt_gemm_args                              */
 } bolt_layer_args;
 
+/* kernels one bolt_moe_layer call with these arguments launches (-1: invalid arguments) */
+int bolt_moe_layer_kernel_count(const bolt_layer_args* args);
 size_t bolt_moe_layer_workspace_bytes(const bolt_layer_args* args);
 int bolt_moe_layer(const bolt_layer_args* args, void* stream);
 

@@ -327,3 +327,93 @@ def test_gemm_tile_pairs_equal_single_tiles(kind_name, m, e, topk):
             assert torch.equal(s1, s2)
         if dtype == torch.bfloat16 and not case.get("scatter"):
             assert (c2 != sentinel).any()
+
+
+@pytest.mark.parametrize("kind_name", ["bf16", "fp8_block", "int8_channel"])
+@pytest.mark.parametrize("m,e,topk,wide", [(1500, 8, 2, False), (33, 16, 4, True), (300, 16, 4, False)])
+def test_gemm_rows_gathered_by_the_kernel_equal_sorted_rows(kind_name, m, e, topk, wide):
+    """The row operand read from TOKEN order through the sorted ids (16-byte asynchronous copies
+    by two warps of the kernel, padding positions zero-filled) against the same rows copied into
+    sorted order first: the
+    tiles in shared memory must be identical, so every output bit is.  `wide`: token rows that
+    are slices of a wider buffer (a_row_bytes)."""
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    torch.manual_seed(m + e)
+    inter, k = 256, 512
+    pr = _pair_problem(m, e, topk, 5 + m)
+    x = (torch.randn(m, k) / 2).bfloat16().cuda()
+
+    def token_order(t):
+        """the token rows, optionally as slices of a wider buffer"""
+        if not wide:
+            return t
+        buf = torch.zeros((m, k + 64), dtype=torch.uint8 if t.element_size() == 1
+                          else t.dtype, device="cuda")
+        view = buf[:, :k]
+        view[:m] = t.view(buf.dtype) if t.element_size() == 1 else t
+        return view.view(t.dtype) if t.element_size() == 1 else view
+
+    extra = {}
+    if kind_name == "bf16":
+        kind = _cabi.GEMM_BF16
+        w1 = (torch.randn(e, 2 * inter, k) / 8).bfloat16()
+        a_sorted, _ = ops.gather_rows(x, pr["s_ids"], pr["nv"], pr["cap"])
+        a_tok = token_order(x)
+    elif kind_name == "fp8_block":
+        kind = _cabi.GEMM_FP8_BLOCK
+        w1 = (torch.randn(e, 2 * inter, k) * 40).clamp(-448, 448).to(FP8)
+        a_sorted, a_scale = ops.quant_scatter_rows(x, 128, FP8, pr["pos"], pr["s_ids"], pr["nv"],
+                                                   pr["cap"])
+        xq, _ = ops.per_block_quant(x, 128, FP8)
+        a_tok = token_order(xq)
+        extra = dict(a_scale=a_scale, a_scale_ld=pr["cap"],
+                     b_scale=(torch.rand(e, 2 * inter // 128, k // 128) * 1e-2 + 1e-3).cuda())
+    else:
+        kind = _cabi.GEMM_INT8_CHANNEL
+        w1 = torch.randint(-127, 128, (e, 2 * inter, k), dtype=torch.int8)
+        xq, xs = ops.per_token_quant(x, quant_dtype=torch.int8)
+        a_sorted, a_scale = ops.gather_rows(xq, pr["s_ids"], pr["nv"], pr["cap"], xs)
+        a_tok = token_order(xq)
+        extra = dict(a_scale=a_scale, b_scale=(torch.rand(e, 2 * inter) * 1e-2 + 1e-3).cuda())
+    common = dict(kind=kind, sorted_expert_ids=pr["s_e"], num_valid=pr["nv"], b=w1.cuda(),
+                  sorted_ids=pr["s_ids"], sorted_weights=pr["s_w"], num_tokens=m, topk=topk,
+                  **extra)
+    cap = pr["cap"]
+    for case in [dict(epilogue=_cabi.EPI_STORE, shape=(cap, 2 * inter)),
+                 dict(epilogue=_cabi.EPI_SILU_MUL, mid_dtype=torch.bfloat16, shape=(cap, inter)),
+                 dict(epilogue=_cabi.EPI_STORE, scatter=True, mul_routed_weight=True,
+                      shape=(m * topk, 2 * inter))]:
+        shape = case.pop("shape")
+        outs = []
+        for a, kw in ((a_sorted, {}), (a_tok, dict(a_gather=True))):
+            c = torch.full(shape, -12345.0, dtype=torch.bfloat16, device="cuda")
+            ops.grouped_gemm(a=a, c=c, **kw, **case, **common)
+            torch.cuda.synchronize()
+            ops.check_device_status(c.device)
+            outs.append(c)
+        assert (outs[1] != -12345.0).any()
+        assert torch.equal(outs[0], outs[1]), f"{kind_name} {case['epilogue']} differs"
+
+
+def test_gemm_gathered_rows_with_reduction_and_column_tails():
+    """k = 336 (not a multiple of the 64-element K block) and n = 384: the gathered copies must
+    zero-fill the reduction tail exactly as the box copy does."""
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    m, e, topk, n, k = 200, 4, 2, 384, 336
+    torch.manual_seed(9)
+    pr = _sorted_problem(m, e, topk, 11)
+    x = (torch.randn(m, k) / 4).bfloat16().cuda()
+    b = (torch.randn(e, n, k) / 8).bfloat16().cuda()
+    a_sorted, _ = ops.gather_rows(x, pr["s_ids"], pr["nv"], pr["cap"])
+    outs = []
+    for a, kw in ((a_sorted, {}), (x, dict(a_gather=True))):
+        c = torch.full((pr["cap"], n), -12345.0, dtype=torch.bfloat16, device="cuda")
+        ops.grouped_gemm(kind=_cabi.GEMM_BF16, epilogue=_cabi.EPI_STORE, a=a, b=b, c=c,
+                         sorted_expert_ids=pr["s_e"], num_valid=pr["nv"], sorted_ids=pr["s_ids"],
+                         sorted_weights=pr["s_w"], num_tokens=m, topk=topk, **kw)
+        torch.cuda.synchronize()
+        ops.check_device_status(c.device)
+        outs.append(c)
+    assert torch.equal(outs[0], outs[1])

@@ -442,7 +442,7 @@ def test_layer_one_call_equals_kernel_by_kernel(monkeypatch, kind):
             monkeypatch.setattr(layer, "_ONE_CALL", one_call)
             before = ops.launch_count()
             outs.append(_finish(fused_experts(*a, **k)))
-            assert ops.launch_count() - before >= 5
+            assert ops.launch_count() - before >= 4
         assert torch.equal(outs[0], outs[1])
     monkeypatch.setattr(layer, "_ONE_CALL", True)
     x = args[0].clone()
