@@ -377,6 +377,40 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # roofline bookkeeping
 # ---------------------------------------------------------------------------
+def host_memory_near_gpu(local_rank):
+    """Before the pinned host buffers are allocated: prefer the NUMA node the GPU hangs off, so
+    that eight ranks do not all stage their copies through node 0.  Reads the node from sysfs
+    (PCI address from NVML), narrows the CPU affinity to that node's CPUs when the process is
+    allowed on any of them, and asks for that node's memory (set_mempolicy, MPOL_PREFERRED).
+    Touches only this process; every step is optional and reported in the JSON line."""
+    info = dict(gpu_node=None, cpus_bound=0, mempolicy=False)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local_rank)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bdf = bus.lower()[-12:]                    # 0000:1b:00.0
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return info
+        info["gpu_node"] = node
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["cpus_bound"] = len(allowed)
+        import ctypes
+        mask = ctypes.c_ulong(1 << node)
+        rc = ctypes.CDLL(None, use_errno=True).syscall(238, 1, ctypes.byref(mask), 64)  # x86-64
+        info["mempolicy"] = rc == 0
+    except Exception as exc:                       # no NVML, no sysfs, other architecture ...
+        info["error"] = type(exc).__name__
+    return info
+
+
 def gemm1_algorithmic(cfg, m, active_experts):
     """Algorithmic bytes and flops of one GEMM1 launch (gate/up GEMM + fused epilogue)."""
     K, H, I = cfg["K"], cfg["H"], cfg["I"]
@@ -500,11 +534,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--measure-peaks", action="store_true",
                     help="measure the library GEMM peaks (bf16, e4m3, int8) on cuda:0 and exit")
-    ap.add_argument("--ep-chunks", type=int, default=2,
+    ap.add_argument("--ep-direct", type=int, default=1,
+                    help="N > 1: 1 = exchange over peer memory (no collective call and no host "
+                         "synchronisation on the data path), 0 = NCCL all-to-all")
+    ap.add_argument("--ep-chunks", type=int, default=1,
                     help="N > 1: token chunks of the pipelined dispatch / return exchange (1 = serial)")
     ap.add_argument("--ep-comm-sms", type=int, default=16,
                     help="N > 1: SMs left to the exchange kernels while GEMMs run beside them "
                          "(also the CTA limit given to NCCL)")
+    ap.add_argument("--no-numa", action="store_true",
+                    help="N > 1: leave CPU affinity and memory policy of the ranks as they are")
     ap.add_argument("--graph", action="store_true",
                     help="1 GPU only: replay the layer from a CUDA graph in the device-resident timing")
     args = ap.parse_args()
@@ -567,6 +606,7 @@ def main():
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.ep_comm_sms))
         dist.init_process_group("nccl", device_id=device)
 
+    numa = host_memory_near_gpu(local_rank) if world > 1 and not args.no_numa else None
     E = cfg["E"]
     per_rank = E // world
     my_experts = list(range(rank * per_rank, (rank + 1) * per_rank))
@@ -584,11 +624,14 @@ def main():
         # every rank brings the same number of tokens here, so decode-sized batches may take the
         # replicated-token path (no host round trips); the headline batch stays on the dispatch
         ep.replicate_below = 4096
+        ep.direct_max_tokens = m if args.ep_direct else 0
         ep.pipeline_chunks = args.ep_chunks
         ep.comm_sms = args.ep_comm_sms
         ep.topk_hint = cfg["K"]
-        config["ep_chunks"] = ep.num_chunks(m)
-        config["ep_comm_sms"] = args.ep_comm_sms
+        config["ep_exchange"] = "peer memory" if args.ep_direct else "nccl all-to-all"
+        if not args.ep_direct:
+            config["ep_chunks"] = ep.num_chunks(m)
+            config["ep_comm_sms"] = args.ep_comm_sms
 
         def step(h, w, i):
             return ep.forward(h, w1, w2, w, i, **kwargs)
@@ -737,6 +780,8 @@ def main():
         step(hidden, wts, ids)
         ep_stats = dict(ep.last_stats)
         ep_stats["local_stage_ms"] = layer.STAGE_TIMER.summary()
+        if ep._direct_failed is not None:
+            ep_stats["peer_memory_unavailable"] = ep._direct_failed
         layer.STAGE_TIMER = None
         ep.profile = False
         # load balance: routes each rank's experts receive from the whole job (the Zipf workload
@@ -774,6 +819,8 @@ def main():
                          h2d_bytes_per_step=(hidden_h.numel() * 2 + wts_h.numel() * 4
                                              + ids_h.numel() * 4) * world,
                          d2h_bytes_per_step=out_host.numel() * 2 * world))
+    if numa is not None:
+        line["e2e"]["host_numa_rank0"] = numa
     if ep_stats is not None:
         line["ep_rank0"] = ep_stats
     if ep_check is not None:

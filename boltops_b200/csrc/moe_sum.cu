@@ -71,6 +71,60 @@ __global__ void __launch_bounds__(256) k_gather_sum(const T* __restrict__ src,
   }
 }
 
+// The same sum, written to other ranks' memory: row m belongs to segment s = m / seg_rows (the
+// rank the token came from), rows q = m % seg_rows >= hdr[2 s] are not live and are skipped, and
+// the result goes to row hdr[2 s + 1] + q of the region at seg_ptrs[s] (plain stores; the region
+// may be peer memory).  first_row = index of row 0 of this call within the whole batch.
+template <typename T, typename TOut, int VEC>
+__global__ void __launch_bounds__(256) k_gather_sum_to_peers(
+    const T* __restrict__ src, const int32_t* __restrict__ pos, int64_t num_tokens, int slots, int n,
+    float scale, int64_t seg_rows, const int64_t* __restrict__ seg_ptrs,
+    const int32_t* __restrict__ hdr, int64_t first_row) {
+  using V = Vec<T, VEC>;
+  using VO = Vec<TOut, VEC>;
+  const int nvec = n / VEC;
+  const int64_t total = num_tokens * nvec;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = idx / nvec;
+    const int c = (int)(idx - m * nvec) * VEC;
+    const int64_t g = first_row + m;
+    const int64_t s = g / seg_rows, q = g - s * seg_rows;
+    if (q >= hdr[2 * s]) continue;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    for (int j = 0; j < slots; ++j) {
+      const int r = __ldg(pos + m * slots + j);
+      if (r < 0) continue;
+      const V v = *reinterpret_cast<const V*>(src + (int64_t)r * n + c);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] += to_f32(v.v[i]);
+    }
+    VO o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o.v[i] = from_f32<TOut>(acc[i] * scale);
+    TOut* out = reinterpret_cast<TOut*>(seg_ptrs[s]);
+    *reinterpret_cast<VO*>(out + (hdr[2 * s + 1] + q) * (int64_t)n + c) = o;
+  }
+}
+
+template <typename T, typename TOut>
+int launch_gather_sum_to_peers(const void* src, const int32_t* pos, int64_t num_tokens, int slots,
+                               int n, float scale, int64_t seg_rows, const int64_t* seg_ptrs,
+                               const int32_t* hdr, int64_t first_row, cudaStream_t st) {
+  constexpr int VEC = 16 / (sizeof(T) > sizeof(TOut) ? sizeof(T) : sizeof(TOut));
+  const int64_t total = num_tokens * (n / VEC);
+  if (total == 0) return BOLT_OK;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 32;
+  if (blocks > cap) blocks = cap;
+  k_gather_sum_to_peers<T, TOut, VEC><<<(unsigned)blocks, 256, 0, st>>>(
+      static_cast<const T*>(src), pos, num_tokens, slots, n, scale, seg_rows, seg_ptrs, hdr, first_row);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
 template <typename T, typename TOut>
 int launch_gather_sum(const void* src, const int32_t* pos, void* out, int64_t num_tokens,
                       int slots, int n, float scale, cudaStream_t st) {
@@ -173,5 +227,32 @@ extern "C" int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* po
     case BOLT_F32:
       return dispatch_gather_out<float>(src, pos, out, out_dtype, num_tokens, slots, n, scale, st);
     default: set_error("gather_sum: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
+  }
+}
+
+extern "C" int bolt_moe_gather_sum_to_peers(const void* src, int dtype, const int32_t* pos,
+                                            int64_t num_tokens, int slots, int n, float scale,
+                                            int64_t seg_rows, const int64_t* seg_ptrs,
+                                            const int32_t* hdr, int64_t first_row, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(num_tokens >= 0 && slots > 0 && n > 0 && seg_rows > 0 && first_row >= 0,
+               "gather_sum_to_peers: bad shape");
+  BOLT_REQUIRE(num_tokens == 0 || (src && pos && seg_ptrs && hdr), "gather_sum_to_peers: null pointer");
+  BOLT_REQUIRE(reinterpret_cast<uintptr_t>(src) % 16 == 0, "gather_sum_to_peers: src must be 16-byte aligned");
+  switch (dtype) {
+    case BOLT_BF16:
+      BOLT_REQUIRE(n % 8 == 0, "gather_sum_to_peers: n must be a multiple of 8");
+      return launch_gather_sum_to_peers<__nv_bfloat16, __nv_bfloat16>(
+          src, pos, num_tokens, slots, n, scale, seg_rows, seg_ptrs, hdr, first_row, st);
+    case BOLT_F16:
+      BOLT_REQUIRE(n % 8 == 0, "gather_sum_to_peers: n must be a multiple of 8");
+      return launch_gather_sum_to_peers<__half, __half>(src, pos, num_tokens, slots, n, scale,
+                                                        seg_rows, seg_ptrs, hdr, first_row, st);
+    case BOLT_F32:
+      BOLT_REQUIRE(n % 4 == 0, "gather_sum_to_peers: n must be a multiple of 4");
+      return launch_gather_sum_to_peers<float, float>(src, pos, num_tokens, slots, n, scale, seg_rows,
+                                                      seg_ptrs, hdr, first_row, st);
+    default: set_error("gather_sum_to_peers: unsupported dtype %d", dtype); return BOLT_ERR_INVALID;
   }
 }

@@ -384,3 +384,176 @@ extern "C" int bolt_ep_pack_rows(const void* data, int row_bytes, const float* s
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }
+
+
+// ---------------------------------------------------------------------------
+// Direct exchange over peer memory (expert parallelism without a collective library call on the
+// data path).  Every rank owns one exchange buffer with the same layout, mapped into all ranks
+// (peer pointers in a device table):
+//   [ header: per source rank {rows, first return row} ][ flags ][ receive region: world segments
+//     of seg_rows wire rows ][ return region: partial output rows in the owner's send order ]
+// A sender writes its wire rows for rank d into segment `me` of d's receive region with plain
+// 16-byte stores and leaves {rows, first return row} in d's header; the owner of the experts
+// later writes a token's partial output row straight into the sender's return region
+// (k_gather_sum_to_peers, moe_sum.cu).  Nothing here waits; ranks meet in k_ep_barrier.
+namespace bolt {
+namespace {
+
+constexpr int kMaxWorld = 64;
+
+// One warp per wire row, rows in send order (rank-major); segment boundaries from the per-rank
+// counts of the dispatch sort.
+__global__ void __launch_bounds__(256) k_ep_dispatch(
+    const uint4* __restrict__ data, int data_vecs, const float* __restrict__ scales, int groups,
+    const int32_t* __restrict__ ids, const float* __restrict__ wts, int topk,
+    const int32_t* __restrict__ send_ids, const int32_t* __restrict__ counts, int world, int me,
+    int64_t seg_rows, const int64_t* __restrict__ peers, int64_t hdr_off, int64_t recv_off,
+    int64_t wire_bytes, int32_t* __restrict__ status) {
+  __shared__ int starts[kMaxWorld + 1];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int d = 0; d < world; ++d) {
+      starts[d] = acc;
+      const int c = counts[d];
+      acc += c < 0 ? 0 : (c > seg_rows ? (int)seg_rows : c);
+      if ((c < 0 || c > seg_rows) && status != nullptr) atomicCAS(status, 0, 21);
+    }
+    starts[world] = acc;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int32_t* hdr = reinterpret_cast<int32_t*>(peers[d] + hdr_off) + 2 * me;
+    hdr[0] = starts[d + 1] - starts[d];
+    hdr[1] = starts[d];
+  }
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int sc_bytes = (groups * 4 + 15) & ~15, k_bytes = (topk * 4 + 15) & ~15;
+  const int64_t rows = starts[world];
+  for (int64_t i = warp; i < rows; i += warps) {
+    int d = 0;
+    while (d + 1 < world && i >= starts[d + 1]) ++d;
+    const int64_t q = i - starts[d];
+    const int64_t t = send_ids[i] & 0xFFFFFF;
+    uint8_t* o = reinterpret_cast<uint8_t*>(peers[d] + recv_off) + ((int64_t)me * seg_rows + q) * wire_bytes;
+    const uint4* src = data + t * data_vecs;
+    for (int v = lane; v < data_vecs; v += 32) reinterpret_cast<uint4*>(o)[v] = __ldg(src + v);
+    o += (int64_t)data_vecs * 16;
+    for (int g = lane; g < groups; g += 32) reinterpret_cast<float*>(o)[g] = scales[t * groups + g];
+    o += sc_bytes;
+    for (int k = lane; k < topk; k += 32) {
+      reinterpret_cast<int32_t*>(o)[k] = ids[t * topk + k];
+      reinterpret_cast<float*>(o + k_bytes)[k] = wts[t * topk + k];
+    }
+  }
+}
+
+// Receiver: dense top-k ids / weights of all segment rows; rows a segment does not hold get id -1
+// (no expert) so that the local layer ignores them.
+__global__ void __launch_bounds__(256) k_ep_unpack_routes(
+    const uint8_t* __restrict__ recv, int64_t wire_bytes, int64_t ids_off, int64_t wts_off, int topk,
+    int64_t seg_rows, int nseg, const int32_t* __restrict__ hdr, int32_t* __restrict__ ids,
+    float* __restrict__ wts) {
+  const int64_t total = (int64_t)nseg * seg_rows * topk;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / topk;
+    const int k = (int)(i - row * topk);
+    const int64_t s = row / seg_rows, q = row - s * seg_rows;
+    const bool live = q < hdr[2 * s];
+    const uint8_t* r = recv + row * wire_bytes;
+    ids[i] = live ? reinterpret_cast<const int32_t*>(r + ids_off)[k] : -1;
+    wts[i] = live ? reinterpret_cast<const float*>(r + wts_off)[k] : 0.f;
+  }
+}
+
+// All ranks meet: thread r tells rank r "rank `me` has reached `epoch`" (a flag in r's buffer) and
+// waits until rank r has said the same here.  Kernels before this launch are complete (stream
+// order), so their peer stores are performed before the flag is written; the fences order the
+// flag against them at system scope.  The wait is bounded (~1 s): on expiry the status word is
+// set and the kernel returns.
+__global__ void k_ep_barrier(const int64_t* __restrict__ peers, int world, int me, int64_t flag_off,
+                             int epoch, int32_t* __restrict__ status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  volatile int32_t* theirs = reinterpret_cast<volatile int32_t*>(peers[r] + flag_off) + me;
+  *theirs = epoch;
+  __threadfence_system();
+  volatile int32_t* mine = reinterpret_cast<volatile int32_t*>(peers[me] + flag_off) + r;
+  const long long t0 = clock64();
+  while (*mine - epoch < 0) {
+    if (clock64() - t0 > 2000000000ll) {
+      if (status != nullptr) atomicCAS(status, 0, 20);
+      break;
+    }
+    __nanosleep(100);
+  }
+  __threadfence_system();
+}
+
+}  // namespace
+}  // namespace bolt
+
+extern "C" int bolt_ep_dispatch_rows(const void* data, int row_bytes, const float* scales, int groups,
+                                     const int32_t* topk_ids, const float* topk_weights, int topk,
+                                     const int32_t* send_ids, const int32_t* counts, int world,
+                                     int me, int64_t max_rows, int64_t seg_rows,
+                                     const int64_t* peers, int64_t hdr_off, int64_t recv_off,
+                                     int64_t wire_bytes, int32_t* status, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "ep_dispatch: row_bytes must be a multiple of 16");
+  BOLT_REQUIRE(groups >= 0 && topk > 0 && max_rows >= 0 && seg_rows > 0, "ep_dispatch: bad sizes");
+  BOLT_REQUIRE(world > 0 && world <= kMaxWorld && me >= 0 && me < world, "ep_dispatch: bad rank");
+  BOLT_REQUIRE(wire_bytes >= bolt_ep_wire_row_bytes(row_bytes, groups, topk) && wire_bytes % 16 == 0,
+               "ep_dispatch: wire row too small");
+  BOLT_REQUIRE(hdr_off % 16 == 0 && recv_off % 16 == 0, "ep_dispatch: regions must be 16-byte aligned");
+  BOLT_REQUIRE(data && topk_ids && topk_weights && send_ids && counts && peers && (groups == 0 || scales),
+               "ep_dispatch: null pointer");
+  BOLT_REQUIRE(reinterpret_cast<uintptr_t>(data) % 16 == 0, "ep_dispatch: data must be 16-byte aligned");
+  int64_t blocks = (max_rows + 7) / 8;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  k_ep_dispatch<<<(unsigned)blocks, 256, 0, st>>>(
+      static_cast<const uint4*>(data), row_bytes / 16, scales, groups, topk_ids, topk_weights, topk,
+      send_ids, counts, world, me, seg_rows, peers, hdr_off, recv_off, wire_bytes, status);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+extern "C" int bolt_ep_unpack_routes(const void* recv, int64_t wire_bytes, int64_t ids_off,
+                                     int64_t wts_off, int topk, int64_t seg_rows, int nseg,
+                                     const int32_t* hdr, int32_t* topk_ids, float* topk_weights,
+                                     void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(recv && hdr && topk_ids && topk_weights, "ep_unpack: null pointer");
+  BOLT_REQUIRE(topk > 0 && seg_rows > 0 && nseg > 0 && wire_bytes % 4 == 0 && ids_off % 4 == 0 &&
+                   wts_off % 4 == 0,
+               "ep_unpack: bad layout");
+  const int64_t total = (int64_t)nseg * seg_rows * topk;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)sm_count_of_current_device() * 16;
+  if (blocks > cap) blocks = cap;
+  k_ep_unpack_routes<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(recv), wire_bytes,
+                                                       ids_off, wts_off, topk, seg_rows, nseg, hdr,
+                                                       topk_ids, topk_weights);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}
+
+extern "C" int bolt_ep_barrier(const int64_t* peers, int world, int me, int64_t flag_off, int epoch,
+                               int32_t* status, void* stream) {
+  using namespace bolt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BOLT_REQUIRE(peers != nullptr && world > 0 && world <= kMaxWorld && me >= 0 && me < world &&
+                   flag_off % 4 == 0,
+               "ep_barrier: bad arguments");
+  k_ep_barrier<<<1, kMaxWorld, 0, st>>>(peers, world, me, flag_off, epoch, status);
+  BOLT_LAUNCH_CHECK();
+  return BOLT_OK;
+}

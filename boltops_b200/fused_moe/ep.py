@@ -25,6 +25,138 @@ import torch
 import torch.distributed as dist
 
 
+def _a16(n: int) -> int:
+    return (n + 15) // 16 * 16
+
+
+def _a256(n: int) -> int:
+    return (n + 255) // 256 * 256
+
+
+def wire_layout(row_bytes: int, groups: int, topk: int):
+    """Byte offsets of the parts of a wire row: scales, ids, weights; total size."""
+    o_scale = _a16(row_bytes)
+    o_ids = o_scale + _a16(groups * 4)
+    o_w = o_ids + _a16(topk * 4)
+    return o_scale, o_ids, o_w, o_w + _a16(topk * 4)
+
+
+class DirectExchange:
+    """One rank's side of the exchange over peer memory (CUDA only, one process per GPU).
+
+    Every rank owns a buffer of the same layout that all ranks can address::
+
+        header  int32 [world][2]   {rows rank s sent me, first row of s's return region for me}
+        flags   int32 [world]      epochs of the barrier
+        receive world segments of seg_rows wire rows; segment s is written by rank s
+        return  partial output rows of MY tokens, in my send order, written by the experts' ranks
+
+    A step is three phases with a meeting of all ranks between them: ``dispatch`` (quantise,
+    write my wire rows into the owners' receive regions), ``experts`` (masked local layer over
+    everything received; its top-k combine writes each partial row straight into the sender's
+    return region), ``combine`` (sum a token's partial rows in ascending rank order).  Nothing
+    in a step reads device data on the host: counts and offsets stay in device memory, the
+    local layer always takes ``world * seg_rows`` rows and ignores those no rank sent.
+
+    Hazards between steps are covered by the two meetings of a step: a receive region is
+    rewritten only after every rank has passed the second meeting of the previous step (its
+    local layer is done), a return region only after the first meeting of this step (its
+    owner's final combine of the previous step is done).
+    """
+
+    def __init__(self, world: int, rank: int, num_experts: int, seg_rows: int, row_bytes: int,
+                 groups: int, topk: int, hidden: int, out_dtype: torch.dtype, device,
+                 code_dtype: torch.dtype):
+        self.world, self.rank, self.num_experts = world, rank, num_experts
+        self.per_rank = num_experts // world
+        self.seg_rows, self.row_bytes, self.groups, self.topk = seg_rows, row_bytes, groups, topk
+        self.hidden, self.out_dtype, self.code_dtype = hidden, out_dtype, code_dtype
+        self.device = torch.device(device)
+        self.o_scale, self.o_ids, self.o_w, self.wire_bytes = wire_layout(row_bytes, groups, topk)
+        self.back_rows = seg_rows * min(world, topk)
+        self.hdr_off = 0
+        self.flag_off = _a256(world * 8)
+        self.recv_off = self.flag_off + _a256(world * 4)
+        self.back_off = self.recv_off + _a256(world * seg_rows * self.wire_bytes)
+        self.total_bytes = self.back_off + _a256(
+            self.back_rows * hidden * torch.empty((), dtype=out_dtype).element_size())
+        self.buf = None
+        self.epoch = 0
+        self.meet = None          # callable: all ranks meet on the current stream
+        emap = torch.full((num_experts,), -1, dtype=torch.int32)
+        emap[rank * self.per_rank:(rank + 1) * self.per_rank] = torch.arange(self.per_rank,
+                                                                            dtype=torch.int32)
+        self.expert_map = emap.to(self.device)
+
+    def key(self):
+        return (self.seg_rows, self.row_bytes, self.groups, self.topk, self.hidden, self.out_dtype)
+
+    def attach(self, buf: torch.Tensor, peer_ptrs) -> None:
+        """``buf``: this rank's exchange buffer (uint8, ``total_bytes``, zeroed header and
+        flags); ``peer_ptrs``: base address of every rank's buffer, in rank order."""
+        assert buf.dtype == torch.uint8 and buf.numel() >= self.total_bytes and buf.is_cuda
+        assert buf.data_ptr() % 256 == 0 and len(peer_ptrs) == self.world
+        self.buf = buf
+        dev = self.device
+        self.peers = torch.tensor(list(peer_ptrs), dtype=torch.int64, device=dev)
+        self.back_ptrs = self.peers + self.back_off
+        self.hdr = buf[self.hdr_off:self.hdr_off + self.world * 8].view(torch.int32).view(
+            self.world, 2)
+        self.recv = buf[self.recv_off:self.recv_off + self.world * self.seg_rows
+                        * self.wire_bytes].view(self.world * self.seg_rows, self.wire_bytes)
+        esz = torch.empty((), dtype=self.out_dtype).element_size()
+        self.back = buf[self.back_off:self.back_off + self.back_rows * self.hidden * esz].view(
+            self.out_dtype).view(self.back_rows, self.hidden)
+
+    # -- the three phases ---------------------------------------------------------------------
+    def dispatch(self, hidden_states, topk_weights, topk_ids, quant):
+        """Plan, quantise (``quant(x) -> (codes, scales)`` or None) and write the wire rows.
+        Returns ``pos`` [M, world]: row of every partial result in the return region."""
+        from . import ops
+        m = hidden_states.shape[0]
+        assert m <= self.seg_rows, "more tokens than the exchange buffers were sized for"
+        routes = ops.ep_dest_ranks(topk_ids, self.num_experts, self.per_rank, self.world, 0)
+        dummy_w = torch.empty((m, self.world), dtype=torch.float32, device=self.device)
+        pos = torch.empty((m, self.world), dtype=torch.int32, device=self.device)
+        sorted_ids, _, _, _, counts, _ = ops.moe_sorting_ck(
+            routes, dummy_w, self.world, None, None, 1, None, alloc_moe_buf=False, route_pos=pos)
+        x, x_scale = quant(hidden_states) if quant is not None else (hidden_states, None)
+        ops.ep_dispatch_rows(x.contiguous(), x_scale, topk_ids.to(torch.int32).contiguous(),
+                             topk_weights.to(torch.float32).contiguous(), sorted_ids,
+                             counts[:self.world], self.rank, self.seg_rows, self.peers,
+                             self.hdr_off, self.recv_off, self.wire_bytes)
+        return pos
+
+    def experts(self, w1_local, w2_local, **kwargs):
+        """Masked local layer over every row of the receive region; partial rows go straight to
+        the return regions of the ranks that sent the tokens."""
+        from . import layer, ops
+        r_ids, r_w = ops.ep_unpack_routes(self.recv, self.o_ids, self.o_w, self.topk,
+                                          self.seg_rows, self.world, self.hdr)
+        r_x = self.recv[:, :self.row_bytes].view(self.code_dtype)
+        if self.groups:
+            kwargs["a1_scale"] = self.recv[:, self.o_scale:self.o_scale + 4 * self.groups].view(
+                torch.float32)
+            kwargs["output_dtype"] = self.out_dtype
+        else:
+            r_x = r_x.contiguous()
+        kwargs["activation"] = kwargs.get("activation") or "silu"
+        layer.fused_experts_impl(
+            r_x, w1_local, w2_local, r_w, r_ids, expert_map=self.expert_map,
+            global_num_experts=self.num_experts,
+            _out_peers=dict(seg_rows=self.seg_rows, seg_ptrs=self.back_ptrs, hdr=self.hdr),
+            **kwargs)
+
+    def combine(self, pos, out, combine_fn):
+        combine_fn(self.back, pos, out)
+        return out
+
+    def barrier(self) -> None:
+        from . import ops
+        self.epoch += 1
+        ops.ep_barrier(self.peers, self.rank, self.flag_off, self.epoch)
+
+
 class ExpertParallelMoE:
     """Dispatch → local experts → combine for one process group.
 
@@ -72,6 +204,13 @@ class ExpertParallelMoE:
         self.topk_hint = 0                    # set by forward() from topk_ids
         self.comm_sms = 16
         self._comm = None
+        # Exchange over peer memory (DirectExchange): used for CUDA batches of at most
+        # direct_max_tokens tokens per rank (0 = off; every rank must set the same value, it sizes
+        # the exchange buffers).  Falls back to the all-to-all path when the buffers cannot be
+        # mapped into all ranks.
+        self.direct_max_tokens = 0
+        self._direct = {}
+        self._direct_failed = None
 
     # -- index construction ---------------------------------------------------------------
     def plan(self, topk_ids: torch.Tensor, chunks: int = 1):
@@ -173,17 +312,83 @@ class ExpertParallelMoE:
         self.last_stats = dict(mode="replicated", tokens=m * world)
         return mine.to(out_dtype)
 
+    # -- exchange over peer memory -------------------------------------------------------------
+    def _quantiser(self, hidden_states, kwargs):
+        """The quantiser the dispatch applies before the wire (None: rows travel as they are)."""
+        w8a8 = kwargs.get("use_fp8_w8a8") or kwargs.get("use_int8_w8a8")
+        if not (self.quantize_dispatch and w8a8 and hidden_states.is_cuda
+                and hidden_states.dtype in (torch.float16, torch.bfloat16)
+                and not kwargs.get("use_ue8m0")):
+            return None, hidden_states.dtype, 0
+        from . import ops
+        qd = torch.float8_e4m3fn if kwargs.get("use_fp8_w8a8") else torch.int8
+        if kwargs.get("per_channel_quant"):
+            return (lambda x: ops.per_token_quant(x, quant_dtype=qd)), qd, 1
+        if kwargs.get("block_shape") is not None:
+            bn = kwargs["block_shape"][1]
+            return (lambda x: ops.per_block_quant(x, bn, qd)), qd, hidden_states.shape[1] // bn
+        return None, hidden_states.dtype, 0
+
+    def _direct_exchange(self, hidden_states, topk, code_dtype, groups, out_dtype):
+        """The exchange buffers for this configuration, mapped into all ranks on first use."""
+        h = hidden_states.shape[1]
+        row_bytes = h * torch.empty((), dtype=code_dtype).element_size()
+        hit = self._direct.get((self.direct_max_tokens, row_bytes, groups, topk, h, out_dtype))
+        if hit is not None:
+            return hit
+        ex = DirectExchange(self.world, self.rank, self.num_experts, self.direct_max_tokens,
+                            row_bytes, groups, topk, h, out_dtype, hidden_states.device, code_dtype)
+        import torch.distributed._symmetric_memory as symm_mem
+        buf = symm_mem.empty(ex.total_bytes, dtype=torch.uint8, device=hidden_states.device)
+        handle = symm_mem.rendezvous(buf, self.group)
+        buf[:ex.recv_off].zero_()
+        ex.attach(buf, [int(p) for p in handle.buffer_ptrs])
+        ex.handle = handle
+        torch.cuda.synchronize(hidden_states.device)
+        dist.barrier(group=self.group)        # every rank's header and flags are zero from here on
+        self._direct[ex.key()] = ex
+        return ex
+
+    def forward_direct(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
+        """One step over peer memory; see :class:`DirectExchange`.  No host synchronisation."""
+        m, h = hidden_states.shape
+        out_dtype = kwargs.get("output_dtype") or hidden_states.dtype
+        quant, code_dtype, groups = self._quantiser(hidden_states, kwargs)
+        ex = self._direct_exchange(hidden_states, topk_ids.shape[1], code_dtype, groups, out_dtype)
+        marks = []
+
+        def mark(name):
+            if self.profile:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
+        pos = ex.dispatch(hidden_states, topk_weights, topk_ids, quant)
+        mark("dispatch")
+        ex.barrier()
+        mark("meet 1")
+        ex.experts(w1_local, w2_local, **kwargs)
+        mark("experts+return")
+        ex.barrier()
+        mark("meet 2")
+        out = torch.empty((m, h), dtype=out_dtype, device=hidden_states.device)
+        ex.combine(pos, out, self.combine_fn)
+        mark("combine")
+        self.last_stats = dict(mode="direct", routes=m * topk_ids.shape[1],
+                               exchange_bytes=ex.total_bytes)
+        if marks:
+            torch.cuda.synchronize()
+            self.last_stats["ms"] = {b[0]: a[1].elapsed_time(b[1])
+                                     for a, b in zip(marks[:-1], marks[1:])}
+        return out
+
     # -- wire format -------------------------------------------------------------------------
-    @staticmethod
-    def _a16(n: int) -> int:
-        return (n + 15) // 16 * 16
+    _a16 = staticmethod(_a16)
 
     def _wire_layout(self, row_bytes: int, groups: int, topk: int):
         """Byte offsets of the parts of a wire row: data, scales, ids, weights; total size."""
-        o_scale = self._a16(row_bytes)
-        o_ids = o_scale + self._a16(groups * 4)
-        o_w = o_ids + self._a16(topk * 4)
-        return o_scale, o_ids, o_w, o_w + self._a16(topk * 4)
+        return wire_layout(row_bytes, groups, topk)
 
     def _pack(self, x, x_scale, ids32, w32, tok_idx, send_ids, first, rows, wire):
         """Send buffer of one chunk: one wire row per (token, destination rank)."""
@@ -227,6 +432,18 @@ class ExpertParallelMoE:
         if self.replicate_below and m * self.world <= self.replicate_below \
                 and not kwargs.get("no_combine"):
             return self.forward_replicated(hidden_states, w1_local, w2_local, topk_weights,
+                                           topk_ids, **kwargs)
+        if (self.direct_max_tokens and hidden_states.is_cuda and m <= self.direct_max_tokens
+                and self._direct_failed is None and not kwargs.get("no_combine")
+                and not kwargs.get("use_mxfp8") and not kwargs.get("use_mxfp4_w4a8")):
+            try:
+                self._direct_exchange(hidden_states, topk_ids.shape[1],
+                                      *self._quantiser(hidden_states, kwargs)[1:],
+                                      kwargs.get("output_dtype") or hidden_states.dtype)
+            except Exception as exc:           # no peer mapping on this box: all-to-all path
+                self._direct_failed = repr(exc)
+            else:
+                return self.forward_direct(hidden_states, w1_local, w2_local, topk_weights,
                                            topk_ids, **kwargs)
         k = topk_ids.shape[1]
         world = self.world

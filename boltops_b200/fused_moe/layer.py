@@ -174,6 +174,7 @@ def fused_experts_impl(
     use_ue8m0: bool = False,
     use_mxfp8: bool = False,
     gemm1_beta: Optional[float] = None,
+    _out_peers=None,
 ) -> torch.Tensor:
     # ---- variants outside this build -------------------------------------------------
     if use_mxfp4_w4a8 or use_mxfp8:
@@ -297,7 +298,12 @@ def fused_experts_impl(
     dev = hidden_states.device
     mid_dtype = output_dtype
 
-    if no_combine:
+    if _out_peers is not None:
+        # expert parallelism over peer memory: the top-k combine writes every live row straight
+        # into the exchange buffer of the rank the token came from (ep.py); nothing is returned
+        assert not (no_combine or inplace), "the direct exchange returns combined rows"
+        out = None
+    elif no_combine:
         assert not inplace, "no_combine + inplace is not supported"
         out = torch.empty((num_tokens, topk, model_dim), device=dev, dtype=output_dtype)
     elif inplace:
@@ -322,6 +328,7 @@ def fused_experts_impl(
     # workspace instead of one of each per kernel, which is what a decode-sized layer's time is
     # made of.  Used whenever the variant is the common one.
     if (_ONE_CALL and STAGE_TIMER is None and fused_silu and not no_combine
+            and _out_peers is None
             and num_tokens <= chunk and not use_ue8m0 and hidden_states.is_contiguous()
             and hidden_states.dtype in (torch.float16, torch.bfloat16)
             and output_dtype == hidden_states.dtype
@@ -493,5 +500,9 @@ def fused_experts_impl(
                                  a_scale=act_scale, a_scale_ld=cap, b_scale=w2_scale_c, bias=b2,
                                  scatter=False, mul_routed_weight=needs_router_weight, **common)
             with _Stage("combine"):
-                ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
+                if _out_peers is not None:
+                    ops.gather_sum_to_peers(c_sorted, route_pos, routed_scaling_factor,
+                                            first_row=begin, **_out_peers)
+                else:
+                    ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
     return out

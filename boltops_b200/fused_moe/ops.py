@@ -368,6 +368,79 @@ def gather_sum(src: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
     return out
 
 
+def gather_sum_to_peers(src: torch.Tensor, pos: torch.Tensor, scale: float, *, seg_rows: int,
+                        seg_ptrs: torch.Tensor, hdr: torch.Tensor, first_row: int = 0) -> None:
+    """``gather_sum`` whose row ``first_row + i`` (segment ``s = row // seg_rows``, ``q = row %
+    seg_rows``) goes to row ``hdr[s, 1] + q`` of the region at address ``seg_ptrs[s]`` -- possibly
+    another rank's memory -- and is skipped when ``q >= hdr[s, 0]``."""
+    _require_cuda(src, pos, seg_ptrs, hdr)
+    lib = _cabi.load()
+    m, slots = pos.shape
+    assert pos.dtype == torch.int32 and pos.is_contiguous() and src.is_contiguous()
+    assert seg_ptrs.dtype == torch.int64 and hdr.dtype == torch.int32 and hdr.is_contiguous()
+    with _cabi.on_device(src.device):
+        check(lib.bolt_moe_gather_sum_to_peers(ptr(src), dtype_code(src.dtype), ptr(pos), m, slots,
+                                               src.shape[1], float(scale), seg_rows, ptr(seg_ptrs),
+                                               ptr(hdr), first_row, stream_of(src)))
+    _count()
+
+
+def ep_dispatch_rows(data: torch.Tensor, scales: Optional[torch.Tensor], topk_ids: torch.Tensor,
+                     topk_weights: torch.Tensor, send_ids: torch.Tensor, counts: torch.Tensor,
+                     me: int, seg_rows: int, peers: torch.Tensor, hdr_off: int, recv_off: int,
+                     wire_bytes: int) -> None:
+    """Write this rank's wire rows (send order ``send_ids``, per-destination ``counts``, both on
+    the device) into segment ``me`` of every destination's receive region and the
+    ``{count, first return row}`` pair into its header (``bolt_ep_dispatch_rows``)."""
+    _require_cuda(data, topk_ids, topk_weights, send_ids, counts, peers)
+    lib = _cabi.load()
+    assert data.is_contiguous() and topk_ids.is_contiguous() and topk_weights.is_contiguous()
+    assert topk_ids.dtype == torch.int32 and topk_weights.dtype == torch.float32
+    assert send_ids.dtype == torch.int32 and counts.dtype == torch.int32
+    assert peers.dtype == torch.int64
+    groups = 0
+    if scales is not None:
+        scales = scales.reshape(data.shape[0], -1).contiguous()
+        groups = scales.shape[1]
+    world = peers.numel()
+    max_rows = data.shape[0] * min(world, topk_ids.shape[1])
+    with _cabi.on_device(data.device):
+        check(lib.bolt_ep_dispatch_rows(ptr(data), data.shape[1] * data.element_size(), ptr(scales),
+                                        groups, ptr(topk_ids), ptr(topk_weights), topk_ids.shape[1],
+                                        ptr(send_ids), ptr(counts), world, me, max_rows, seg_rows,
+                                        ptr(peers), hdr_off, recv_off, wire_bytes,
+                                        ptr(device_status(data.device)), stream_of(data)))
+    _count()
+
+
+def ep_unpack_routes(recv: torch.Tensor, ids_off: int, wts_off: int, topk: int, seg_rows: int,
+                     nseg: int, hdr: torch.Tensor):
+    """Dense ``(topk_ids, topk_weights)`` of all ``nseg * seg_rows`` rows of a receive region
+    (``recv`` uint8 ``[nseg * seg_rows, wire_bytes]``); rows a segment does not hold get id -1."""
+    _require_cuda(recv, hdr)
+    lib = _cabi.load()
+    assert recv.dtype == torch.uint8 and recv.is_contiguous() and hdr.dtype == torch.int32
+    rows = nseg * seg_rows
+    ids = torch.empty((rows, topk), dtype=torch.int32, device=recv.device)
+    wts = torch.empty((rows, topk), dtype=torch.float32, device=recv.device)
+    with _cabi.on_device(recv.device):
+        check(lib.bolt_ep_unpack_routes(ptr(recv), recv.shape[1], ids_off, wts_off, topk, seg_rows,
+                                        nseg, ptr(hdr), ptr(ids), ptr(wts), stream_of(recv)))
+    _count()
+    return ids, wts
+
+
+def ep_barrier(peers: torch.Tensor, me: int, flag_off: int, epoch: int) -> None:
+    """All ranks of the exchange meet on the current stream (bounded wait; see
+    ``bolt_ep_barrier``).  One process per GPU only."""
+    _require_cuda(peers)
+    lib = _cabi.load()
+    with _cabi.on_device(peers.device):
+        check(lib.bolt_ep_barrier(ptr(peers), peers.numel(), me, flag_off, epoch,
+                                  ptr(device_status(peers.device)), stream_of(peers)))
+    _count()
+
+
 def ep_dest_ranks(topk_ids: torch.Tensor, num_experts: int, experts_per_rank: int,
                   world: int, chunk_tokens: int = 0) -> torch.Tensor:
     """``routes[t, r] = r`` if one of token t's experts lives on rank r, else -1 (int32 [M, world]);

@@ -347,6 +347,45 @@ int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* ou
                         int64_t num_tokens, int slots, int n, float scale, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Direct expert-parallel exchange over peer memory (no reference counterpart: the reference
+ * leaves expert parallelism to the serving engine, boltops/fused_moe/__init__.py:127-133).
+ * Every rank owns one exchange buffer of the same layout that all ranks can address (`peers`: a
+ * device array of the `world` base addresses, in rank order):
+ *   hdr_off  : int32 [world][2]  = {rows sent by rank s, first row of s's return region for me}
+ *   flag_off : int32 [world]     = epochs of bolt_ep_barrier
+ *   recv_off : world segments of seg_rows wire rows (layout of bolt_ep_pack_rows), segment s
+ *              written by rank s
+ *   return region (its address goes into seg_ptrs): partial output rows, in the owner's send order
+ * bolt_ep_dispatch_rows: rank `me` writes its wire rows (send order = sorted ids of the dispatch
+ *   sort, counts [world] = its per-rank counts, both in device memory: no host round trip) into
+ *   segment `me` of every destination's receive region and {count, first row} into its header;
+ *   max_rows bounds the grid.  Counts above seg_rows are clamped and flagged in *status (21).
+ * bolt_ep_unpack_routes: the receiver's dense top-k ids (-1 for rows a segment does not hold) and
+ *   weights for all world * seg_rows rows, which the masked local layer then takes as its batch.
+ * bolt_moe_gather_sum_to_peers: bolt_moe_gather_sum whose output row m (m = first_row + i) goes to
+ *   row hdr[2 s + 1] + q of the region seg_ptrs[s], s = m / seg_rows, q = m % seg_rows, and is
+ *   skipped when q >= hdr[2 s]: the top-k combine of the local layer writes every partial row
+ *   straight into the return region of the rank the token came from.
+ * bolt_ep_barrier: all ranks meet (flags in peer memory, epoch must grow by one per call);
+ *   every wait is bounded (~1 s), on expiry *status is set to 20 and the kernel returns.
+ * One process per GPU; the kernels use plain loads and stores on peer addresses only.
+ */
+int bolt_ep_dispatch_rows(const void* data, int row_bytes, const float* scales, int groups,
+                          const int32_t* topk_ids, const float* topk_weights, int topk,
+                          const int32_t* send_ids, const int32_t* counts, int world, int me,
+                          int64_t max_rows, int64_t seg_rows, const int64_t* peers, int64_t hdr_off,
+                          int64_t recv_off, int64_t wire_bytes, int32_t* status, void* stream);
+int bolt_ep_unpack_routes(const void* recv, int64_t wire_bytes, int64_t ids_off, int64_t wts_off,
+                          int topk, int64_t seg_rows, int nseg, const int32_t* hdr,
+                          int32_t* topk_ids, float* topk_weights, void* stream);
+int bolt_moe_gather_sum_to_peers(const void* src, int dtype, const int32_t* pos, int64_t num_tokens,
+                                 int slots, int n, float scale, int64_t seg_rows,
+                                 const int64_t* seg_ptrs, const int32_t* hdr, int64_t first_row,
+                                 void* stream);
+int bolt_ep_barrier(const int64_t* peers, int world, int me, int64_t flag_off, int epoch,
+                    int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------
  * MXFP4 (w4a8) experts.  Replace the element-wise parts of fused_experts_mxfp_impl with
  * use_mxfp4_w4a8 (boltops/fused_moe/triton/fused_moe.py:923-1197): weight decoding
  * (boltops/fused_moe/triton/mxfp4.py:61-157 reads packed e2m1 nibbles, low nibble first, with

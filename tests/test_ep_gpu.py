@@ -67,6 +67,18 @@ def _worker(rank, world, port, ret):
         mfull = fused_experts(hidden.to(dev), fw1, fw2, wts.to(dev), ids.to(dev), use_mxfp8=True,
                               w1_scale=fs1, w2_scale=fs2, block_shape=[1, 32])
         torch.cuda.synchronize()
+        # exchange over peer memory: same kernels in the local layer, same summation order in the
+        # combine, so the result equals the all-to-all path bit for bit; twice, to cross the
+        # hazards between steps
+        ep.direct_max_tokens = 256
+        for _ in range(2):
+            direct = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
+                                w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+            torch.cuda.synchronize()
+            ops.check_device_status(dev)
+            assert ep._direct_failed is None, ep._direct_failed
+            assert ep.last_stats.get("mode") == "direct"
+            assert torch.equal(direct, out), "the exchange over peer memory changed the result"
         ret[rank] = max(err, O.rel_l2(mx.cpu(), mfull.cpu()))
     finally:
         dist.destroy_process_group()
@@ -100,3 +112,62 @@ def test_ep_plan_cuda_equals_torch_plan():
         assert torch.equal(cnt_a.cpu(), cnt_b.cpu())
         assert torch.equal(tok_a.cpu(), tok_b[:n].cpu())
         assert torch.equal(pos_a.cpu(), pos_b.cpu())
+
+
+@pytest.mark.parametrize("kind", ["fp8_block", "bf16", "int8_channel"])
+def test_direct_exchange_phases_with_emulated_ranks(kind):
+    """The three phases of the exchange over peer memory for four ranks held by ONE process on
+    one GPU (every "peer" buffer is a local tensor, ranks run phase by phase, no rank ever waits
+    for another): headers, segment addressing, masking of unused rows and the combine are those
+    of the real thing.  Expected: the sum over ranks, in rank order, of the masked local layer on
+    the same tokens, each partial rounded to the output dtype -- bit for bit."""
+    import bench as B
+    from boltops_b200.fused_moe import fused_experts, ops
+    from boltops_b200.fused_moe.ep import DirectExchange
+    dev = torch.device("cuda", 0)
+    world, m_max = 4, 96
+    cfg = dict(kind=kind, E=16, K=4, H=512, I=256)
+    per = cfg["E"] // world
+    if kind == "fp8_block":
+        kw = dict(use_fp8_w8a8=True, block_shape=[128, 128])
+        code, groups = torch.float8_e4m3fn, cfg["H"] // 128
+        quant = lambda x: ops.per_block_quant(x, 128, torch.float8_e4m3fn)
+    elif kind == "int8_channel":
+        kw = dict(use_int8_w8a8=True, per_channel_quant=True)
+        code, groups = torch.int8, 1
+        quant = lambda x: ops.per_token_quant(x, quant_dtype=torch.int8)
+    else:
+        kw, code, groups, quant = {}, torch.bfloat16, 0, None
+    ranks, toks, weights = [], [], []
+    for r in range(world):
+        ex = DirectExchange(world, r, cfg["E"], m_max, cfg["H"] * (2 if groups == 0 else 1), groups,
+                            cfg["K"], cfg["H"], torch.bfloat16, dev, code)
+        ranks.append(ex)
+        hidden, wts, ids = B.make_tokens(cfg, 40 + 17 * r, 70 + r)       # ragged batch sizes
+        toks.append((hidden.to(dev), wts.to(dev), ids.to(dev)))
+        w1, w2, w1s, w2s = B.make_weights(cfg, dev, list(range(r * per, (r + 1) * per)), 0)
+        weights.append((w1, w2, dict(kw, w1_scale=w1s, w2_scale=w2s) if w1s is not None else dict(kw)))
+    bufs = [torch.full((ex.total_bytes,), 0x7B, dtype=torch.uint8, device=dev) for ex in ranks]
+    for ex, buf in zip(ranks, bufs):
+        buf[:ex.recv_off].zero_()
+        ex.attach(buf, [b.data_ptr() for b in bufs])
+    for step in range(2):                                   # twice: stale rows of step one remain
+        pos = [ex.dispatch(h, w, i, quant) for ex, (h, w, i) in zip(ranks, toks)]
+        for ex, (w1, w2, k) in zip(ranks, weights):
+            ex.experts(w1, w2, **k)
+        for r, ex in enumerate(ranks):
+            h, w, i = toks[r]
+            out = torch.empty_like(h)
+            ex.combine(pos[r], out, ops.gather_sum)
+            acc = torch.zeros(h.shape, dtype=torch.float32, device=dev)
+            for q, (w1, w2, k) in enumerate(weights):
+                emap = torch.full((cfg["E"],), -1, dtype=torch.int32, device=dev)
+                emap[q * per:(q + 1) * per] = torch.arange(per, dtype=torch.int32, device=dev)
+                acc += fused_experts(h, w1, w2, w, i, expert_map=emap,
+                                     global_num_experts=cfg["E"], **k).float()
+            torch.cuda.synchronize()
+            ops.check_device_status(dev)
+            assert torch.equal(out, acc.to(out.dtype)), f"rank {r}, step {step}"
+            sent = int((pos[r] >= 0).sum())
+            assert int(ex.hdr[:, 0].sum()) == sum(int((p[:, r] >= 0).sum()) for p in pos)
+            assert sent <= ex.back_rows

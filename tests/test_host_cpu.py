@@ -204,3 +204,34 @@ def test_mxfp8_rejections_match_reference(case):
             output_dtype=torch.float32 if case == "output_dtype" else None,
             w1_scale=torch.ones(1, 256, 4, dtype=scale_dtype),
             w2_scale=torch.ones(1, 128, 4, dtype=scale_dtype))
+
+
+def test_gathered_row_operand_rule_and_layer_kernel_count(monkeypatch):
+    """The rule that picks the gathered row operand is the same on both sides of the C ABI (up
+    to 64 routes per expert), and the one-call layer reports the kernels it would launch (host
+    arithmetic only: nothing runs on a device)."""
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import layer
+    monkeypatch.setattr(layer, "_GATHER", None)
+    assert layer._use_gather(64 * 256, 256) and not layer._use_gather(64 * 256 + 1, 256)
+    monkeypatch.setattr(layer, "_GATHER", False)
+    assert not layer._use_gather(8, 256)
+    lib = _cabi.load()
+
+    def count(kind, tokens):
+        a = _cabi.LayerArgs()
+        a.kind, a.x_dtype, a.out_dtype = kind, _cabi.BF16, _cabi.BF16
+        a.num_tokens, a.topk = tokens, 8
+        a.hidden, a.inter, a.model_dim = 1024, 512, 1024
+        a.num_experts = a.global_num_experts = 32
+        a.w1_scale = a.w2_scale = 1          # non-null: only checked for presence here
+        return lib.bolt_moe_layer_kernel_count(a)
+
+    import os
+    if os.environ.get("BOLTOPS_B200_GATHER") is None:
+        small = 32 * 64 // 8                 # 64 routes per expert
+        assert count(_cabi.GEMM_BF16, small) == count(_cabi.GEMM_BF16, small + 1) - 1
+    fp8 = count(_cabi.GEMM_FP8_BLOCK, 16)
+    assert fp8 >= 5 and count(_cabi.GEMM_INT8_CHANNEL, 16) == fp8 + 2
+    bad = _cabi.LayerArgs()
+    assert lib.bolt_moe_layer_kernel_count(bad) == -1
