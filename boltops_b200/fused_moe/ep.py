@@ -194,11 +194,13 @@ class ExpertParallelMoE:
         # all-gather the tokens, run the masked local layer on all of them, reduce-scatter
         # the partial outputs.  0 = never (the caller must guarantee equal token counts).
         self.replicate_below = 0
-        # Pipelined exchange: batches of at least pipeline_min_tokens tokens are cut into
-        # pipeline_chunks token chunks; the all-to-alls of neighbouring chunks run on a second
+        # Pipelined all-to-all exchange: batches of at least pipeline_min_tokens tokens are cut
+        # into pipeline_chunks token chunks; the all-to-alls of neighbouring chunks run on a second
         # stream under the expert GEMMs of the current one.  The GEMMs then leave comm_sms SMs
         # to the exchange kernels (a persistent GEMM on every SM would keep them waiting).
-        self.pipeline_chunks = 2
+        # Off by default (1 chunk): measured on 4 GPUs every chunk streams the local experts'
+        # weights again and runs on fewer SMs, which costs more than the overlap hides.
+        self.pipeline_chunks = 1
         self.pipeline_min_tokens = 1024
         self.pipeline_rows_per_expert = 384   # expected rows per local expert and chunk, at least
         self.topk_hint = 0                    # set by forward() from topk_ids
