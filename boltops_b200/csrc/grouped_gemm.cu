@@ -115,6 +115,7 @@ struct GemmParams {
   const uint8_t* sfb;   // [num_experts][n_blocks128][num_kb][512]
   int n_blocks128;
   int mx_stage_tx;      // operand bytes one K block brings (packed 4-bit weights count as stored)
+  int mx_group128;      // gated epilogue: 1 x 128 power-of-two groups (the MXFP4 w4a8 recipe)
   float act_alpha, act_beta, act_limit;   // MX gated epilogue
   int act_has_limit;
 };
@@ -1066,6 +1067,8 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
   const uint32_t bar_empty = bar_full + 8 * kMxStages;
   const uint32_t bar_tfull = bar_empty + 8 * kMxStages;
   const uint32_t bar_tempty = bar_tfull + 8;
+  const uint32_t bar_x = bar_tempty + 8;                      // [4 lane quarters]: absmax exchange
+  float* amax_x = reinterpret_cast<float*>(ctrl + 1024);      // [2 tile parities][2 halves][128 rows]
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -1076,6 +1079,7 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
     }
     mbar_init(bar_tfull, 1);
     mbar_init(bar_tempty, 8);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_x + 8 * i, 2);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1179,7 +1183,7 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
     const bool has_ids = p.sorted_ids != nullptr;
     const bool has_rw = p.mul_routed_weight && p.sorted_weights != nullptr;
     uint8_t* out_stage = ctrl + 4096 + kMxSfSlots * kMxSfSlotBytes + (warp - 4) * 2560;
-    uint32_t tph = 0;
+    uint32_t tph = 0, xph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += stride) {
       const TileCoord tc = tile_coord(tile, num_m, p.tiles_n, p.group_m);
@@ -1223,6 +1227,79 @@ k_mx_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUt
           }
           store_chunk<1>(out_stage, 0, p, &tma_c, tile_row0, row_off, ocol + 32 * i, p.n, live,
                          lane, v);
+        }
+      } else if (p.mx_group128) {
+        // The w4a8 recipe between its GEMMs (boltops/fused_moe/triton/mxfp4_quant.py:38-56 of the
+        // reference project): both operands rounded through mid_dtype, gate <= L, |up| <= L,
+        // y = bf16(up * gate / (1 + exp(-gate))), then ONE power-of-two scale per 1 x 128 group:
+        // the smallest 2^k >= max(amax, 1e-10) / 448 (not below 1e-10), codes e4m3(y / scale).
+        // A tile's 128 output columns are exactly one group; this thread holds 64 of them (half
+        // h), the thread of the same row in the other half the rest: the two exchange their
+        // absmax through shared memory (bounded barrier per lane quarter).
+        const int ocol_g = tc.n_blk * 128 + 64 * h;
+        uint8_t* c8 = static_cast<uint8_t*>(p.c) + row * (int64_t)p.c_ld + ocol_g;
+        uint8_t* s8 = reinterpret_cast<uint8_t*>(p.c_scale) + row * p.c_scale_ld + ocol_g / 32;
+        float y[64];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float g0 = __uint_as_float(raw[i][j]), g1 = __uint_as_float(raw[i][j + 1]);
+            float u0 = __uint_as_float(raw[2 + i][j]), u1 = __uint_as_float(raw[2 + i][j + 1]);
+            if (p.mid_dtype == BOLT_BF16) {
+              round2<BOLT_BF16>(g0, g1);
+              round2<BOLT_BF16>(u0, u1);
+            } else if (p.mid_dtype == BOLT_F16) {
+              round2<BOLT_F16>(g0, g1);
+              round2<BOLT_F16>(u0, u1);
+            }
+            if (p.act_has_limit) {
+              g0 = fminf(g0, p.act_limit);
+              g1 = fminf(g1, p.act_limit);
+              u0 = fminf(fmaxf(u0, -p.act_limit), p.act_limit);
+              u1 = fminf(fmaxf(u1, -p.act_limit), p.act_limit);
+            }
+            float y0 = __fdiv_rn(u0 * g0, 1.0f + expf(-g0));
+            float y1 = __fdiv_rn(u1 * g1, 1.0f + expf(-g1));
+            round2<BOLT_BF16>(y0, y1);
+            if (!live) y0 = y1 = 0.f;
+            y[32 * i + j] = y0;
+            y[32 * i + j + 1] = y1;
+            amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
+          }
+        }
+        const int par = (int)(xph & 1u);
+        amax_x[(par * 2 + h) * 128 + row_in_tile] = amax;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_x + 8 * q);
+        ok = mbar_wait(bar_x + 8 * q, xph & 1u, abort_flag, p.status, 6);
+        if (!ok) break;
+        ++xph;
+        amax = fmaxf(amax, amax_x[(par * 2 + (h ^ 1)) * 128 + row_in_tile]);
+        const float rawsc = fmaxf(__fdiv_rn(fmaxf(amax, 1.0e-10f), 448.0f), 1.0e-10f);
+        const uint32_t bits = __float_as_uint(rawsc);
+        const uint32_t e = ((bits >> 23) & 255u) + ((bits & 0x7fffffu) != 0u ? 1u : 0u);
+        const float inv = __fdiv_rn(1.0f, __uint_as_float(e << 23));
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float v[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              v[t] = fminf(fmaxf(y[32 * i + 4 * j + t] * inv, -448.0f), 448.0f);
+            const uint32_t lo =
+                __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi =
+                __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);
+            w[j] = lo | (hi << 16);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(c8 + 32 * i);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          s8[i] = live ? (uint8_t)e : (uint8_t)0;
         }
       } else {
         // half h: columns [0,64) gate and [64,128) up of output columns 128 n_blk + 64 h + [0,64)
@@ -1423,8 +1500,6 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
                  "grouped_gemm: the MX gated epilogue needs n/2 a multiple of 128");
     BOLT_REQUIRE(a->k % 128 == 0, "grouped_gemm: the MX kind needs k a multiple of 128");
     BOLT_REQUIRE(a->bias == nullptr, "grouped_gemm: the MX kind takes no bias");
-    BOLT_REQUIRE(!mx4 || a->epilogue == BOLT_EPI_STORE,
-                 "grouped_gemm: the MXFP4 kind has the plain epilogue");
     BOLT_REQUIRE(!mx4 || reinterpret_cast<uintptr_t>(a->b) % 32 == 0,
                  "grouped_gemm: packed e2m1 weights must be 32-byte aligned");
   }
@@ -1607,6 +1682,7 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
     // the copy of packed 4-bit values completes the barrier by the bytes it read (half of the
     // shared-memory footprint it writes)
     p.mx_stage_tx = kABytes + (mx4 ? kBBytes / 2 : kBBytes);
+    p.mx_group128 = mx4 ? 1 : 0;
     p.sfa = reinterpret_cast<const uint8_t*>(a->a_scale);
     p.sfb = reinterpret_cast<const uint8_t*>(a->b_scale);
     p.n_blocks128 = gated ? 2 * p.tiles_n : (a->n + 127) / 128;

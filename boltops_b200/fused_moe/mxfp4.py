@@ -39,6 +39,9 @@ from .activation import apply_activation
 
 _decoded = {}
 _NATIVE = os.environ.get("BOLTOPS_B200_MXFP4", "native") != "decoded"
+# native kind, SiLU: the activation and the second quantisation run in GEMM1's epilogue
+# (BOLTOPS_B200_MXFP4_FUSED=0: plain GEMM1 + the stand-alone kernel; same codes bit for bit)
+_FUSED = os.environ.get("BOLTOPS_B200_MXFP4_FUSED", "1") != "0"
 
 
 def _decode_weights(w: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -212,7 +215,8 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
               and w1.data_ptr() % 32 == 0 and w2.data_ptr() % 32 == 0)
     if native:
         from .mxfp8 import _tile_weight_scales
-        sfb1 = _tile_weight_scales(w1, w1_scale.contiguous())
+        fuse_act = _FUSED and activation == "silu" and inter % 128 == 0
+        sfb1 = _tile_weight_scales(w1, w1_scale.contiguous(), gated=fuse_act)
         sfb2 = _tile_weight_scales(w2, w2_scale.contiguous())
     else:
         w1_d = _decode_weights(w1, w1_scale)
@@ -279,6 +283,15 @@ def fused_experts_mxfp4(hidden_states, w1, w2, topk_weights, topk_ids, *, w1_sca
                     ptr(sorted_w) if apply_router_weight_on_input else None, ptr(a2_scale),
                     ptr(act), _cabi.BF16, stream_of(g1)))
             ops._count()
+        elif native and fuse_act:
+            # one kernel: GEMM1, rounding to the output dtype, SiLU(gate) * up through bf16, the
+            # 1 x 128 power-of-two quantiser; codes and exponent bytes go straight to GEMM2
+            act = torch.empty((cap, inter), device=dev, dtype=torch.float8_e4m3fn)
+            act_s = torch.empty((cap, inter // 32), device=dev, dtype=torch.uint8)
+            ops.grouped_gemm(epilogue=_cabi.EPI_SILU_MUL_QUANT, a=a_sorted, c=act, c_scale=act_s,
+                             c_scale_ld=inter // 32, mid_dtype=out_dtype, act_limit=limit,
+                             **gemm1, **common)
+            gemm2 = dict(a=act, b=w2, a_scale=ops.mx_sf_layout(act_s, cap), b_scale=sfb2)
         else:
             g1 = torch.empty((cap, n1), device=dev, dtype=out_dtype)
             ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=a_sorted, c=g1, **gemm1, **common)

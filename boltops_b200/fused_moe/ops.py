@@ -503,8 +503,9 @@ def set_gemm_sm_reserve(sms: int) -> None:
 
 
 def device_status(device: torch.device) -> torch.Tensor:
-    """Per-device int32 word that the grouped GEMM sets when a bounded device-side
-    wait expired (0 = healthy).  Reading it synchronises; kernels never do."""
+    """Per-device int32 word that the grouped GEMM and the expert-parallel exchange kernels set
+    when a bounded device-side wait expired (0 = healthy).  Reading it synchronises; kernels
+    never do."""
     key = torch.device(device).index or 0
     if key not in _status_words:
         _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -515,7 +516,8 @@ def check_device_status(device: torch.device) -> None:
     code = int(device_status(device).item())
     if code != 0:
         device_status(device).zero_()
-        raise _cabi.BoltError(f"grouped GEMM reported an expired device-side wait (code {code})")
+        raise _cabi.BoltError(f"a kernel reported an expired device-side wait (code {code}: 1-5 grouped "
+                              f"GEMM, 20 exchange barrier, 21 exchange segment overflow)")
 
 
 def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,

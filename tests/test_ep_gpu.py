@@ -171,3 +171,31 @@ def test_direct_exchange_phases_with_emulated_ranks(kind):
             sent = int((pos[r] >= 0).sum())
             assert int(ex.hdr[:, 0].sum()) == sum(int((p[:, r] >= 0).sum()) for p in pos)
             assert sent <= ex.back_rows
+
+
+def test_exchange_barrier_gives_up_when_a_rank_never_arrives():
+    """Failure detection without a fault: a meeting in which one "rank" never sets its flag
+    (its buffer is a local tensor nothing writes to).  The wait runs out after about a second,
+    the kernel returns, the status word reports it and the context stays usable; a meeting in
+    which the flag is there returns at once."""
+    import time
+    from boltops_b200 import _cabi
+    from boltops_b200.fused_moe import ops
+    dev = torch.device("cuda", 0)
+    mine = torch.zeros(64, dtype=torch.int32, device=dev)
+    absent = torch.zeros(64, dtype=torch.int32, device=dev)
+    peers = torch.tensor([mine.data_ptr(), absent.data_ptr()], dtype=torch.int64, device=dev)
+    ops.device_status(dev).zero_()
+    mine[1] = 1                                   # the other rank has "arrived" at epoch 1
+    ops.ep_barrier(peers, 0, 0, 1)
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)                  # healthy
+    assert int(absent[0].item()) == 1             # and this rank told it so
+    t0 = time.time()
+    ops.ep_barrier(peers, 0, 0, 2)                # nobody ever writes epoch 2 into `mine`
+    torch.cuda.synchronize()
+    assert 0.2 < time.time() - t0 < 10.0
+    with pytest.raises(_cabi.BoltError, match="code 20"):
+        ops.check_device_status(dev)
+    ops.check_device_status(dev)                  # cleared; the context still works
+    assert int((mine + 1)[5].item()) == 1         # (slot 5 is not a flag anybody wrote)

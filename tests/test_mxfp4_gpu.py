@@ -108,6 +108,18 @@ def test_mxfp4_packed_weights_on_the_tensor_core_equal_decoded_operands(monkeypa
     assert torch.isfinite(outs["native"]).all()
     err = (outs["native"] - outs["decoded"]).norm() / outs["decoded"].norm()
     assert err < 2e-3, float(err)
+    # the activation + quantiser fused into GEMM1's epilogue against the stand-alone kernel: the
+    # same operations in the same order on the same accumulators, so every output bit agrees
+    monkeypatch.setattr(mxfp4, "_NATIVE", True)
+    monkeypatch.setattr(mxfp4, "_FUSED", False)
+    unfused = fused_experts(x, w1, w2, wts.cuda(), ids.int().cuda(), use_mxfp4_w4a8=True,
+                            w1_scale=s1, w2_scale=s2, block_shape=[1, 32], gemm1_limit=0.75).float()
+    monkeypatch.setattr(mxfp4, "_FUSED", True)
+    fused = fused_experts(x, w1, w2, wts.cuda(), ids.int().cuda(), use_mxfp4_w4a8=True,
+                          w1_scale=s1, w2_scale=s2, block_shape=[1, 32], gemm1_limit=0.75).float()
+    torch.cuda.synchronize()
+    ops.check_device_status(x.device)
+    assert torch.equal(fused, unfused)
     _, codes, scales, sf = mxfp4.act_quant(x, want_codes=True, want_deq=False, want_sf=True)
     assert torch.equal(torch.exp2(sf.float() - 127.0),
                        scales.repeat_interleave(4, dim=1))
