@@ -184,3 +184,27 @@ def test_ep_plan_is_deterministic_and_dedups():
     assert counts.tolist() == [2, 3, 1, 1]
     assert tok.tolist() == [0, 2, 0, 2, 3, 2, 1]
     assert pos.tolist() == [[0, 2, -1, -1], [-1, -1, -1, 6], [1, 3, 5, -1], [-1, 4, -1, -1]]
+
+
+def test_direct_exchange_buffer_layout():
+    """Layout arithmetic of the peer-memory exchange buffer (host only): regions do not
+    overlap, are 256-byte aligned, hold what the kernels address, and depend only on the
+    configuration (every rank must compute the same offsets)."""
+    import torch
+    from boltops_b200.fused_moe.ep import DirectExchange, wire_layout
+    o_scale, o_ids, o_w, wire = wire_layout(7168, 56, 8)
+    assert (o_scale, o_ids, o_w, wire) == (7168, 7168 + 224, 7168 + 224 + 32, 7168 + 224 + 64)
+    exs = [DirectExchange(8, r, 256, 4096, 7168, 56, 8, 7168, torch.bfloat16, "cpu",
+                          torch.float8_e4m3fn) for r in (0, 5)]
+    a, b = exs
+    assert a.key() == b.key() and a.total_bytes == b.total_bytes
+    assert (a.hdr_off, a.flag_off, a.recv_off, a.back_off) == (b.hdr_off, b.flag_off, b.recv_off,
+                                                               b.back_off)
+    assert a.hdr_off == 0 and a.flag_off >= 8 * 8 and a.recv_off >= a.flag_off + 8 * 4
+    assert a.back_off >= a.recv_off + 8 * 4096 * wire
+    assert all(off % 256 == 0 for off in (a.flag_off, a.recv_off, a.back_off, a.total_bytes))
+    assert a.back_rows == 4096 * 8 and a.total_bytes >= a.back_off + a.back_rows * 7168 * 2
+    assert b.expert_map.tolist() == [-1] * 160 + list(range(32)) + [-1] * 64
+    # fewer ranks than top-k: a token cannot go to more ranks than there are
+    assert DirectExchange(2, 0, 64, 100, 1024, 0, 8, 512, torch.bfloat16, "cpu",
+                          torch.bfloat16).back_rows == 200
