@@ -114,8 +114,13 @@ def test_ep_plan_cuda_equals_torch_plan():
         assert torch.equal(pos_a.cpu(), pos_b.cpu())
 
 
-@pytest.mark.parametrize("kind", ["fp8_block", "bf16", "int8_channel"])
-def test_direct_exchange_phases_with_emulated_ranks(kind):
+@pytest.mark.parametrize("kind,world,shape", [
+    ("fp8_block", 4, dict(E=16, K=4, H=512, I=256)),
+    ("bf16", 4, dict(E=16, K=4, H=512, I=256)),
+    ("int8_channel", 4, dict(E=16, K=4, H=512, I=256)),
+    ("fp8_block", 8, dict(E=64, K=8, H=1024, I=512)),       # eight ranks, top-8: the 8-GPU index space
+])
+def test_direct_exchange_phases_with_emulated_ranks(kind, world, shape):
     """The three phases of the exchange over peer memory for four ranks held by ONE process on
     one GPU (every "peer" buffer is a local tensor, ranks run phase by phase, no rank ever waits
     for another): headers, segment addressing, masking of unused rows and the combine are those
@@ -125,8 +130,8 @@ def test_direct_exchange_phases_with_emulated_ranks(kind):
     from boltops_b200.fused_moe import fused_experts, ops
     from boltops_b200.fused_moe.ep import DirectExchange
     dev = torch.device("cuda", 0)
-    world, m_max = 4, 96
-    cfg = dict(kind=kind, E=16, K=4, H=512, I=256)
+    m_max = 40 + 17 * (world - 1)
+    cfg = dict(kind=kind, **shape)
     per = cfg["E"] // world
     if kind == "fp8_block":
         kw = dict(use_fp8_w8a8=True, block_shape=[128, 128])
