@@ -537,6 +537,9 @@ def main():
     ap.add_argument("--ep-direct", type=int, default=1,
                     help="N > 1: 1 = exchange over peer memory (no collective call and no host "
                          "synchronisation on the data path), 0 = NCCL all-to-all")
+    ap.add_argument("--ep-replicate-below", type=int, default=4096,
+                    help="N > 1: batches of at most this many tokens over all ranks take the "
+                         "replicated-token path (all-gather + reduce-scatter); 0 = never")
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="N > 1: token chunks of the pipelined dispatch / return exchange (1 = serial)")
     ap.add_argument("--ep-comm-sms", type=int, default=16,
@@ -623,7 +626,7 @@ def main():
         ep = ExpertParallelMoE(dist.group.WORLD, E, device)
         # every rank brings the same number of tokens here, so decode-sized batches may take the
         # replicated-token path (no host round trips); the headline batch stays on the dispatch
-        ep.replicate_below = 4096
+        ep.replicate_below = args.ep_replicate_below
         ep.direct_max_tokens = m if args.ep_direct else 0
         ep.pipeline_chunks = args.ep_chunks
         ep.comm_sms = args.ep_comm_sms

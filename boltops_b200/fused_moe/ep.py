@@ -431,10 +431,6 @@ class ExpertParallelMoE:
 
     def forward(self, hidden_states, w1_local, w2_local, topk_weights, topk_ids, **kwargs):
         m, h = hidden_states.shape
-        if self.replicate_below and m * self.world <= self.replicate_below \
-                and not kwargs.get("no_combine"):
-            return self.forward_replicated(hidden_states, w1_local, w2_local, topk_weights,
-                                           topk_ids, **kwargs)
         if (self.direct_max_tokens and hidden_states.is_cuda and m <= self.direct_max_tokens
                 and self._direct_failed is None and not kwargs.get("no_combine")
                 and not kwargs.get("use_mxfp8") and not kwargs.get("use_mxfp4_w4a8")):
@@ -446,6 +442,13 @@ class ExpertParallelMoE:
                 self._direct_failed = repr(exc)
             else:
                 return self.forward_direct(hidden_states, w1_local, w2_local, topk_weights,
+                                           topk_ids, **kwargs)
+        # (the exchange over peer memory comes first: measured on 2 GPUs it is as fast as the
+        # replicated-token path at 16 tokens per rank and 4-9 % faster from 256 on, and its
+        # traffic does not grow with the number of ranks)
+        if self.replicate_below and m * self.world <= self.replicate_below \
+                and not kwargs.get("no_combine"):
+            return self.forward_replicated(hidden_states, w1_local, w2_local, topk_weights,
                                            topk_ids, **kwargs)
         k = topk_ids.shape[1]
         world = self.world
