@@ -548,7 +548,8 @@ def main():
     ap.add_argument("--no-numa", action="store_true",
                     help="N > 1: leave CPU affinity and memory policy of the ranks as they are")
     ap.add_argument("--graph", action="store_true",
-                    help="1 GPU only: replay the layer from a CUDA graph in the device-resident timing")
+                    help="replay the layer from a CUDA graph in the device-resident timing (1 GPU, or "
+                         "N > 1 with the exchange over peer memory)")
     args = ap.parse_args()
 
     if args.measure_peaks:
@@ -685,7 +686,8 @@ def main():
     if rank == 0:
         sampler.start()
     launches0 = ops.launch_count()
-    if args.graph and world == 1:
+    if args.graph and (world == 1 or args.ep_direct):
+        # (N > 1: the peer-memory step holds no host-side state, so it replays from a graph too)
         step(hidden, wts, ids)
         launches = ops.launch_count() - launches0
         graph = torch.cuda.CUDAGraph()

@@ -156,7 +156,7 @@ _SIGNATURES = {
     "bolt_moe_gather_sum_to_peers": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int,
                                                C.c_int, C.c_float, C.c_int64, C.c_void_p,
                                                C.c_void_p, C.c_int64, C.c_void_p]),
-    "bolt_ep_barrier": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_void_p,
+    "bolt_ep_barrier": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p,
                                   C.c_void_p]),
     "bolt_moe_layer_workspace_bytes": (C.c_size_t, [C.POINTER(LayerArgs)]),
     "bolt_moe_layer_kernel_count": (C.c_int, [C.POINTER(LayerArgs)]),

@@ -469,13 +469,23 @@ __global__ void __launch_bounds__(256) k_ep_unpack_routes(
   }
 }
 
-// All ranks meet: thread r tells rank r "rank `me` has reached `epoch`" (a flag in r's buffer) and
-// waits until rank r has said the same here.  Kernels before this launch are complete (stream
-// order), so their peer stores are performed before the flag is written; the fences order the
-// flag against them at system scope.  The wait is bounded (~1 s): on expiry the status word is
-// set and the kernel returns.
+// All ranks meet: thread r tells rank r "rank `me` has reached epoch n" (a flag in r's buffer) and
+// waits until rank r has said the same here.  The epoch is a counter in this rank's own buffer
+// (slot `world` behind the flags) that the kernel advances itself, so a step carries no host-side
+// state and can be replayed.  Kernels before this launch are complete (stream order), so their
+// peer stores are performed before the flag is written; the fences order the flag against them
+// at system scope.  The wait is bounded (~1 s): on expiry the status word is set and the kernel
+// returns.
 __global__ void k_ep_barrier(const int64_t* __restrict__ peers, int world, int me, int64_t flag_off,
-                             int epoch, int32_t* __restrict__ status) {
+                             int32_t* __restrict__ status) {
+  __shared__ int epoch_s;
+  if (threadIdx.x == 0) {
+    int32_t* counter = reinterpret_cast<int32_t*>(peers[me] + flag_off) + world;
+    epoch_s = *counter + 1;
+    *counter = epoch_s;
+  }
+  __syncthreads();
+  const int epoch = epoch_s;
   const int r = threadIdx.x;
   if (r >= world) return;
   __threadfence_system();
@@ -546,14 +556,14 @@ extern "C" int bolt_ep_unpack_routes(const void* recv, int64_t wire_bytes, int64
   return BOLT_OK;
 }
 
-extern "C" int bolt_ep_barrier(const int64_t* peers, int world, int me, int64_t flag_off, int epoch,
+extern "C" int bolt_ep_barrier(const int64_t* peers, int world, int me, int64_t flag_off,
                                int32_t* status, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(peers != nullptr && world > 0 && world <= kMaxWorld && me >= 0 && me < world &&
                    flag_off % 4 == 0,
                "ep_barrier: bad arguments");
-  k_ep_barrier<<<1, kMaxWorld, 0, st>>>(peers, world, me, flag_off, epoch, status);
+  k_ep_barrier<<<1, kMaxWorld, 0, st>>>(peers, world, me, flag_off, status);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }

@@ -47,7 +47,7 @@ class DirectExchange:
     Every rank owns a buffer of the same layout that all ranks can address::
 
         header  int32 [world][2]   {rows rank s sent me, first row of s's return region for me}
-        flags   int32 [world]      epochs of the barrier
+        flags   int32 [world + 1]  epochs of the barrier (every rank's flag, then my own counter)
         receive world segments of seg_rows wire rows; segment s is written by rank s
         return  partial output rows of MY tokens, in my send order, written by the experts' ranks
 
@@ -76,13 +76,11 @@ class DirectExchange:
         self.back_rows = seg_rows * min(world, topk)
         self.hdr_off = 0
         self.flag_off = _a256(world * 8)
-        self.recv_off = self.flag_off + _a256(world * 4)
+        self.recv_off = self.flag_off + _a256((world + 1) * 4)
         self.back_off = self.recv_off + _a256(world * seg_rows * self.wire_bytes)
         self.total_bytes = self.back_off + _a256(
             self.back_rows * hidden * torch.empty((), dtype=out_dtype).element_size())
         self.buf = None
-        self.epoch = 0
-        self.meet = None          # callable: all ranks meet on the current stream
         emap = torch.full((num_experts,), -1, dtype=torch.int32)
         emap[rank * self.per_rank:(rank + 1) * self.per_rank] = torch.arange(self.per_rank,
                                                                             dtype=torch.int32)
@@ -153,8 +151,7 @@ class DirectExchange:
 
     def barrier(self) -> None:
         from . import ops
-        self.epoch += 1
-        ops.ep_barrier(self.peers, self.rank, self.flag_off, self.epoch)
+        ops.ep_barrier(self.peers, self.rank, self.flag_off)
 
 
 class ExpertParallelMoE:

@@ -430,13 +430,13 @@ def ep_unpack_routes(recv: torch.Tensor, ids_off: int, wts_off: int, topk: int, 
     return ids, wts
 
 
-def ep_barrier(peers: torch.Tensor, me: int, flag_off: int, epoch: int) -> None:
+def ep_barrier(peers: torch.Tensor, me: int, flag_off: int) -> None:
     """All ranks of the exchange meet on the current stream (bounded wait; see
     ``bolt_ep_barrier``).  One process per GPU only."""
     _require_cuda(peers)
     lib = _cabi.load()
     with _cabi.on_device(peers.device):
-        check(lib.bolt_ep_barrier(ptr(peers), peers.numel(), me, flag_off, epoch,
+        check(lib.bolt_ep_barrier(ptr(peers), peers.numel(), me, flag_off,
                                   ptr(device_status(peers.device)), stream_of(peers)))
     _count()
 

@@ -352,7 +352,8 @@ int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* ou
  * Every rank owns one exchange buffer of the same layout that all ranks can address (`peers`: a
  * device array of the `world` base addresses, in rank order):
  *   hdr_off  : int32 [world][2]  = {rows sent by rank s, first row of s's return region for me}
- *   flag_off : int32 [world]     = epochs of bolt_ep_barrier
+ *   flag_off : int32 [world + 1] = epochs of bolt_ep_barrier: flag of every rank, then this rank's
+ *                                  own epoch counter (all zero before the first call)
  *   recv_off : world segments of seg_rows wire rows (layout of bolt_ep_pack_rows), segment s
  *              written by rank s
  *   return region (its address goes into seg_ptrs): partial output rows, in the owner's send order
@@ -366,8 +367,10 @@ int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* ou
  *   row hdr[2 s + 1] + q of the region seg_ptrs[s], s = m / seg_rows, q = m % seg_rows, and is
  *   skipped when q >= hdr[2 s]: the top-k combine of the local layer writes every partial row
  *   straight into the return region of the rank the token came from.
- * bolt_ep_barrier: all ranks meet (flags in peer memory, epoch must grow by one per call);
- *   every wait is bounded (~1 s), on expiry *status is set to 20 and the kernel returns.
+ * bolt_ep_barrier: all ranks meet (flags in peer memory; the kernel advances its rank's epoch
+ *   counter itself, so every rank must call it the same number of times and a step holds no
+ *   host-side state); every wait is bounded (~1 s), on expiry *status is set to 20 and the
+ *   kernel returns.
  * One process per GPU; the kernels use plain loads and stores on peer addresses only.
  */
 int bolt_ep_dispatch_rows(const void* data, int row_bytes, const float* scales, int groups,
@@ -382,8 +385,8 @@ int bolt_moe_gather_sum_to_peers(const void* src, int dtype, const int32_t* pos,
                                  int slots, int n, float scale, int64_t seg_rows,
                                  const int64_t* seg_ptrs, const int32_t* hdr, int64_t first_row,
                                  void* stream);
-int bolt_ep_barrier(const int64_t* peers, int world, int me, int64_t flag_off, int epoch,
-                    int32_t* status, void* stream);
+int bolt_ep_barrier(const int64_t* peers, int world, int me, int64_t flag_off, int32_t* status,
+                    void* stream);
 
 /* ---------------------------------------------------------------------------
  * MXFP4 (w4a8) experts.  Replace the element-wise parts of fused_experts_mxfp_impl with

@@ -200,7 +200,7 @@ def test_direct_exchange_buffer_layout():
     assert a.key() == b.key() and a.total_bytes == b.total_bytes
     assert (a.hdr_off, a.flag_off, a.recv_off, a.back_off) == (b.hdr_off, b.flag_off, b.recv_off,
                                                                b.back_off)
-    assert a.hdr_off == 0 and a.flag_off >= 8 * 8 and a.recv_off >= a.flag_off + 8 * 4
+    assert a.hdr_off == 0 and a.flag_off >= 8 * 8 and a.recv_off >= a.flag_off + 9 * 4
     assert a.back_off >= a.recv_off + 8 * 4096 * wire
     assert all(off % 256 == 0 for off in (a.flag_off, a.recv_off, a.back_off, a.total_bytes))
     assert a.back_rows == 4096 * 8 and a.total_bytes >= a.back_off + a.back_rows * 7168 * 2

@@ -79,6 +79,23 @@ def _worker(rank, world, port, ret):
             assert ep._direct_failed is None, ep._direct_failed
             assert ep.last_stats.get("mode") == "direct"
             assert torch.equal(direct, out), "the exchange over peer memory changed the result"
+        # no host-side state in a step: captured once in a CUDA graph, replayed three times
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
+                       w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        hd, wd, idd = hidden.to(dev), wts.to(dev), ids.to(dev)
+        with torch.cuda.graph(graph):
+            replayed = ep.forward(hd, w1, w2, wd, idd, use_fp8_w8a8=True, w1_scale=w1s,
+                                  w2_scale=w2s, block_shape=[128, 128])
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ops.check_device_status(dev)
+        assert torch.equal(replayed, out), "graph replay of the peer-memory step changed the result"
         ret[rank] = max(err, O.rel_l2(mx.cpu(), mfull.cpu()))
     finally:
         dist.destroy_process_group()
@@ -192,12 +209,12 @@ def test_exchange_barrier_gives_up_when_a_rank_never_arrives():
     peers = torch.tensor([mine.data_ptr(), absent.data_ptr()], dtype=torch.int64, device=dev)
     ops.device_status(dev).zero_()
     mine[1] = 1                                   # the other rank has "arrived" at epoch 1
-    ops.ep_barrier(peers, 0, 0, 1)
+    ops.ep_barrier(peers, 0, 0)                   # (my own epoch counter, slot 2, goes 0 -> 1)
     torch.cuda.synchronize()
     ops.check_device_status(dev)                  # healthy
     assert int(absent[0].item()) == 1             # and this rank told it so
     t0 = time.time()
-    ops.ep_barrier(peers, 0, 0, 2)                # nobody ever writes epoch 2 into `mine`
+    ops.ep_barrier(peers, 0, 0)                   # epoch 2: nobody ever writes it into `mine`
     torch.cuda.synchronize()
     assert 0.2 < time.time() - t0 < 10.0
     with pytest.raises(_cabi.BoltError, match="code 20"):
