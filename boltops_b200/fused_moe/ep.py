@@ -13,9 +13,13 @@ tokens.  One exchange each way:
   order with an fp32 accumulator (``bolt_moe_gather_sum``).
 
 The reference has no collective of its own: it leaves the cross-rank reduction to
-the caller.  The exchange here is ``all_to_all_single`` (NCCL over NVLink on GPUs,
-gloo in the CPU tests); index construction is device-agnostic torch so the same
-code runs under both.
+the caller.  Two exchanges are built.  On GPUs with peer access the rows travel by
+plain stores into buffers that every rank can address (:class:`DirectExchange`:
+the dispatch kernel writes into the owners' receive regions, the local layer's
+combine writes partial rows into the senders' return regions, ranks meet at a
+bounded flag barrier; no host synchronisation, replayable from a CUDA graph).
+Otherwise, and for CPU ranks in the tests, the exchange is ``all_to_all_single``
+(NCCL or gloo) with device-agnostic index construction in torch.
 """
 from __future__ import annotations
 
