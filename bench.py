@@ -537,6 +537,9 @@ def main():
     ap.add_argument("--ep-direct", type=int, default=1,
                     help="N > 1: 1 = exchange over peer memory (no collective call and no host "
                          "synchronisation on the data path), 0 = NCCL all-to-all")
+    ap.add_argument("--ep-return", default="routes", choices=["routes", "partials"],
+                    help="N > 1, peer memory: what the owners write back -- every route's row from "
+                         "the down projection's epilogue, or one partial row per token from their combine")
     ap.add_argument("--ep-replicate-below", type=int, default=4096,
                     help="N > 1: batches of at most this many tokens over all ranks take the "
                          "replicated-token path (all-gather + reduce-scatter); 0 = never")
@@ -629,10 +632,12 @@ def main():
         # replicated-token path (no host round trips); the headline batch stays on the dispatch
         ep.replicate_below = args.ep_replicate_below
         ep.direct_max_tokens = m if args.ep_direct else 0
+        ep.direct_return = args.ep_return
         ep.pipeline_chunks = args.ep_chunks
         ep.comm_sms = args.ep_comm_sms
         ep.topk_hint = cfg["K"]
-        config["ep_exchange"] = "peer memory" if args.ep_direct else "nccl all-to-all"
+        config["ep_exchange"] = f"peer memory, {args.ep_return} returned" if args.ep_direct \
+            else "nccl all-to-all"
         if not args.ep_direct:
             config["ep_chunks"] = ep.num_chunks(m)
             config["ep_comm_sms"] = args.ep_comm_sms

@@ -61,6 +61,7 @@ class GemmArgs(C.Structure):
         ("schedule", C.c_int), ("max_segments", C.c_int),
         ("segments", C.c_void_p), ("num_segments", C.c_void_p),
         ("a_gather", C.c_int), ("a_rows", C.c_int), ("a_row_bytes", C.c_int64),
+        ("scatter_src", C.c_void_p), ("scatter_seg_off", C.c_void_p), ("scatter_seg_rows", C.c_int),
     ]
 
 
@@ -152,7 +153,7 @@ _SIGNATURES = {
                                         C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "bolt_ep_unpack_routes": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int,
                                         C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
-                                        C.c_void_p]),
+                                        C.c_int64, C.c_void_p, C.c_void_p]),
     "bolt_moe_gather_sum_to_peers": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int,
                                                C.c_int, C.c_float, C.c_int64, C.c_void_p,
                                                C.c_void_p, C.c_int64, C.c_void_p]),

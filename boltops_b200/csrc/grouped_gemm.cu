@@ -100,6 +100,12 @@ struct GemmParams {
   int kb_scale_cols;  // k/128 (block-scaled kinds)
   uint32_t idesc;
   int group_m;
+  // scattered output with per-segment bases: row of token t goes to row scatter_src[t] * topk + slot
+  // of the region that lies scatter_seg_off[t / scatter_seg_rows] ELEMENTS behind c (another
+  // rank's memory in the expert-parallel exchange)
+  const int32_t* scatter_src;
+  const int64_t* scatter_seg_off;
+  int scatter_seg_rows;
   // gathered row operand: A is in TOKEN order; sorted position p reads row (sorted_ids[p] & 0xFFFFFF),
   // or zeros when that id is not a token (tile padding)
   int a_gather;
@@ -205,6 +211,36 @@ __device__ __forceinline__ void store_rows_64B(uint8_t* stage, const uint4 (&w)[
     const int64_t off = __shfl_sync(0xffffffffu, row_byte_off, r);
     if ((live_mask >> r) & 1u) {
       const uint4 x = *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
+      *reinterpret_cast<uint4*>(c + off + seg * 16) = x;
+    }
+  }
+  __syncwarp();
+}
+
+// Warp-cooperative store of a 32-row x 256-byte block (one row per lane, 128 16-bit columns) to
+// rows anywhere in memory: staged in 8 KiB of shared memory (16-byte chunk c of row r at chunk
+// position c ^ (r & 15): conflict-free both ways), then sixteen lanes write one row's 256
+// contiguous bytes per instruction.  Whole 256-byte segments are what a store over NVLink wants.
+__device__ __forceinline__ void store_rows_256B(uint8_t* stage, const float (&v)[4][32], int dt,
+                                                uint8_t* c, int64_t row_byte_off, bool live,
+                                                int lane) {
+  const unsigned live_mask = __ballot_sync(0xffffffffu, live);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 w[4];
+    pack32_16bit(v[i], dt, w);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(stage + lane * 256 + (((4 * i + j) ^ (lane & 15)) << 4)) = w[j];
+  }
+  __syncwarp();
+  const int seg = lane & 15;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const int r = (lane >> 4) + 2 * k;
+    const int64_t off = __shfl_sync(0xffffffffu, row_byte_off, r);
+    if ((live_mask >> r) & 1u) {
+      const uint4 x = *reinterpret_cast<const uint4*>(stage + r * 256 + ((seg ^ (r & 15)) << 4));
       *reinterpret_cast<uint4*>(c + off + seg * 16) = x;
     }
   }
@@ -720,8 +756,16 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const bool wr = cur.has_tile && (live || (GATED && !p.scatter));
       const float rw = cur.rw;
       int64_t out_row = row;
-      if (p.scatter) out_row = (int64_t)token * p.topk + ((uint32_t)cur.sid >> 24);
-      const int64_t row_off = out_row * p.c_ld;
+      int64_t seg_off = 0;
+      if (p.scatter) {
+        int src = token;
+        if (p.scatter_src != nullptr && live) {
+          src = p.scatter_src[token];
+          seg_off = p.scatter_seg_off[token / p.scatter_seg_rows];
+        }
+        out_row = (int64_t)src * p.topk + ((uint32_t)cur.sid >> 24);
+      }
+      const int64_t row_off = seg_off + out_row * p.c_ld;
       const int64_t brow = (int64_t)expert * p.n;  // first bias / channel-scale entry of the expert
       // first output column of this thread's half
       const int ocol = GATED ? tc.n_blk * 128 + 64 * h : tc.n_blk * 256 + 128 * h;
@@ -883,6 +927,10 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         // ---- finalise ----
         if (lane == 0) bulk_wait_read();   // the previous tile's bulk stores have left the slots
         __syncwarp();
+        // scattered 16-bit rows whose 128 columns are all inside the matrix leave as whole
+        // 256-byte segments (warp-uniform)
+        const bool wide_rows = !GATED && kSlots == 4 && p.scatter && p.c_vec_ok &&
+                               p.c_dtype != BOLT_F32 && ocol + 128 <= p.n;
         float v[4][32];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -905,8 +953,12 @@ k_grouped_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[i][j] *= rw;
             }
-            store_chunk<kSlots>(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v[i]);
+            if (!wide_rows)
+              store_chunk<kSlots>(out_stage, i, p, &tma_c, tile_row0, row_off, col0, ncols, live, lane, v[i]);
           }
+          if (wide_rows)
+            store_rows_256B(out_stage, v, p.c_dtype, static_cast<uint8_t*>(p.c), (row_off + ocol) * 2,
+                            live, lane);
         } else {
           // chunks 0,1 = gate, chunks 2,3 = up of output columns ocol + [0,64)
           float amax = 0.f;
@@ -1532,6 +1584,10 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
                  "grouped_gemm: bad c_dtype %d", a->c_dtype);
   }
   BOLT_REQUIRE(!a->scatter || a->sorted_ids, "grouped_gemm: scatter needs sorted_ids");
+  BOLT_REQUIRE(a->scatter_src == nullptr ||
+                   (a->scatter && a->scatter_seg_off != nullptr && a->scatter_seg_rows > 0 && !mx),
+               "grouped_gemm: segment-scattered output needs scatter, offsets and a segment size "
+               "(plain kinds)");
   BOLT_REQUIRE(!a->mul_routed_weight || a->sorted_weights,
                "grouped_gemm: mul_routed_weight needs sorted_weights");
 
@@ -1615,6 +1671,9 @@ extern "C" int bolt_grouped_gemm(const bolt_gemm_args* a, void* stream) {
   p.c_scale = a->c_scale;
   p.c_scale_ld = a->c_scale_ld;
   p.scatter = a->scatter;
+  p.scatter_src = a->scatter_src;
+  p.scatter_seg_off = a->scatter_seg_off;
+  p.scatter_seg_rows = a->scatter_seg_rows;
   p.c_vec_ok = (reinterpret_cast<uintptr_t>(a->c) % 16 == 0) &&
                ((a->c_ld * (int64_t)dtype_bytes(a->c_dtype)) % 16 == 0);
   // 16-bit output in sorted row order: blocks of 32 rows x 32 columns leave by bulk tensor

@@ -447,6 +447,10 @@ __global__ void __launch_bounds__(256) k_ep_dispatch(
       reinterpret_cast<int32_t*>(o)[k] = ids[t * topk + k];
       reinterpret_cast<float*>(o + k_bytes)[k] = wts[t * topk + k];
     }
+    // a wire row with 16 bytes to spare also carries the token's index on this rank (for
+    // results that come back per route, addressed by token)
+    if (lane == 0 && wire_bytes >= (int64_t)data_vecs * 16 + sc_bytes + 2 * k_bytes + 16)
+      *reinterpret_cast<int32_t*>(o + 2 * k_bytes) = (int32_t)t;
   }
 }
 
@@ -455,7 +459,7 @@ __global__ void __launch_bounds__(256) k_ep_dispatch(
 __global__ void __launch_bounds__(256) k_ep_unpack_routes(
     const uint8_t* __restrict__ recv, int64_t wire_bytes, int64_t ids_off, int64_t wts_off, int topk,
     int64_t seg_rows, int nseg, const int32_t* __restrict__ hdr, int32_t* __restrict__ ids,
-    float* __restrict__ wts) {
+    float* __restrict__ wts, int64_t src_off, int32_t* __restrict__ src) {
   const int64_t total = (int64_t)nseg * seg_rows * topk;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -466,6 +470,7 @@ __global__ void __launch_bounds__(256) k_ep_unpack_routes(
     const uint8_t* r = recv + row * wire_bytes;
     ids[i] = live ? reinterpret_cast<const int32_t*>(r + ids_off)[k] : -1;
     wts[i] = live ? reinterpret_cast<const float*>(r + wts_off)[k] : 0.f;
+    if (src != nullptr && k == 0) src[row] = live ? *reinterpret_cast<const int32_t*>(r + src_off) : 0;
   }
 }
 
@@ -538,20 +543,22 @@ extern "C" int bolt_ep_dispatch_rows(const void* data, int row_bytes, const floa
 extern "C" int bolt_ep_unpack_routes(const void* recv, int64_t wire_bytes, int64_t ids_off,
                                      int64_t wts_off, int topk, int64_t seg_rows, int nseg,
                                      const int32_t* hdr, int32_t* topk_ids, float* topk_weights,
-                                     void* stream) {
+                                     int64_t src_off, int32_t* src_tokens, void* stream) {
   using namespace bolt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BOLT_REQUIRE(recv && hdr && topk_ids && topk_weights, "ep_unpack: null pointer");
   BOLT_REQUIRE(topk > 0 && seg_rows > 0 && nseg > 0 && wire_bytes % 4 == 0 && ids_off % 4 == 0 &&
                    wts_off % 4 == 0,
                "ep_unpack: bad layout");
+  BOLT_REQUIRE(src_tokens == nullptr || (src_off % 4 == 0 && src_off + 4 <= wire_bytes),
+               "ep_unpack: bad offset of the source token index");
   const int64_t total = (int64_t)nseg * seg_rows * topk;
   int64_t blocks = (total + 255) / 256;
   const int64_t cap = (int64_t)sm_count_of_current_device() * 16;
   if (blocks > cap) blocks = cap;
   k_ep_unpack_routes<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(recv), wire_bytes,
                                                        ids_off, wts_off, topk, seg_rows, nseg, hdr,
-                                                       topk_ids, topk_weights);
+                                                       topk_ids, topk_weights, src_off, src_tokens);
   BOLT_LAUNCH_CHECK();
   return BOLT_OK;
 }

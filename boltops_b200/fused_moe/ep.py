@@ -70,14 +70,21 @@ class DirectExchange:
 
     def __init__(self, world: int, rank: int, num_experts: int, seg_rows: int, row_bytes: int,
                  groups: int, topk: int, hidden: int, out_dtype: torch.dtype, device,
-                 code_dtype: torch.dtype):
+                 code_dtype: torch.dtype, per_route: bool = False):
         self.world, self.rank, self.num_experts = world, rank, num_experts
         self.per_rank = num_experts // world
         self.seg_rows, self.row_bytes, self.groups, self.topk = seg_rows, row_bytes, groups, topk
         self.hidden, self.out_dtype, self.code_dtype = hidden, out_dtype, code_dtype
         self.device = torch.device(device)
         self.o_scale, self.o_ids, self.o_w, self.wire_bytes = wire_layout(row_bytes, groups, topk)
-        self.back_rows = seg_rows * min(world, topk)
+        # per_route: the owners' down projection writes every ROUTE's row straight into this rank's
+        # [tokens, topk, H] return region (instead of one partial row per token and rank written by
+        # their combine), so the wire row also carries the token's index here
+        self.per_route = per_route
+        self.o_src = self.wire_bytes
+        if per_route:
+            self.wire_bytes += 16
+        self.back_rows = seg_rows * (topk if per_route else min(world, topk))
         self.hdr_off = 0
         self.flag_off = _a256(world * 8)
         self.recv_off = self.flag_off + _a256((world + 1) * 4)
@@ -91,7 +98,8 @@ class DirectExchange:
         self.expert_map = emap.to(self.device)
 
     def key(self):
-        return (self.seg_rows, self.row_bytes, self.groups, self.topk, self.hidden, self.out_dtype)
+        return (self.seg_rows, self.row_bytes, self.groups, self.topk, self.hidden, self.out_dtype,
+                self.per_route)
 
     def attach(self, buf: torch.Tensor, peer_ptrs) -> None:
         """``buf``: this rank's exchange buffer (uint8, ``total_bytes``, zeroed header and
@@ -102,6 +110,10 @@ class DirectExchange:
         dev = self.device
         self.peers = torch.tensor(list(peer_ptrs), dtype=torch.int64, device=dev)
         self.back_ptrs = self.peers + self.back_off
+        esz = torch.empty((), dtype=self.out_dtype).element_size()
+        # every rank's return region, as an element offset from my own
+        self.back_seg_off = torch.tensor([(int(p) - int(peer_ptrs[self.rank])) // esz
+                                          for p in peer_ptrs], dtype=torch.int64, device=dev)
         self.hdr = buf[self.hdr_off:self.hdr_off + self.world * 8].view(torch.int32).view(
             self.world, 2)
         self.recv = buf[self.recv_off:self.recv_off + self.world * self.seg_rows
@@ -133,8 +145,16 @@ class DirectExchange:
         """Masked local layer over every row of the receive region; partial rows go straight to
         the return regions of the ranks that sent the tokens."""
         from . import layer, ops
-        r_ids, r_w = ops.ep_unpack_routes(self.recv, self.o_ids, self.o_w, self.topk,
-                                          self.seg_rows, self.world, self.hdr)
+        if self.per_route:
+            r_ids, r_w, src = ops.ep_unpack_routes(self.recv, self.o_ids, self.o_w, self.topk,
+                                                   self.seg_rows, self.world, self.hdr, self.o_src)
+            out_peers = dict(routes=self.back, src=src, seg_off=self.back_seg_off,
+                             seg_rows=self.seg_rows)
+            kwargs.pop("routed_scaling_factor", None)     # applied by the owner's final sum
+        else:
+            r_ids, r_w = ops.ep_unpack_routes(self.recv, self.o_ids, self.o_w, self.topk,
+                                              self.seg_rows, self.world, self.hdr)
+            out_peers = dict(seg_rows=self.seg_rows, seg_ptrs=self.back_ptrs, hdr=self.hdr)
         r_x = self.recv[:, :self.row_bytes].view(self.code_dtype)
         if self.groups:
             kwargs["a1_scale"] = self.recv[:, self.o_scale:self.o_scale + 4 * self.groups].view(
@@ -145,12 +165,21 @@ class DirectExchange:
         kwargs["activation"] = kwargs.get("activation") or "silu"
         layer.fused_experts_impl(
             r_x, w1_local, w2_local, r_w, r_ids, expert_map=self.expert_map,
-            global_num_experts=self.num_experts,
-            _out_peers=dict(seg_rows=self.seg_rows, seg_ptrs=self.back_ptrs, hdr=self.hdr),
-            **kwargs)
+            global_num_experts=self.num_experts, _out_peers=out_peers, **kwargs)
 
     def combine(self, pos, out, combine_fn):
         combine_fn(self.back, pos, out)
+        return out
+
+    def combine_routes(self, topk_ids, out, scale: float = 1.0):
+        """Per-route return: ``out[m] = cast(scale * sum_k f32(back[m * topk + k]))`` over the
+        routes with a valid expert id, k ascending -- the single-GPU layer's own sum."""
+        from . import ops
+        m, k = topk_ids.shape
+        slot = torch.arange(m * k, dtype=torch.int32, device=self.device).view(m, k)
+        valid = (topk_ids >= 0) & (topk_ids < self.num_experts)
+        pos = torch.where(valid, slot, torch.full_like(slot, -1))
+        ops.gather_sum(self.back, pos.contiguous(), out, scale)
         return out
 
     def barrier(self) -> None:
@@ -212,6 +241,10 @@ class ExpertParallelMoE:
         # the exchange buffers).  Falls back to the all-to-all path when the buffers cannot be
         # mapped into all ranks.
         self.direct_max_tokens = 0
+        # what comes back: "routes" = every route's row, written by the owners' down projection
+        # into [tokens, topk, H] here and summed here in the single-GPU order; "partials" = one
+        # partial row per token and rank, written by the owners' top-k combine
+        self.direct_return = "routes"
         self._direct = {}
         self._direct_failed = None
 
@@ -336,11 +369,17 @@ class ExpertParallelMoE:
         """The exchange buffers for this configuration, mapped into all ranks on first use."""
         h = hidden_states.shape[1]
         row_bytes = h * torch.empty((), dtype=code_dtype).element_size()
-        hit = self._direct.get((self.direct_max_tokens, row_bytes, groups, topk, h, out_dtype))
+        from .layer import _chunk_size
+        # per-route return needs the local layer to take everything received as one chunk
+        per_route = (self.direct_return == "routes"
+                     and self.world * self.direct_max_tokens <= _chunk_size())
+        hit = self._direct.get((self.direct_max_tokens, row_bytes, groups, topk, h, out_dtype,
+                                per_route))
         if hit is not None:
             return hit
         ex = DirectExchange(self.world, self.rank, self.num_experts, self.direct_max_tokens,
-                            row_bytes, groups, topk, h, out_dtype, hidden_states.device, code_dtype)
+                            row_bytes, groups, topk, h, out_dtype, hidden_states.device, code_dtype,
+                            per_route)
         import torch.distributed._symmetric_memory as symm_mem
         buf = symm_mem.empty(ex.total_bytes, dtype=torch.uint8, device=hidden_states.device)
         handle = symm_mem.rendezvous(buf, self.group)
@@ -376,10 +415,14 @@ class ExpertParallelMoE:
         ex.barrier()
         mark("meet 2")
         out = torch.empty((m, h), dtype=out_dtype, device=hidden_states.device)
-        ex.combine(pos, out, self.combine_fn)
+        if ex.per_route:
+            ex.combine_routes(topk_ids, out, float(kwargs.get("routed_scaling_factor") or 1.0))
+        else:
+            ex.combine(pos, out, self.combine_fn)
         mark("combine")
         self.last_stats = dict(mode="direct", routes=m * topk_ids.shape[1],
-                               exchange_bytes=ex.total_bytes)
+                               exchange_bytes=ex.total_bytes,
+                               returned="routes" if ex.per_route else "partial rows")
         if marks:
             torch.cuda.synchronize()
             self.last_stats["ms"] = {b[0]: a[1].elapsed_time(b[1])

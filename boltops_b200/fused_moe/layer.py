@@ -481,7 +481,18 @@ def fused_experts_impl(
                 act = act_f
 
         # ---- GEMM2 (router weight in the epilogue) + combine --------------------------------
-        if no_combine:
+        if _out_peers is not None and "routes" in _out_peers:
+            # expert parallelism over peer memory, per-route return: every route's row goes from
+            # the epilogue straight to its slot of the [tokens, topk, H] buffer of the rank that
+            # owns the token (ep.py); the sum over the routes happens there
+            assert begin == 0 and end == num_tokens, "per-route return takes one chunk"
+            with _Stage("gemm2"):
+                ops.grouped_gemm(epilogue=_cabi.EPI_STORE, a=act, b=w2, c=_out_peers["routes"],
+                                 a_scale=act_scale, a_scale_ld=cap, b_scale=w2_scale_c, bias=b2,
+                                 scatter=True, mul_routed_weight=needs_router_weight,
+                                 scatter_src=_out_peers["src"], scatter_seg_off=_out_peers["seg_off"],
+                                 scatter_seg_rows=_out_peers["seg_rows"], **common)
+        elif no_combine:
             # the caller wants [m, topk, H]: scatter rows to their route slots
             c3 = out[begin:end]
             if expert_map is not None:
@@ -502,7 +513,8 @@ def fused_experts_impl(
             with _Stage("combine"):
                 if _out_peers is not None:
                     ops.gather_sum_to_peers(c_sorted, route_pos, routed_scaling_factor,
-                                            first_row=begin, **_out_peers)
+                                            first_row=begin, seg_rows=_out_peers["seg_rows"],
+                                            seg_ptrs=_out_peers["seg_ptrs"], hdr=_out_peers["hdr"])
                 else:
                     ops.gather_sum(c_sorted, route_pos, out[begin:end], routed_scaling_factor)
     return out

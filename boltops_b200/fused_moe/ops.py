@@ -414,20 +414,23 @@ def ep_dispatch_rows(data: torch.Tensor, scales: Optional[torch.Tensor], topk_id
 
 
 def ep_unpack_routes(recv: torch.Tensor, ids_off: int, wts_off: int, topk: int, seg_rows: int,
-                     nseg: int, hdr: torch.Tensor):
+                     nseg: int, hdr: torch.Tensor, src_off: Optional[int] = None):
     """Dense ``(topk_ids, topk_weights)`` of all ``nseg * seg_rows`` rows of a receive region
-    (``recv`` uint8 ``[nseg * seg_rows, wire_bytes]``); rows a segment does not hold get id -1."""
+    (``recv`` uint8 ``[nseg * seg_rows, wire_bytes]``); rows a segment does not hold get id -1.
+    With ``src_off`` a third tensor: every row's token index on the rank it came from."""
     _require_cuda(recv, hdr)
     lib = _cabi.load()
     assert recv.dtype == torch.uint8 and recv.is_contiguous() and hdr.dtype == torch.int32
     rows = nseg * seg_rows
     ids = torch.empty((rows, topk), dtype=torch.int32, device=recv.device)
     wts = torch.empty((rows, topk), dtype=torch.float32, device=recv.device)
+    src = torch.empty((rows,), dtype=torch.int32, device=recv.device) if src_off is not None else None
     with _cabi.on_device(recv.device):
         check(lib.bolt_ep_unpack_routes(ptr(recv), recv.shape[1], ids_off, wts_off, topk, seg_rows,
-                                        nseg, ptr(hdr), ptr(ids), ptr(wts), stream_of(recv)))
+                                        nseg, ptr(hdr), ptr(ids), ptr(wts), src_off or 0, ptr(src),
+                                        stream_of(recv)))
     _count()
-    return ids, wts
+    return (ids, wts, src) if src_off is not None else (ids, wts)
 
 
 def ep_barrier(peers: torch.Tensor, me: int, flag_off: int) -> None:
@@ -532,11 +535,13 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
                  act_alpha: float = 1.0, act_beta: float = 0.0,
                  act_limit: Optional[float] = None, segments: Optional[torch.Tensor] = None,
                  num_segments: Optional[torch.Tensor] = None,
-                 a_gather: bool = False) -> None:
+                 a_gather: bool = False, scatter_src: Optional[torch.Tensor] = None,
+                 scatter_seg_off: Optional[torch.Tensor] = None, scatter_seg_rows: int = 0) -> None:
     """One grouped expert GEMM launch (see ``bolt_grouped_gemm``).  With ``segments`` (from
     ``moe_sorting_ck(..., segment_rows=PAIR_SEGMENT_ROWS)``) the tile-pair schedule runs.  With
     ``a_gather`` the row operand ``a`` is in TOKEN order and the kernel gathers its rows through
-    ``sorted_ids`` (padding positions read zeros)."""
+    ``sorted_ids`` (padding positions read zeros).  ``scatter_src`` / ``scatter_seg_off`` /
+    ``scatter_seg_rows``: scattered rows go to per-segment regions (see ``bolt_gemm_args``)."""
     lib = _cabi.load()
     args = _cabi.GemmArgs()
     args.kind = kind
@@ -582,6 +587,11 @@ def grouped_gemm(*, kind: int, epilogue: int, a: torch.Tensor, b: torch.Tensor, 
     args.act_beta = float(act_beta)
     args.act_limit = float(act_limit or 0.0)
     args.act_has_limit = int(act_limit is not None)
+    if scatter_src is not None:
+        assert scatter and scatter_src.dtype == torch.int32 and scatter_seg_off.dtype == torch.int64
+        args.scatter_src = ptr(scatter_src)
+        args.scatter_seg_off = ptr(scatter_seg_off)
+        args.scatter_seg_rows = scatter_seg_rows
     if segments is not None:
         args.schedule = _cabi.SCHEDULE_TILE_PAIRS
         args.max_segments = segments.shape[0]

@@ -362,7 +362,10 @@ int bolt_moe_gather_sum(const void* src, int dtype, const int32_t* pos, void* ou
  *   segment `me` of every destination's receive region and {count, first row} into its header;
  *   max_rows bounds the grid.  Counts above seg_rows are clamped and flagged in *status (21).
  * bolt_ep_unpack_routes: the receiver's dense top-k ids (-1 for rows a segment does not hold) and
- *   weights for all world * seg_rows rows, which the masked local layer then takes as its batch.
+ *   weights for all world * seg_rows rows, which the masked local layer then takes as its batch;
+ *   optionally (src_tokens != NULL) every row's token index on the rank it came from, which
+ *   bolt_ep_dispatch_rows leaves at byte bolt_ep_wire_row_bytes(...) of a wire row that is at
+ *   least 16 bytes longer than that (src_off = that byte offset).
  * bolt_moe_gather_sum_to_peers: bolt_moe_gather_sum whose output row m (m = first_row + i) goes to
  *   row hdr[2 s + 1] + q of the region seg_ptrs[s], s = m / seg_rows, q = m % seg_rows, and is
  *   skipped when q >= hdr[2 s]: the top-k combine of the local layer writes every partial row
@@ -380,7 +383,8 @@ int bolt_ep_dispatch_rows(const void* data, int row_bytes, const float* scales, 
                           int64_t recv_off, int64_t wire_bytes, int32_t* status, void* stream);
 int bolt_ep_unpack_routes(const void* recv, int64_t wire_bytes, int64_t ids_off, int64_t wts_off,
                           int topk, int64_t seg_rows, int nseg, const int32_t* hdr,
-                          int32_t* topk_ids, float* topk_weights, void* stream);
+                          int32_t* topk_ids, float* topk_weights, int64_t src_off,
+                          int32_t* src_tokens, void* stream);
 int bolt_moe_gather_sum_to_peers(const void* src, int dtype, const int32_t* pos, int64_t num_tokens,
                                  int slots, int n, float scale, int64_t seg_rows,
                                  const int64_t* seg_ptrs, const int32_t* hdr, int64_t first_row,
@@ -498,6 +502,16 @@ typedef struct bolt_gemm_args {
   int a_gather;
   int a_rows;
   int64_t a_row_bytes;
+  /* Scattered output with per-segment bases (scatter != 0, plain kinds): the row of token t goes
+     to row scatter_src[t] * topk + slot of the region that begins scatter_seg_off[t /
+     scatter_seg_rows] ELEMENTS behind c.  In the expert-parallel exchange over peer memory the
+     tokens of segment s came from rank s, scatter_src is their index there and the region is
+     rank s's [tokens, topk, n] return buffer: the down projection writes every route's row
+     straight to the rank that owns the token.  16-bit rows of the block-scaled kinds leave as
+     whole 256-byte segments.                                                                  */
+  const int32_t* scatter_src;
+  const int64_t* scatter_seg_off;
+  int scatter_seg_rows;
 } bolt_gemm_args;
 
 int bolt_grouped_gemm(const bolt_gemm_args* args, void* stream);

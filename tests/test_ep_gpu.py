@@ -71,14 +71,20 @@ def _worker(rank, world, port, ret):
         # combine, so the result equals the all-to-all path bit for bit; twice, to cross the
         # hazards between steps
         ep.direct_max_tokens = 256
-        for _ in range(2):
-            direct = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev), use_fp8_w8a8=True,
-                                w1_scale=w1s, w2_scale=w2s, block_shape=[128, 128])
-            torch.cuda.synchronize()
-            ops.check_device_status(dev)
-            assert ep._direct_failed is None, ep._direct_failed
-            assert ep.last_stats.get("mode") == "direct"
-            assert torch.equal(direct, out), "the exchange over peer memory changed the result"
+        for returned, want in (("partials", out), ("routes", full)):
+            ep.direct_return = returned
+            for _ in range(2):
+                direct = ep.forward(hidden.to(dev), w1, w2, wts.to(dev), ids.to(dev),
+                                    use_fp8_w8a8=True, w1_scale=w1s, w2_scale=w2s,
+                                    block_shape=[128, 128])
+                torch.cuda.synchronize()
+                ops.check_device_status(dev)
+                assert ep._direct_failed is None, ep._direct_failed
+                assert ep.last_stats.get("mode") == "direct"
+                # partial rows: the all-to-all path's arithmetic; per-route rows: the single-GPU
+                # layer's own sum over the routes
+                assert torch.equal(direct, want), f"exchange over peer memory ({returned})"
+        out = full
         # no host-side state in a step: captured once in a CUDA graph, replayed three times
         graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -131,18 +137,21 @@ def test_ep_plan_cuda_equals_torch_plan():
         assert torch.equal(pos_a.cpu(), pos_b.cpu())
 
 
+@pytest.mark.parametrize("per_route", [False, True])
 @pytest.mark.parametrize("kind,world,shape", [
     ("fp8_block", 4, dict(E=16, K=4, H=512, I=256)),
     ("bf16", 4, dict(E=16, K=4, H=512, I=256)),
     ("int8_channel", 4, dict(E=16, K=4, H=512, I=256)),
     ("fp8_block", 8, dict(E=64, K=8, H=1024, I=512)),       # eight ranks, top-8: the 8-GPU index space
 ])
-def test_direct_exchange_phases_with_emulated_ranks(kind, world, shape):
+def test_direct_exchange_phases_with_emulated_ranks(kind, world, shape, per_route):
     """The three phases of the exchange over peer memory for four ranks held by ONE process on
     one GPU (every "peer" buffer is a local tensor, ranks run phase by phase, no rank ever waits
     for another): headers, segment addressing, masking of unused rows and the combine are those
-    of the real thing.  Expected: the sum over ranks, in rank order, of the masked local layer on
-    the same tokens, each partial rounded to the output dtype -- bit for bit."""
+    of the real thing.  Expected, bit for bit: with partial rows coming back, the sum over ranks,
+    in rank order, of the masked local layer on the same tokens, each partial rounded to the output
+    dtype; with per-route rows coming back (the owners' down projection writes every route's row
+    into the token owner's [tokens, topk, H] region), the single-GPU layer over all experts."""
     import bench as B
     from boltops_b200.fused_moe import fused_experts, ops
     from boltops_b200.fused_moe.ep import DirectExchange
@@ -163,7 +172,7 @@ def test_direct_exchange_phases_with_emulated_ranks(kind, world, shape):
     ranks, toks, weights = [], [], []
     for r in range(world):
         ex = DirectExchange(world, r, cfg["E"], m_max, cfg["H"] * (2 if groups == 0 else 1), groups,
-                            cfg["K"], cfg["H"], torch.bfloat16, dev, code)
+                            cfg["K"], cfg["H"], torch.bfloat16, dev, code, per_route)
         ranks.append(ex)
         hidden, wts, ids = B.make_tokens(cfg, 40 + 17 * r, 70 + r)       # ragged batch sizes
         toks.append((hidden.to(dev), wts.to(dev), ids.to(dev)))
@@ -173,23 +182,32 @@ def test_direct_exchange_phases_with_emulated_ranks(kind, world, shape):
     for ex, buf in zip(ranks, bufs):
         buf[:ex.recv_off].zero_()
         ex.attach(buf, [b.data_ptr() for b in bufs])
+    full = None
+    if per_route:
+        fw1, fw2, fw1s, fw2s = B.make_weights(cfg, dev, list(range(cfg["E"])), 0)
+        full = (fw1, fw2, dict(kw, w1_scale=fw1s, w2_scale=fw2s) if fw1s is not None else dict(kw))
     for step in range(2):                                   # twice: stale rows of step one remain
         pos = [ex.dispatch(h, w, i, quant) for ex, (h, w, i) in zip(ranks, toks)]
         for ex, (w1, w2, k) in zip(ranks, weights):
-            ex.experts(w1, w2, **k)
+            ex.experts(w1, w2, routed_scaling_factor=1.5, **k)
         for r, ex in enumerate(ranks):
             h, w, i = toks[r]
             out = torch.empty_like(h)
-            ex.combine(pos[r], out, ops.gather_sum)
-            acc = torch.zeros(h.shape, dtype=torch.float32, device=dev)
-            for q, (w1, w2, k) in enumerate(weights):
-                emap = torch.full((cfg["E"],), -1, dtype=torch.int32, device=dev)
-                emap[q * per:(q + 1) * per] = torch.arange(per, dtype=torch.int32, device=dev)
-                acc += fused_experts(h, w1, w2, w, i, expert_map=emap,
-                                     global_num_experts=cfg["E"], **k).float()
+            if per_route:
+                ex.combine_routes(i, out, 1.5)
+                want = fused_experts(h, full[0], full[1], w, i, routed_scaling_factor=1.5, **full[2])
+            else:
+                ex.combine(pos[r], out, ops.gather_sum)
+                acc = torch.zeros(h.shape, dtype=torch.float32, device=dev)
+                for q, (w1, w2, k) in enumerate(weights):
+                    emap = torch.full((cfg["E"],), -1, dtype=torch.int32, device=dev)
+                    emap[q * per:(q + 1) * per] = torch.arange(per, dtype=torch.int32, device=dev)
+                    acc += fused_experts(h, w1, w2, w, i, expert_map=emap, global_num_experts=cfg["E"],
+                                         routed_scaling_factor=1.5, **k).float()
+                want = acc.to(out.dtype)
             torch.cuda.synchronize()
             ops.check_device_status(dev)
-            assert torch.equal(out, acc.to(out.dtype)), f"rank {r}, step {step}"
+            assert torch.equal(out, want), f"rank {r}, step {step}"
             sent = int((pos[r] >= 0).sum())
             assert int(ex.hdr[:, 0].sum()) == sum(int((p[:, r] >= 0).sum()) for p in pos)
             assert sent <= ex.back_rows
