@@ -205,6 +205,13 @@ def test_direct_exchange_buffer_layout():
     assert all(off % 256 == 0 for off in (a.flag_off, a.recv_off, a.back_off, a.total_bytes))
     assert a.back_rows == 4096 * 8 and a.total_bytes >= a.back_off + a.back_rows * 7168 * 2
     assert b.expert_map.tolist() == [-1] * 160 + list(range(32)) + [-1] * 64
+    # per-route return: the wire row carries the token's index, the return region has topk slots
+    c = DirectExchange(2, 1, 64, 100, 1024, 8, 4, 1024, torch.bfloat16, "cpu", torch.float8_e4m3fn,
+                       per_route=True)
+    base = wire_layout(1024, 8, 4)[3]
+    assert (c.o_src, c.wire_bytes, c.back_rows) == (base, base + 16, 100 * 4)
+    assert c.key() != DirectExchange(2, 1, 64, 100, 1024, 8, 4, 1024, torch.bfloat16, "cpu",
+                                     torch.float8_e4m3fn).key()
     # fewer ranks than top-k: a token cannot go to more ranks than there are
     assert DirectExchange(2, 0, 64, 100, 1024, 0, 8, 512, torch.bfloat16, "cpu",
                           torch.bfloat16).back_rows == 200
